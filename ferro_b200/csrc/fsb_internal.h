@@ -1,0 +1,86 @@
+// fsb_internal.h - structures shared by the host shim (fsb_shim.cpp) and the CUDA kernels (fsb_kernels.cu).
+#pragma once
+#include <stdint.h>
+
+namespace fsb {
+
+// ---- compile-time geometry of the streaming kernel ---------------------------------------------------------
+constexpr int kThreads = 256;                 // threads per CTA (8 warps)
+constexpr int kTile = 4096;                   // fp32 logits per tile (16 KiB, one bulk copy)
+constexpr int kStages = 4;                    // tiles in flight per CTA
+constexpr int kMaxK = 256;                    // largest k of the candidate path (== FSB_MAX_CANDIDATE_K)
+constexpr int kTrigger = 512;                 // candidate count above which a segment re-selects its top-k
+constexpr int kCap = kTile + kTrigger;        // candidate buffer entries: a whole tile always fits after a re-select
+constexpr int kMergeCap = kCap;               // most candidates one row may gather from all of its segments
+constexpr int kBitmapSpan = 65536;            // columns one penalty bitmap covers (one segment never spans more)
+constexpr int kBitmapWords = kBitmapSpan / 32;
+constexpr int kMaxTilesPerCta = kBitmapSpan / kTile;
+
+// status word bits written by kernels (0 = fine)
+enum : uint32_t {
+    kStatusCopyTimeout = 1u,     // a bulk copy did not land within the wait limit
+    kStatusCandOverflow = 2u,    // candidate buffer overflow (cannot happen by construction; checked anyway)
+    kStatusMergeOverflow = 4u,   // a row gathered more candidates than kMergeCap
+    kStatusEmptyRow = 8u,        // a row produced no candidate (all logits NaN)
+    kStatusBadTie = 16u          // duplicate candidate keys met in a selection
+};
+
+// row flags
+enum : int32_t {
+    kRowGreedy = 1,       // temperature <= 0 or top_k == 1: argmax, no draw
+    kRowPenalty = 2       // the row has a non-empty penalty window and penalty != 1
+};
+
+// One row of a batch, as the kernels see it (64 bytes).
+struct RowDesc {
+    uint64_t rng_word;     // raw 64-bit engine output of this row's draw (unused for greedy rows)
+    int64_t logits_off;    // element offset of the row from the logits base pointer
+    int64_t hist_begin;    // first id of the penalty window in the device history array
+    int32_t hist_len;      // ids in the window (0: no penalty)
+    int32_t k;             // effective candidate count: 1 for greedy, else (0 < top_k < n) ? top_k : n
+    float temperature;
+    float top_p;
+    float min_p;
+    float penalty;
+    int32_t flags;
+    int32_t out_index;     // position of the row's token in the output array
+    int32_t pad[2];
+};
+static_assert(sizeof(RowDesc) == 64, "RowDesc layout");
+
+// Arguments of the streaming candidate kernel.
+struct StreamArgs {
+    const float* logits;       // base of the [rows][ld] matrix
+    const RowDesc* rows;       // n_rows descriptors (only rows of the candidate path)
+    const int32_t* hist;       // packed penalty-window ids
+    uint64_t* scratch;         // [n_rows][kMergeCap] candidates emitted by the segments of each row
+    uint32_t* fill;            // [n_rows] entries used in scratch (self-resetting)
+    uint32_t* ticket;          // [n_rows] segments that have finished (self-resetting)
+    int32_t* tokens;           // output tokens, indexed by RowDesc::out_index
+    uint32_t* status;          // one word, OR of kStatus* bits
+    // optional kept-set record, indexed by out_index (null = off)
+    int32_t* kept_ids;         // [rows][kMaxK]
+    double* kept_pr;           // [rows][kMaxK]
+    int32_t* kept_n;           // [rows]
+    // optional per-row sorted candidates for the vocabulary-sharded mode (null = run the epilogue here)
+    uint64_t* shard_out;       // [rows][kMaxK] composites, descending
+    int32_t* shard_n;          // [rows]
+    int32_t n_rows;
+    int32_t n_vocab;
+    int32_t tiles_per_row;
+    int32_t tiles_per_cta;
+    int32_t total_tiles;
+    int32_t bulk_ok;           // rows start on 16-byte boundaries: tiles can come by bulk async copy
+    int32_t write_back;        // store penalised values into the caller's rows
+    int32_t vocab_offset;      // token id of column 0
+    float softcap;             // 0 = off
+};
+
+size_t stream_kernel_smem_bytes();
+// Defined in fsb_kernels.cu.  All return a cudaError_t as int (0 = success).
+int prepare_device_kernels(int* ctas_per_sm);
+int launch_stream_kernel(const StreamArgs& a, int grid, void* stream);
+int launch_merge_lists(const void* lists, const int32_t* list_n, int n_lists, int n_rows, const RowDesc* rows, int32_t* tokens,
+                       int32_t* kept_ids, double* kept_pr, int32_t* kept_n, uint32_t* status, void* stream);
+
+}  // namespace fsb

@@ -1,0 +1,787 @@
+// fsb_shim.cpp - host side of the C ABI declared in include/ferro_sampler_b200.h.
+//
+// Keeps what the reference keeps on the host, per stream: the parameter struct and the std::mt19937_64 engine
+// (src/sampler.h:30-32 of paragontasx/ferro), so the draws come from the reference's own random stream by
+// construction.  Everything that touches logits runs in the CUDA kernels; there is no host implementation of
+// the sampling path in this file.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <random>
+#include <string>
+#include <unordered_set>
+#include <vector>
+
+#include "../../include/ferro_sampler_b200.h"
+#include "fsb_internal.h"
+
+static_assert(sizeof(ferro_sampler_params) == 40, "parameter struct must match the reference's 40-byte SamplerParams");
+static_assert(offsetof(ferro_sampler_params, seed) == 32, "seed sits at offset 32 in the reference struct");
+static_assert(FSB_MAX_CANDIDATE_K == fsb::kMaxK, "header constant out of step with the kernel geometry");
+
+namespace {
+
+struct Stream {
+    ferro_sampler_params p{};
+    std::mt19937_64 rng;
+    uint64_t seed_used = 0;
+    uint64_t draws = 0;
+    bool open = false;
+};
+
+struct Plan {
+    int tiles_per_row = 0, tiles_per_cta = 0, total_tiles = 0, grid = 0;
+};
+
+}  // namespace
+
+struct fsb_batch {
+    int n_rows = 0, n_vocab = 0;
+    int64_t ld = 0;
+    unsigned flags = 0;
+    int cap_rows = 0;
+    int64_t cap_hist = 0;
+    int n_cand = 0, n_full = 0;   // rows of the candidate kernel / of the full-row kernel
+    int kmax = 1;
+    Plan plan;
+    int64_t hist_ids = 0;
+    // pinned host staging: [RowDesc x cap_rows][int32 x cap_hist], tokens
+    unsigned char* h_in = nullptr;
+    int32_t* h_tokens = nullptr;
+    // device
+    unsigned char* d_in = nullptr;
+    int32_t* d_tokens = nullptr;
+    std::vector<int> sid;
+    std::vector<unsigned char> stochastic;
+    bool launched = false;
+
+    fsb::RowDesc* h_rows() const { return reinterpret_cast<fsb::RowDesc*>(h_in); }
+    int32_t* h_hist() const { return reinterpret_cast<int32_t*>(h_in + sizeof(fsb::RowDesc) * (size_t)cap_rows); }
+    fsb::RowDesc* d_rows() const { return reinterpret_cast<fsb::RowDesc*>(d_in); }
+    int32_t* d_hist() const { return reinterpret_cast<int32_t*>(d_in + sizeof(fsb::RowDesc) * (size_t)cap_rows); }
+    size_t in_bytes_used() const { return sizeof(fsb::RowDesc) * (size_t)cap_rows + sizeof(int32_t) * (size_t)hist_ids; }
+};
+
+struct fsb_handle {
+    int device = 0;
+    int max_rows = 0, max_vocab = 0;
+    int64_t max_hist = 0;
+    int sm_count = 0, ctas_per_sm = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    float softcap = 0.0f;
+    int32_t vocab_offset = 0;
+    std::vector<Stream> streams;
+    std::vector<int> free_ids;
+    // device scratch shared by all batches of this handle
+    uint64_t* d_scratch = nullptr;
+    uint32_t* d_fill = nullptr;     // [max_rows] fill, then [max_rows] ticket, then the status word
+    uint32_t* d_status = nullptr;
+    uint32_t* h_status = nullptr;   // pinned
+    int32_t* d_kept_ids = nullptr;
+    double* d_kept_pr = nullptr;
+    int32_t* d_kept_n = nullptr;
+    bool kept_valid = false;
+    float* d_logits_stage = nullptr;   // device copy of host logits, grown on demand
+    size_t logits_stage_elems = 0;
+    fsb_batch* own = nullptr;          // the batch behind fsb_sample_batch / fsb_verify_windows
+    fsb_counters_t counters{};
+    std::string err;
+};
+
+namespace {
+
+int fail(fsb_handle* h, int code, const char* fmt, ...) {
+    if (h) {
+        char tmp[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(tmp, sizeof tmp, fmt, ap);
+        va_end(ap);
+        h->err = tmp;
+    }
+    return code;
+}
+
+#define FSB_CUDA(h, call)                                                                                  \
+    do {                                                                                                   \
+        cudaError_t e_ = (call);                                                                           \
+        if (e_ != cudaSuccess) return fail(h, FSB_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_));      \
+    } while (0)
+
+bool is_greedy(const ferro_sampler_params& p) { return p.temperature <= 0.0f || p.top_k == 1; }   // src/sampler.cpp:19
+
+// penalty window [b, len) of src/sampler.cpp:11-14; returns len when the window is empty or the penalty is off
+int64_t window_begin(const ferro_sampler_params& p, int64_t len) {
+    if (p.repetition_penalty == 1.0f || p.repeat_last_n == 0 || len <= 0) return len;
+    int64_t b = (p.repeat_last_n > 0 && (int64_t)p.repeat_last_n < len) ? len - (int64_t)p.repeat_last_n : 0;
+    if (p.penalty_from > 0) b = std::max<int64_t>(b, (int64_t)p.penalty_from);
+    return std::min(b, len);
+}
+
+Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
+    Plan pl;
+    pl.tiles_per_row = (n_vocab + fsb::kTile - 1) / fsb::kTile;
+    pl.total_tiles = n_rows * pl.tiles_per_row;
+    const int slots = std::max(1, h->sm_count * std::max(1, h->ctas_per_sm));
+    int q = (pl.total_tiles + slots - 1) / slots;
+    // a row may gather at most kMergeCap candidates: segments per row <= kMergeCap / kmax
+    const int max_seg = std::max(2, fsb::kMergeCap / std::max(1, kmax));
+    const int q_min = (pl.tiles_per_row + (max_seg - 1) - 1) / (max_seg - 1);
+    q = std::max(q, q_min);
+    q = std::max(1, std::min(q, fsb::kMaxTilesPerCta));
+    pl.tiles_per_cta = q;
+    pl.grid = (pl.total_tiles + q - 1) / q;
+    return pl;
+}
+
+void free_batch_buffers(fsb_batch* b) {
+    if (!b) return;
+    if (b->h_in) cudaFreeHost(b->h_in);
+    if (b->h_tokens) cudaFreeHost(b->h_tokens);
+    if (b->d_in) cudaFree(b->d_in);
+    if (b->d_tokens) cudaFree(b->d_tokens);
+    b->h_in = nullptr; b->h_tokens = nullptr; b->d_in = nullptr; b->d_tokens = nullptr;
+}
+
+int alloc_batch(fsb_handle* h, int cap_rows, int64_t cap_hist, fsb_batch** out) {
+    fsb_batch* b = new (std::nothrow) fsb_batch();
+    if (!b) return fail(h, FSB_ERR_INVALID, "out of host memory");
+    b->cap_rows = cap_rows;
+    b->cap_hist = std::max<int64_t>(cap_hist, 1);
+    const size_t in_bytes = sizeof(fsb::RowDesc) * (size_t)cap_rows + sizeof(int32_t) * (size_t)b->cap_hist;
+    cudaError_t e = cudaMallocHost(reinterpret_cast<void**>(&b->h_in), in_bytes);
+    if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&b->h_tokens), sizeof(int32_t) * (size_t)cap_rows);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->d_in), in_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->d_tokens), sizeof(int32_t) * (size_t)cap_rows);
+    if (e != cudaSuccess) {
+        free_batch_buffers(b);
+        delete b;
+        return fail(h, FSB_ERR_CUDA, "batch allocation: %s", cudaGetErrorString(e));
+    }
+    *out = b;
+    return FSB_OK;
+}
+
+Stream* get_stream(fsb_handle* h, int sid) {
+    if (sid < 0 || sid >= (int)h->streams.size() || !h->streams[(size_t)sid].open) return nullptr;
+    return &h->streams[(size_t)sid];
+}
+
+void fill_desc(fsb::RowDesc& d, const ferro_sampler_params& p, int n_vocab, int64_t logits_off, int64_t hist_begin, int64_t hist_len,
+               uint64_t word, int out_index) {
+    std::memset(&d, 0, sizeof d);
+    d.rng_word = word;
+    d.logits_off = logits_off;
+    d.hist_begin = hist_begin;
+    d.hist_len = (int32_t)hist_len;
+    const bool greedy = is_greedy(p);
+    d.k = greedy ? 1 : ((p.top_k > 0 && p.top_k < n_vocab) ? p.top_k : n_vocab);   // src/sampler.cpp:27
+    d.temperature = p.temperature;
+    d.top_p = p.top_p;
+    d.min_p = p.min_p;
+    d.penalty = p.repetition_penalty;
+    d.flags = (greedy ? fsb::kRowGreedy : 0) | (hist_len > 0 ? fsb::kRowPenalty : 0);
+    d.out_index = out_index;
+}
+
+// Orders the staged descriptors: candidate-path rows first, full-row-path rows after; fixes the launch plan.
+int finalize_batch(fsb_handle* h, fsb_batch* b, std::vector<fsb::RowDesc>& descs) {
+    std::vector<fsb::RowDesc> full;
+    int n_cand = 0, kmax = 1;
+    fsb::RowDesc* dst = b->h_rows();
+    for (const auto& d : descs) {
+        if (d.k <= fsb::kMaxK) {
+            dst[n_cand++] = d;
+            kmax = std::max(kmax, d.k);
+        } else {
+            full.push_back(d);
+        }
+    }
+    for (size_t i = 0; i < full.size(); ++i) dst[n_cand + (int)i] = full[i];
+    b->n_cand = n_cand;
+    b->n_full = (int)full.size();
+    b->kmax = kmax;
+    b->plan = make_plan(h, std::max(n_cand, 1), b->n_vocab, kmax);
+    if (b->n_full > 0)
+        return fail(h, FSB_ERR_CAPACITY, "rows with an effective top_k above %d need the full-row kernel, which this build lacks",
+                    fsb::kMaxK);
+    return FSB_OK;
+}
+
+int upload_batch(fsb_handle* h, fsb_batch* b) {
+    FSB_CUDA(h, cudaMemcpyAsync(b->d_in, b->h_in, b->in_bytes_used(), cudaMemcpyHostToDevice, h->stream));
+    return FSB_OK;
+}
+
+int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep_kept) {
+    if (b->n_cand > 0) {
+        fsb::StreamArgs a{};
+        a.logits = logits_dev;
+        a.rows = b->d_rows();
+        a.hist = b->d_hist();
+        a.scratch = h->d_scratch;
+        a.fill = h->d_fill;
+        a.ticket = h->d_fill + h->max_rows;
+        a.tokens = b->d_tokens;
+        a.status = h->d_status;
+        a.kept_ids = keep_kept ? h->d_kept_ids : nullptr;
+        a.kept_pr = keep_kept ? h->d_kept_pr : nullptr;
+        a.kept_n = keep_kept ? h->d_kept_n : nullptr;
+        a.shard_out = nullptr;
+        a.shard_n = nullptr;
+        a.n_rows = b->n_cand;
+        a.n_vocab = b->n_vocab;
+        a.tiles_per_row = b->plan.tiles_per_row;
+        a.tiles_per_cta = b->plan.tiles_per_cta;
+        a.total_tiles = b->n_cand * b->plan.tiles_per_row;
+        a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (b->ld & 3) == 0) ? 1 : 0;
+        a.write_back = (b->flags & FSB_WRITE_BACK) ? 1 : 0;
+        a.vocab_offset = h->vocab_offset;
+        a.softcap = h->softcap;
+        const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
+        const int e = fsb::launch_stream_kernel(a, grid, h->stream);
+        if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+        h->counters.kernel_launches++;
+    }
+    b->launched = true;
+    h->kept_valid = keep_kept;
+    return FSB_OK;
+}
+
+int fetch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out) {
+    FSB_CUDA(h, cudaMemcpyAsync(b->h_tokens, b->d_tokens, sizeof(int32_t) * (size_t)b->n_rows, cudaMemcpyDeviceToHost, h->stream));
+    FSB_CUDA(h, cudaMemcpyAsync(h->h_status, h->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, h->stream));
+    FSB_CUDA(h, cudaStreamSynchronize(h->stream));
+    if (*h->h_status != 0u) {
+        const unsigned st = *h->h_status;
+        // put the self-resetting counters and the status word back into their idle state
+        cudaMemsetAsync(h->d_fill, 0, sizeof(uint32_t) * (2 * (size_t)h->max_rows + 1), h->stream);
+        cudaStreamSynchronize(h->stream);
+        return fail(h, FSB_ERR_DEVICE, "kernel status 0x%x (1 copy timeout, 2 candidate overflow, 4 merge overflow, 8 empty row, 16 tie)", st);
+    }
+    if (tokens_out) std::memcpy(tokens_out, b->h_tokens, sizeof(int32_t) * (size_t)b->n_rows);
+    return FSB_OK;
+}
+
+int check_common(fsb_handle* h, int n_rows, int64_t ld, int n_vocab, const fsb_batch* b) {
+    if (n_rows <= 0) return fail(h, FSB_ERR_INVALID, "n_rows must be positive");
+    if (n_vocab <= 0) return fail(h, FSB_ERR_INVALID, "n_vocab must be positive");
+    if (ld < n_vocab) return fail(h, FSB_ERR_INVALID, "row stride ld is smaller than n_vocab");
+    if (n_rows > b->cap_rows) return fail(h, FSB_ERR_CAPACITY, "%d rows exceed the capacity of %d", n_rows, b->cap_rows);
+    if (n_rows > h->max_rows) return fail(h, FSB_ERR_CAPACITY, "%d rows exceed the engine's %d", n_rows, h->max_rows);
+    if (n_vocab > h->max_vocab) return fail(h, FSB_ERR_CAPACITY, "n_vocab %d exceeds the engine's %d", n_vocab, h->max_vocab);
+    return FSB_OK;
+}
+
+// Stages rows "stream_ids[i] samples row i with history i" into batch b.  Consumes engine outputs.
+int stage_rows(fsb_handle* h, fsb_batch* b, int n_rows, const int* stream_ids, int64_t ld, int n_vocab, const int32_t* hist_flat,
+               const int64_t* hist_off, unsigned flags) {
+    int rc = check_common(h, n_rows, ld, n_vocab, b);
+    if (rc) return rc;
+    if (!stream_ids) return fail(h, FSB_ERR_INVALID, "stream_ids is null");
+    if (!hist_off) return fail(h, FSB_ERR_INVALID, "hist_off is null");
+    // first pass: validate and size the staged windows, without touching any engine
+    int64_t need = 0;
+    for (int i = 0; i < n_rows; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        if (!s) return fail(h, FSB_ERR_STREAM_ID, "row %d: unknown stream id %d", i, stream_ids[i]);
+        const int64_t len = hist_off[i + 1] - hist_off[i];
+        if (len < 0) return fail(h, FSB_ERR_INVALID, "row %d: hist_off is not ascending", i);
+        if (len > 0 && !hist_flat) return fail(h, FSB_ERR_INVALID, "hist_flat is null");
+        need += len - window_begin(s->p, len);
+    }
+    if (need > b->cap_hist) return fail(h, FSB_ERR_CAPACITY, "%lld penalty-window ids exceed the capacity of %lld", (long long)need,
+                                        (long long)b->cap_hist);
+    b->n_rows = n_rows;
+    b->n_vocab = n_vocab;
+    b->ld = ld;
+    b->flags = flags;
+    b->sid.assign(stream_ids, stream_ids + n_rows);
+    b->stochastic.assign((size_t)n_rows, 0);
+    std::vector<fsb::RowDesc> descs((size_t)n_rows);
+    int32_t* hs = b->h_hist();
+    int64_t pos = 0;
+    for (int i = 0; i < n_rows; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        const int64_t len = hist_off[i + 1] - hist_off[i];
+        const int64_t wb = window_begin(s->p, len), wl = len - wb;
+        if (wl > 0) std::memcpy(hs + pos, hist_flat + hist_off[i] + wb, sizeof(int32_t) * (size_t)wl);
+        uint64_t word = 0;
+        if (!is_greedy(s->p)) {   // exactly one engine output per stochastic call, none per greedy call
+            word = s->rng();
+            s->draws++;
+            b->stochastic[(size_t)i] = 1;
+        }
+        fill_desc(descs[(size_t)i], s->p, n_vocab, (int64_t)i * ld, pos, wl, word, i);
+        pos += wl;
+    }
+    b->hist_ids = pos;
+    return finalize_batch(h, b, descs);
+}
+
+void count_rows(fsb_handle* h, const fsb_batch* b, int n_sampled_mask_all) {
+    (void)n_sampled_mask_all;
+    for (int i = 0; i < b->n_rows; ++i) {
+        h->counters.rows_sampled++;
+        if (b->stochastic[(size_t)i]) h->counters.rows_stochastic++;
+        else h->counters.rows_greedy++;
+    }
+    h->counters.rows_full_vocab += (uint64_t)b->n_full;
+}
+
+int stage_host_logits(fsb_handle* h, const float* logits, int n_rows, int64_t ld, int n_vocab, const float** dev) {
+    const size_t elems = (size_t)(n_rows - 1) * (size_t)ld + (size_t)n_vocab;
+    if (elems > h->logits_stage_elems) {
+        if (h->d_logits_stage) cudaFree(h->d_logits_stage);
+        h->d_logits_stage = nullptr;
+        h->logits_stage_elems = 0;
+        FSB_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->d_logits_stage), elems * sizeof(float)));
+        h->logits_stage_elems = elems;
+    }
+    FSB_CUDA(h, cudaMemcpyAsync(h->d_logits_stage, logits, elems * sizeof(float), cudaMemcpyHostToDevice, h->stream));
+    *dev = h->d_logits_stage;
+    return FSB_OK;
+}
+
+// The reference modifies the caller's host row in place (src/sampler.cpp:17).  With host logits the kernels work
+// on a device copy, so the side effect is replayed on the caller's buffer: the same fp32 operation on the same
+// distinct ids.  This touches only the penalised entries and takes no part in choosing the token.
+void replay_penalty_on_host(float* row, int n_vocab, const ferro_sampler_params& p, const int32_t* hist, int64_t len, int32_t id_offset) {
+    const int64_t b = window_begin(p, len);
+    if (b >= len) return;
+    std::unordered_set<int> seen;
+    for (int64_t i = b; i < len; ++i) {
+        const int id = hist[i] - id_offset;
+        if (id < 0 || id >= n_vocab || !seen.insert(id).second) continue;
+        row[id] = row[id] > 0 ? row[id] / p.repetition_penalty : row[id] * p.repetition_penalty;
+    }
+}
+
+}  // namespace
+
+// ================================================================================================ C ABI
+extern "C" {
+
+void fsb_params_default(ferro_sampler_params* p) {
+    if (!p) return;
+    std::memset(p, 0, sizeof *p);
+    p->temperature = 0.05f;
+    p->top_k = 50;
+    p->top_p = 1.0f;
+    p->min_p = 0.0f;
+    p->repetition_penalty = 1.05f;
+    p->repeat_last_n = -1;
+    p->penalty_from = 0;
+    p->seed = 0;
+}
+
+int fsb_params_validate(const ferro_sampler_params* p) {
+    if (!p) return FSB_ERR_INVALID;
+    // src/server.cpp:1071, negated; written so that NaNs fail
+    if (!(p->temperature >= 0.0f)) return FSB_ERR_RANGE;
+    if (!(p->top_p > 0.0f && p->top_p <= 1.0f)) return FSB_ERR_RANGE;
+    if (p->top_k < 0) return FSB_ERR_RANGE;
+    if (!(p->repetition_penalty > 0.0f) || std::isinf(p->repetition_penalty)) return FSB_ERR_RANGE;
+    if (p->repeat_last_n < -1) return FSB_ERR_RANGE;
+    if (!(p->min_p >= 0.0f && p->min_p <= 1.0f)) return FSB_ERR_RANGE;
+    if (p->penalty_from < 0) return FSB_ERR_RANGE;
+    if (std::isinf(p->temperature)) return FSB_ERR_RANGE;
+    return FSB_OK;
+}
+
+int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fsb_handle** out) {
+    if (!out) return FSB_ERR_INVALID;
+    *out = nullptr;
+    if (max_rows <= 0 || max_vocab <= 0 || max_hist_ids < 0) return FSB_ERR_INVALID;
+    if (max_vocab > (1 << 20)) return FSB_ERR_CAPACITY;
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev <= 0 || device < 0 || device >= n_dev) {
+        cudaGetLastError();
+        return FSB_ERR_NO_DEVICE;
+    }
+    fsb_handle* h = new (std::nothrow) fsb_handle();
+    if (!h) return FSB_ERR_INVALID;
+    h->device = device;
+    h->max_rows = max_rows;
+    h->max_vocab = max_vocab;
+    h->max_hist = max_hist_ids;
+    auto bail = [&](int code) {
+        fsb_destroy(h);
+        return code;
+    };
+    if (cudaSetDevice(device) != cudaSuccess) return bail(FSB_ERR_NO_DEVICE);
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return bail(FSB_ERR_CUDA);
+    if (prop.major < 10) return bail(FSB_ERR_NO_DEVICE);   // kernels are built for sm_100a only
+    h->sm_count = prop.multiProcessorCount;
+    if (fsb::prepare_device_kernels(&h->ctas_per_sm) != 0 || h->ctas_per_sm <= 0) return bail(FSB_ERR_CUDA);
+    if (cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(FSB_ERR_CUDA);
+    h->own_stream = true;
+    const size_t ctr_words = 2 * (size_t)max_rows + 1;
+    if (cudaMalloc(reinterpret_cast<void**>(&h->d_scratch), sizeof(uint64_t) * (size_t)max_rows * fsb::kMergeCap) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_fill), sizeof(uint32_t) * ctr_words) != cudaSuccess ||
+        cudaMemset(h->d_fill, 0, sizeof(uint32_t) * ctr_words) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void**>(&h->h_status), sizeof(uint32_t)) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_kept_ids), sizeof(int32_t) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_kept_pr), sizeof(double) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_kept_n), sizeof(int32_t) * (size_t)max_rows) != cudaSuccess)
+        return bail(FSB_ERR_CUDA);
+    h->d_status = h->d_fill + 2 * (size_t)max_rows;
+    if (alloc_batch(h, max_rows, max_hist_ids, &h->own) != FSB_OK) return bail(FSB_ERR_CUDA);
+    *out = h;
+    return FSB_OK;
+}
+
+int fsb_destroy(fsb_handle* h) {
+    if (!h) return FSB_ERR_INVALID;
+    cudaSetDevice(h->device);
+    if (h->stream) cudaStreamSynchronize(h->stream);
+    if (h->own) {
+        free_batch_buffers(h->own);
+        delete h->own;
+    }
+    if (h->d_scratch) cudaFree(h->d_scratch);
+    if (h->d_fill) cudaFree(h->d_fill);
+    if (h->h_status) cudaFreeHost(h->h_status);
+    if (h->d_kept_ids) cudaFree(h->d_kept_ids);
+    if (h->d_kept_pr) cudaFree(h->d_kept_pr);
+    if (h->d_kept_n) cudaFree(h->d_kept_n);
+    if (h->d_logits_stage) cudaFree(h->d_logits_stage);
+    if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
+    delete h;
+    return FSB_OK;
+}
+
+const char* fsb_last_error(const fsb_handle* h) { return h ? h->err.c_str() : "null handle"; }
+
+int fsb_set_cuda_stream(fsb_handle* h, void* cuda_stream) {
+    if (!h) return FSB_ERR_INVALID;
+    cudaSetDevice(h->device);
+    if (h->stream) cudaStreamSynchronize(h->stream);
+    if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
+    h->stream = static_cast<cudaStream_t>(cuda_stream);
+    h->own_stream = false;
+    return FSB_OK;
+}
+
+int fsb_set_softcap(fsb_handle* h, float cap) {
+    if (!h) return FSB_ERR_INVALID;
+    if (!(cap >= 0.0f) || std::isinf(cap)) return fail(h, FSB_ERR_RANGE, "softcap must be finite and >= 0");
+    h->softcap = cap;
+    return FSB_OK;
+}
+
+int fsb_set_vocab_offset(fsb_handle* h, int32_t offset) {
+    if (!h) return FSB_ERR_INVALID;
+    if (offset < 0) return fail(h, FSB_ERR_RANGE, "vocab offset must be >= 0");
+    h->vocab_offset = offset;
+    return FSB_OK;
+}
+
+int fsb_stream_open(fsb_handle* h, const ferro_sampler_params* p, int* stream_id) {
+    if (!h || !p || !stream_id) return fail(h, FSB_ERR_INVALID, "null argument");
+    const int v = fsb_params_validate(p);
+    if (v != FSB_OK) return fail(h, v, "sampling parameter out of range");
+    int id;
+    if (!h->free_ids.empty()) {
+        id = h->free_ids.back();
+        h->free_ids.pop_back();
+    } else {
+        id = (int)h->streams.size();
+        h->streams.emplace_back();
+    }
+    Stream& s = h->streams[(size_t)id];
+    s.p = *p;
+    s.seed_used = p->seed ? p->seed : (uint64_t)std::random_device{}();   // src/sampler.h:25
+    s.rng.seed(s.seed_used);
+    s.draws = 0;
+    s.open = true;
+    *stream_id = id;
+    return FSB_OK;
+}
+
+int fsb_stream_close(fsb_handle* h, int stream_id) {
+    if (!h) return FSB_ERR_INVALID;
+    Stream* s = get_stream(h, stream_id);
+    if (!s) return fail(h, FSB_ERR_STREAM_ID, "unknown stream id %d", stream_id);
+    s->open = false;
+    h->free_ids.push_back(stream_id);
+    return FSB_OK;
+}
+
+int fsb_stream_params(const fsb_handle* h, int stream_id, ferro_sampler_params* out) {
+    if (!h || !out) return FSB_ERR_INVALID;
+    Stream* s = get_stream(const_cast<fsb_handle*>(h), stream_id);
+    if (!s) return FSB_ERR_STREAM_ID;
+    *out = s->p;
+    return FSB_OK;
+}
+
+int fsb_stream_state_get(const fsb_handle* h, int stream_id, uint64_t* seed, uint64_t* draws) {
+    if (!h) return FSB_ERR_INVALID;
+    Stream* s = get_stream(const_cast<fsb_handle*>(h), stream_id);
+    if (!s) return FSB_ERR_STREAM_ID;
+    if (seed) *seed = s->seed_used;
+    if (draws) *draws = s->draws;
+    return FSB_OK;
+}
+
+int fsb_stream_state_set(fsb_handle* h, int stream_id, uint64_t seed, uint64_t draws) {
+    if (!h) return FSB_ERR_INVALID;
+    Stream* s = get_stream(h, stream_id);
+    if (!s) return fail(h, FSB_ERR_STREAM_ID, "unknown stream id %d", stream_id);
+    s->seed_used = seed;
+    s->rng.seed(seed);
+    s->rng.discard(draws);
+    s->draws = draws;
+    return FSB_OK;
+}
+
+int fsb_sample_batch(fsb_handle* h, int n_rows, const int* stream_ids, const float* logits, int64_t ld, int n_vocab,
+                     const int32_t* hist_flat, const int64_t* hist_off, int32_t* tokens_out, unsigned flags) {
+    if (!h) return FSB_ERR_INVALID;
+    if (!logits || !tokens_out) return fail(h, FSB_ERR_INVALID, "null logits or tokens_out");
+    cudaSetDevice(h->device);
+    fsb_batch* b = h->own;
+    int rc = stage_rows(h, b, n_rows, stream_ids, ld, n_vocab, hist_flat, hist_off, flags);
+    if (rc) return rc;
+    const bool on_host = (flags & FSB_LOGITS_ON_HOST) != 0;
+    if (on_host) b->flags &= ~FSB_WRITE_BACK;   // the device copy is private; the side effect is replayed below
+    rc = upload_batch(h, b);
+    if (rc) return rc;
+    const float* dev = logits;
+    if (on_host) {
+        rc = stage_host_logits(h, logits, n_rows, ld, n_vocab, &dev);
+        if (rc) return rc;
+    }
+    rc = launch_batch(h, b, dev, (flags & FSB_KEEP_KEPT_SET) != 0);
+    if (rc) return rc;
+    rc = fetch_tokens(h, b, tokens_out);
+    if (rc) return rc;
+    if (on_host && (flags & FSB_WRITE_BACK)) {
+        for (int i = 0; i < n_rows; ++i) {
+            const Stream* s = get_stream(h, stream_ids[i]);
+            replay_penalty_on_host(const_cast<float*>(logits) + (int64_t)i * ld, n_vocab, s->p, hist_flat + hist_off[i],
+                                   hist_off[i + 1] - hist_off[i], h->vocab_offset);
+        }
+    }
+    count_rows(h, b, 0);
+    return FSB_OK;
+}
+
+int fsb_verify_windows(fsb_handle* h, int n_streams, const int* stream_ids, const int* row_off, const int32_t* rows_flat,
+                       const float* logits, int64_t ld, int n_vocab, const int32_t* hist_flat, const int64_t* hist_off,
+                       const int* max_accept, int32_t* tokens_out, int* acc_out, int* confirmed_out, unsigned flags) {
+    if (!h) return FSB_ERR_INVALID;
+    if (!stream_ids || !row_off || !rows_flat || !logits || !hist_off || !tokens_out || !acc_out)
+        return fail(h, FSB_ERR_INVALID, "null argument");
+    if (n_streams <= 0) return fail(h, FSB_ERR_INVALID, "n_streams must be positive");
+    if (flags & FSB_WRITE_BACK) return fail(h, FSB_ERR_INVALID, "write-back is not defined for verification windows");
+    cudaSetDevice(h->device);
+    fsb_batch* b = h->own;
+    const int n_rows = row_off[n_streams] - row_off[0];
+    if (row_off[0] != 0) return fail(h, FSB_ERR_INVALID, "row_off[0] must be 0");
+    int rc = check_common(h, n_rows, ld, n_vocab, b);
+    if (rc) return rc;
+    // validate, size the staging
+    int64_t need = 0;
+    for (int i = 0; i < n_streams; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        if (!s) return fail(h, FSB_ERR_STREAM_ID, "stream %d: unknown stream id %d", i, stream_ids[i]);
+        for (int j = 0; j < i; ++j)
+            if (stream_ids[j] == stream_ids[i]) return fail(h, FSB_ERR_INVALID, "stream id %d appears twice", stream_ids[i]);
+        const int m = row_off[i + 1] - row_off[i];
+        const int64_t len = hist_off[i + 1] - hist_off[i];
+        if (m <= 0 || len < 0) return fail(h, FSB_ERR_INVALID, "stream %d: empty window or bad history offsets", i);
+        if (len > 0 && !hist_flat) return fail(h, FSB_ERR_INVALID, "hist_flat is null");
+        need += (len - window_begin(s->p, len)) + (m - 1);
+    }
+    if (need > b->cap_hist) return fail(h, FSB_ERR_CAPACITY, "%lld penalty-window ids exceed the capacity of %lld", (long long)need,
+                                        (long long)b->cap_hist);
+    b->n_rows = n_rows;
+    b->n_vocab = n_vocab;
+    b->ld = ld;
+    b->flags = flags;
+    b->sid.assign((size_t)n_rows, 0);
+    b->stochastic.assign((size_t)n_rows, 0);
+    std::vector<fsb::RowDesc> descs((size_t)n_rows);
+    int32_t* hs = b->h_hist();
+    int64_t pos = 0;
+    for (int i = 0; i < n_streams; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        const int r0 = row_off[i], m = row_off[i + 1] - r0;
+        const int64_t len = hist_off[i + 1] - hist_off[i];
+        const bool pen_on = !(s->p.repetition_penalty == 1.0f || s->p.repeat_last_n == 0);
+        // row r samples with history_i followed by draft_1..draft_r; the windows of successive rows only move
+        // forward, so one staged copy [b_0 .. len + m - 1) serves the whole stream
+        const int64_t b0 = pen_on ? window_begin(s->p, len) : len;
+        const int64_t base = pos;
+        if (pen_on) {
+            if (len > b0) std::memcpy(hs + pos, hist_flat + hist_off[i] + b0, sizeof(int32_t) * (size_t)(len - b0));
+            pos += len - b0;
+            for (int r = 1; r < m; ++r) hs[pos++] = rows_flat[r0 + r];
+        }
+        std::mt19937_64 look = s->rng;   // draws are taken from a copy; the real engine advances by acc afterwards
+        const bool greedy = is_greedy(s->p);
+        for (int r = 0; r < m; ++r) {
+            int64_t hb = 0, hl = 0;
+            if (pen_on) {
+                const int64_t len_r = len + r;
+                const int64_t br = window_begin(s->p, len_r);
+                hb = base + (br - b0);
+                hl = len_r - br;
+            }
+            const uint64_t word = greedy ? 0ull : look();
+            b->sid[(size_t)(r0 + r)] = stream_ids[i];
+            b->stochastic[(size_t)(r0 + r)] = greedy ? 0 : 1;
+            fill_desc(descs[(size_t)(r0 + r)], s->p, n_vocab, (int64_t)(r0 + r) * ld, hb, hl, word, r0 + r);
+        }
+    }
+    b->hist_ids = pos;
+    rc = finalize_batch(h, b, descs);
+    if (rc) return rc;
+    rc = upload_batch(h, b);
+    if (rc) return rc;
+    const float* dev = logits;
+    if (flags & FSB_LOGITS_ON_HOST) {
+        rc = stage_host_logits(h, logits, n_rows, ld, n_vocab, &dev);
+        if (rc) return rc;
+    }
+    rc = launch_batch(h, b, dev, (flags & FSB_KEEP_KEPT_SET) != 0);
+    if (rc) return rc;
+    rc = fetch_tokens(h, b, nullptr);
+    if (rc) return rc;
+    // accept loop of src/server.cpp:626-636 on the sampled tokens
+    for (int i = 0; i < n_streams; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        const int r0 = row_off[i], m = row_off[i + 1] - r0;
+        const int lim = (max_accept && max_accept[i] > 0 && max_accept[i] < m) ? max_accept[i] : m;
+        int acc = 0, conf = 0;
+        for (int r = 0; r < lim; ++r) {
+            const int tok = b->h_tokens[r0 + r];
+            tokens_out[r0 + r] = tok;
+            acc = r + 1;
+            if (r + 1 < m && tok == rows_flat[r0 + r + 1]) {
+                if (r + 1 < lim) ++conf;
+                continue;
+            }
+            break;
+        }
+        for (int r = acc; r < m; ++r) tokens_out[r0 + r] = -1;
+        acc_out[i] = acc;
+        if (confirmed_out) confirmed_out[i] = conf;
+        if (!is_greedy(s->p)) {
+            s->rng.discard((unsigned long long)acc);
+            s->draws += (uint64_t)acc;
+            h->counters.rows_stochastic += (uint64_t)acc;
+        } else {
+            h->counters.rows_greedy += (uint64_t)acc;
+        }
+        h->counters.rows_sampled += (uint64_t)acc;
+        h->counters.drafted += (uint64_t)(m - 1);
+        h->counters.accepted += (uint64_t)conf;
+    }
+    return FSB_OK;
+}
+
+int fsb_last_kept(fsb_handle* h, int row, int cap, int32_t* ids, double* probs, int* n_keep) {
+    if (!h || !n_keep) return FSB_ERR_INVALID;
+    if (!h->kept_valid) return fail(h, FSB_ERR_INVALID, "the last call did not record kept sets (FSB_KEEP_KEPT_SET)");
+    if (row < 0 || row >= h->max_rows) return fail(h, FSB_ERR_INVALID, "row out of range");
+    cudaSetDevice(h->device);
+    int32_t n = 0;
+    FSB_CUDA(h, cudaMemcpy(&n, h->d_kept_n + row, sizeof n, cudaMemcpyDeviceToHost));
+    *n_keep = n;
+    const int c = std::min(std::min(cap, (int)n), fsb::kMaxK);
+    if (c > 0 && ids) FSB_CUDA(h, cudaMemcpy(ids, h->d_kept_ids + (size_t)row * fsb::kMaxK, sizeof(int32_t) * (size_t)c, cudaMemcpyDeviceToHost));
+    if (c > 0 && probs) FSB_CUDA(h, cudaMemcpy(probs, h->d_kept_pr + (size_t)row * fsb::kMaxK, sizeof(double) * (size_t)c, cudaMemcpyDeviceToHost));
+    return FSB_OK;
+}
+
+int fsb_batch_prepare(fsb_handle* h, int n_rows, const int* stream_ids, int64_t ld, int n_vocab, const int32_t* hist_flat,
+                      const int64_t* hist_off, unsigned flags, fsb_batch** out) {
+    if (!h || !out) return FSB_ERR_INVALID;
+    *out = nullptr;
+    if (flags & FSB_LOGITS_ON_HOST) return fail(h, FSB_ERR_INVALID, "prepared batches take device logits");
+    if (n_rows <= 0 || !hist_off) return fail(h, FSB_ERR_INVALID, "bad arguments");
+    cudaSetDevice(h->device);
+    fsb_batch* b = nullptr;
+    int rc = alloc_batch(h, n_rows, hist_off[n_rows] - hist_off[0], &b);
+    if (rc) return rc;
+    rc = stage_rows(h, b, n_rows, stream_ids, ld, n_vocab, hist_flat, hist_off, flags);
+    if (rc == FSB_OK) rc = upload_batch(h, b);
+    if (rc == FSB_OK && cudaStreamSynchronize(h->stream) != cudaSuccess) rc = fail(h, FSB_ERR_CUDA, "upload failed");
+    if (rc) {
+        free_batch_buffers(b);
+        delete b;
+        return rc;
+    }
+    *out = b;
+    return FSB_OK;
+}
+
+int fsb_batch_redraw(fsb_handle* h, fsb_batch* b) {
+    if (!h || !b) return FSB_ERR_INVALID;
+    cudaSetDevice(h->device);
+    fsb::RowDesc* rows = b->h_rows();
+    for (int j = 0; j < b->n_rows; ++j) {
+        const int i = rows[j].out_index;
+        if (!b->stochastic[(size_t)i]) continue;
+        Stream* s = get_stream(h, b->sid[(size_t)i]);
+        if (!s) return fail(h, FSB_ERR_STREAM_ID, "stream id %d was closed", b->sid[(size_t)i]);
+    }
+    // rows draw in row order, as a per-slot loop would
+    std::vector<int> order((size_t)b->n_rows);
+    for (int j = 0; j < b->n_rows; ++j) order[(size_t)rows[j].out_index] = j;
+    for (int i = 0; i < b->n_rows; ++i) {
+        if (!b->stochastic[(size_t)i]) continue;
+        Stream* s = get_stream(h, b->sid[(size_t)i]);
+        rows[order[(size_t)i]].rng_word = s->rng();
+        s->draws++;
+    }
+    FSB_CUDA(h, cudaMemcpyAsync(b->d_in, b->h_in, sizeof(fsb::RowDesc) * (size_t)b->n_rows, cudaMemcpyHostToDevice, h->stream));
+    return FSB_OK;
+}
+
+int fsb_batch_launch(fsb_handle* h, fsb_batch* b, const float* logits_dev) {
+    if (!h || !b || !logits_dev) return FSB_ERR_INVALID;
+    cudaSetDevice(h->device);
+    return launch_batch(h, b, logits_dev, (b->flags & FSB_KEEP_KEPT_SET) != 0);
+}
+
+int fsb_batch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out) {
+    if (!h || !b || !tokens_out) return FSB_ERR_INVALID;
+    if (!b->launched) return fail(h, FSB_ERR_INVALID, "the batch has not been launched");
+    cudaSetDevice(h->device);
+    const int rc = fetch_tokens(h, b, tokens_out);
+    if (rc == FSB_OK) count_rows(h, b, 0);
+    return rc;
+}
+
+int fsb_batch_kernel_count(const fsb_batch* b) {
+    if (!b) return 0;
+    return (b->n_cand > 0 ? 1 : 0) + (b->n_full > 0 ? 1 : 0);
+}
+
+int fsb_batch_free(fsb_handle* h, fsb_batch* b) {
+    if (!h || !b) return FSB_ERR_INVALID;
+    cudaSetDevice(h->device);
+    cudaStreamSynchronize(h->stream);
+    free_batch_buffers(b);
+    delete b;
+    return FSB_OK;
+}
+
+int fsb_counters(const fsb_handle* h, fsb_counters_t* out) {
+    if (!h || !out) return FSB_ERR_INVALID;
+    *out = h->counters;
+    return FSB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,169 @@
+/*
+ * ferro_sampler_b200.h - C ABI of the B200 batched token sampler.
+ *
+ * Drop-in boundary for the token sampler of paragontasx/ferro (reference paths below are relative
+ * to that project's root).  The reference has no FFI layer for this path: it is a C++ class,
+ * ferro::Sampler (src/sampler.h:23-34), called once per produced token per stream by the decode
+ * loops.  This header exports the same operation as a plain-C interface over hand-written sm_100a
+ * CUDA kernels: one call samples a whole batch of rows (one row per stream / verification-window
+ * position).  A header-only C++ adapter with the reference's own class signature lives in
+ * ferro_sampler_b200.hpp.
+ *
+ * Conventions
+ *   - every function returns 0 (FSB_OK) or a negative fsb_status; nothing throws, nothing aborts;
+ *   - fsb_last_error() gives the text of the most recent failure on a handle;
+ *   - a handle is single-threaded (like the reference sampler, which only the one inference worker
+ *     thread touches, src/server.cpp:3-4); distinct handles are independent;
+ *   - there is no CPU fallback: without a CUDA device fsb_create fails with FSB_ERR_NO_DEVICE.
+ */
+#ifndef FERRO_SAMPLER_B200_H
+#define FERRO_SAMPLER_B200_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define FSB_API __attribute__((visibility("default")))
+#else
+#define FSB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Field-for-field the reference's `struct SamplerParams` (src/sampler.h:12-21): 40 bytes, seed at offset 32. */
+typedef struct ferro_sampler_params {
+    float temperature;        /* <= 0 (or top_k == 1): greedy argmax after the penalty; default 0.05 */
+    int32_t top_k;            /* 0 = off (all tokens are candidates); default 50 */
+    float top_p;              /* 1 = off; default 1 */
+    float min_p;              /* 0 = off; default 0 */
+    float repetition_penalty; /* 1 = off; default 1.05 */
+    int32_t repeat_last_n;    /* penalty window: last N history ids; -1 = whole history; 0 = no penalty */
+    int32_t penalty_from;     /* history positions before this are never penalised */
+    uint64_t seed;            /* 0 = nondeterministic (std::random_device), as in the reference */
+} ferro_sampler_params;
+
+typedef struct fsb_handle fsb_handle; /* one sampler engine bound to one CUDA device */
+typedef struct fsb_batch fsb_batch;   /* a prepared, device-resident batch (see fsb_batch_prepare) */
+
+typedef enum fsb_status {
+    FSB_OK = 0,
+    FSB_ERR_INVALID = -1,   /* null pointer, negative size, bad flag combination */
+    FSB_ERR_RANGE = -2,     /* a sampling parameter outside the ranges the reference's server accepts */
+    FSB_ERR_CAPACITY = -3,  /* rows / vocabulary / history beyond what the handle was created for */
+    FSB_ERR_CUDA = -4,      /* a CUDA runtime call failed; text in fsb_last_error */
+    FSB_ERR_STREAM_ID = -5, /* unknown or closed stream id */
+    FSB_ERR_NO_DEVICE = -6, /* no usable CUDA device */
+    FSB_ERR_DEVICE = -7     /* a kernel reported an internal error through its status word */
+} fsb_status;
+
+/* flags of fsb_sample_batch / fsb_verify_windows / fsb_batch_prepare */
+enum {
+    FSB_LOGITS_ON_HOST = 1u, /* `logits` is a host pointer (staged to the device inside the call); default: device pointer */
+    FSB_WRITE_BACK = 2u,     /* store the penalised logits back into the caller's rows, the reference's in-place side
+                                effect ("logits: [n_vocab], modified in place", src/sampler.h:26) */
+    FSB_KEEP_KEPT_SET = 4u   /* record every row's kept set (ids + probabilities) for fsb_last_kept */
+};
+
+/* Largest effective k (after the reference's clamp k = (0 < top_k < n_vocab) ? top_k : n_vocab) that
+ * the single-pass candidate kernel handles; rows with a larger k take the multi-pass full-row kernel. */
+#define FSB_MAX_CANDIDATE_K 256
+
+/* ---- engine ------------------------------------------------------------------------------------------- */
+
+/* Create an engine on CUDA device `device` able to take batches of up to max_rows rows of up to max_vocab
+ * logits with up to max_hist_ids penalty-window ids per batch in total.  All scratch is allocated here.
+ * Replaces: construction of the per-request samplers' shared resources; no reference counterpart
+ * (the reference keeps a scratch vector inside each Sampler, src/sampler.h:33). */
+FSB_API int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fsb_handle** out);
+FSB_API int fsb_destroy(fsb_handle* h);
+FSB_API const char* fsb_last_error(const fsb_handle* h);
+
+/* Launch on the caller's CUDA stream (a cudaStream_t passed as void*) instead of the handle's own. */
+FSB_API int fsb_set_cuda_stream(fsb_handle* h, void* cuda_stream);
+
+/* Fuse the final-logit softcap x = cap * tanhf(x / cap) in front of the penalty (the producer-side step
+ * of src/model_gemma4.cpp:520-521).  cap = 0 turns it off (the default: the caller's logits are final). */
+FSB_API int fsb_set_softcap(fsb_handle* h, float cap);
+
+/* Column offset of this device's vocabulary shard: local column c is token id c + offset (vocab sharding). */
+FSB_API int fsb_set_vocab_offset(fsb_handle* h, int32_t offset);
+
+/* Reference defaults (src/sampler.h:13-20) and the range check of the reference's request parser
+ * (src/server.cpp:1071: temperature >= 0, 0 < top_p <= 1, top_k >= 0, repetition_penalty > 0, repeat_last_n >= -1)
+ * extended by 0 <= min_p <= 1 and penalty_from >= 0. */
+FSB_API void fsb_params_default(ferro_sampler_params* p);
+FSB_API int fsb_params_validate(const ferro_sampler_params* p);
+
+/* ---- streams: one per request, like `new Sampler(j.sp)` at src/server.cpp:545 ---------------------------- */
+
+/* Opens a stream: copies the parameters and seeds a std::mt19937_64 exactly as src/sampler.h:25 does. */
+FSB_API int fsb_stream_open(fsb_handle* h, const ferro_sampler_params* p, int* stream_id);
+FSB_API int fsb_stream_close(fsb_handle* h, int stream_id);
+/* Sampler::params() (src/sampler.h:29) */
+FSB_API int fsb_stream_params(const fsb_handle* h, int stream_id, ferro_sampler_params* out);
+/* The engine position as (seed actually used, number of 64-bit outputs consumed); set re-creates it. */
+FSB_API int fsb_stream_state_get(const fsb_handle* h, int stream_id, uint64_t* seed, uint64_t* draws);
+FSB_API int fsb_stream_state_set(fsb_handle* h, int stream_id, uint64_t seed, uint64_t draws);
+
+/* ---- sampling ------------------------------------------------------------------------------------------- */
+
+/* Equivalent to, for i in 0..n_rows-1 in order:
+ *     tokens_out[i] = stream[stream_ids[i]].sample(logits + i*ld, n_vocab, history_i)      (src/sampler.cpp:10-50)
+ * i.e. the per-slot loop of a decode step (src/server.cpp:603-608) as one device call.
+ * history_i = hist_flat[hist_off[i] .. hist_off[i+1]) (host memory; all tokens of the context so far).
+ * One 64-bit engine output is consumed per stochastic row, none per greedy row.  Synchronous: tokens are
+ * in tokens_out (host) on return.  The history is not modified (the caller appends, src/server.cpp:342). */
+FSB_API int fsb_sample_batch(fsb_handle* h, int n_rows, const int* stream_ids, const float* logits, int64_t ld, int n_vocab,
+                     const int32_t* hist_flat, const int64_t* hist_off, int32_t* tokens_out, unsigned flags);
+
+/* Speculative verification windows (the accept loop of src/server.cpp:626-645) for n_streams streams.
+ * Stream i owns rows row_off[i] .. row_off[i+1]) of `logits`; rows_flat holds, per stream, [last token, draft_1 ..
+ * draft_{m-1}] as the scheduler builds them (src/server.cpp:617).  Row r is sampled with history_i followed by
+ * draft_1..draft_r, and is accepted while every earlier sampled token equalled the next draft.  On return
+ * tokens_out[row] holds the sampled token of every accepted row (-1 for rows the reference would not have
+ * sampled), acc_out[i] the number of rows sampled, confirmed_out[i] the number of confirmed drafts, and each
+ * stream's engine has advanced by exactly the draws of its sampled rows.  max_accept (may be NULL) caps acc per
+ * stream (e.g. the remaining token budget). */
+FSB_API int fsb_verify_windows(fsb_handle* h, int n_streams, const int* stream_ids, const int* row_off, const int32_t* rows_flat,
+                       const float* logits, int64_t ld, int n_vocab, const int32_t* hist_flat, const int64_t* hist_off,
+                       const int* max_accept, int32_t* tokens_out, int* acc_out, int* confirmed_out, unsigned flags);
+
+/* Kept set of row `row` of the most recent call made with FSB_KEEP_KEPT_SET: the candidates that survived
+ * min-p / top-p in (logit descending, id ascending) order with their probabilities (normalised over the k
+ * candidates, as src/sampler.cpp:41 leaves them).  At most `cap` entries are copied; *n_keep is the full size. */
+FSB_API int fsb_last_kept(fsb_handle* h, int row, int cap, int32_t* ids, double* probs, int* n_keep);
+
+/* ---- device-resident batches (serving loops that keep everything on the device; the benchmark) -------------- */
+
+/* Validates and uploads everything a batch needs except the logits: row descriptors (parameters, penalty
+ * windows, one engine output per stochastic row) and the window ids.  The same batch can then be launched many
+ * times on different logits buffers. */
+FSB_API int fsb_batch_prepare(fsb_handle* h, int n_rows, const int* stream_ids, int64_t ld, int n_vocab,
+                      const int32_t* hist_flat, const int64_t* hist_off, unsigned flags, fsb_batch** out);
+/* Draw fresh engine outputs for the batch's stochastic rows and upload them (8 bytes per row). */
+FSB_API int fsb_batch_redraw(fsb_handle* h, fsb_batch* b);
+/* Enqueue the kernels for one step on `logits_dev` ([n_rows][ld] fp32 in device memory); asynchronous. */
+FSB_API int fsb_batch_launch(fsb_handle* h, fsb_batch* b, const float* logits_dev);
+/* Wait for the last launch of `b` and copy its tokens (n_rows int32) to host memory. */
+FSB_API int fsb_batch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out);
+/* Number of kernels one fsb_batch_launch enqueues (for launch accounting). */
+FSB_API int fsb_batch_kernel_count(const fsb_batch* b);
+FSB_API int fsb_batch_free(fsb_handle* h, fsb_batch* b);
+
+/* ---- counters --------------------------------------------------------------------------------------------- */
+typedef struct fsb_counters_t {
+    uint64_t rows_sampled;    /* rows that produced a token */
+    uint64_t rows_greedy;     /* of those, greedy rows (no engine output) */
+    uint64_t rows_stochastic; /* of those, rows that consumed one engine output */
+    uint64_t rows_full_vocab; /* rows that took the multi-pass full-row kernel */
+    uint64_t drafted;         /* drafts offered to fsb_verify_windows (src/server.cpp:639 spec_drafted) */
+    uint64_t accepted;        /* drafts confirmed (spec_accepted) */
+    uint64_t kernel_launches; /* kernels enqueued by this handle */
+} fsb_counters_t;
+FSB_API int fsb_counters(const fsb_handle* h, fsb_counters_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FERRO_SAMPLER_B200_H */
