@@ -39,6 +39,7 @@ PARAMS_DTYPE = np.dtype(
 
 API_SYMBOLS = [
     "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset",
+    "fsb_set_trace_buffer",
     "fsb_params_default", "fsb_params_validate", "fsb_stream_open", "fsb_stream_close", "fsb_stream_params",
     "fsb_stream_state_get", "fsb_stream_state_set", "fsb_sample_batch", "fsb_verify_windows", "fsb_last_kept",
     "fsb_batch_prepare", "fsb_batch_redraw", "fsb_batch_launch", "fsb_batch_tokens", "fsb_batch_kernel_count",
@@ -85,6 +86,7 @@ def load_library(build_if_missing: bool = True):
     L.fsb_set_cuda_stream.argtypes = [vp, vp]
     L.fsb_set_softcap.argtypes = [vp, C.c_float]
     L.fsb_set_vocab_offset.argtypes = [vp, C.c_int32]
+    L.fsb_set_trace_buffer.argtypes = [vp, vp]
     L.fsb_params_default.argtypes = [vp]
     L.fsb_params_default.restype = None
     L.fsb_params_validate.argtypes = [vp]
@@ -208,6 +210,9 @@ class Engine:
 
     def set_softcap(self, cap: float):
         self._check(self.lib.fsb_set_softcap(self._h, float(cap)))
+
+    def set_trace_buffer(self, device_ptr: int):
+        self._check(self.lib.fsb_set_trace_buffer(self._h, C.c_void_p(int(device_ptr)) if device_ptr else None))
 
     def set_vocab_offset(self, offset: int):
         self._check(self.lib.fsb_set_vocab_offset(self._h, int(offset)))

@@ -5,12 +5,12 @@
 namespace fsb {
 
 // ---- compile-time geometry of the streaming kernel ---------------------------------------------------------
-constexpr int kThreads = 256;                 // threads per CTA (8 warps)
+constexpr int kThreads = 256;                 // consumer threads per CTA (8 warps); the streaming kernel adds one producer warp
 constexpr int kTile = 4096;                   // fp32 logits per tile (16 KiB, one bulk copy)
 constexpr int kStages = 4;                    // tiles in flight per CTA
 constexpr int kMaxK = 256;                    // largest k of the candidate path (== FSB_MAX_CANDIDATE_K)
-constexpr int kTrigger = 512;                 // candidate count above which a segment re-selects its top-k
-constexpr int kCap = kTile + kTrigger;        // candidate buffer entries: a whole tile always fits after a re-select
+constexpr int kLaneQueue = 16;                // candidates each lane can queue between two re-selections
+constexpr int kCap = kLaneQueue * kThreads;   // candidate buffer entries of a CTA (32 KiB)
 constexpr int kMergeCap = kCap;               // most candidates one row may gather from all of its segments
 constexpr int kBitmapSpan = 65536;            // columns one penalty bitmap covers (one segment never spans more)
 constexpr int kBitmapWords = kBitmapSpan / 32;
@@ -65,6 +65,8 @@ struct StreamArgs {
     // optional per-row sorted candidates for the vocabulary-sharded mode (null = run the epilogue here)
     uint64_t* shard_out;       // [rows][kMaxK] composites, descending
     int32_t* shard_n;          // [rows]
+    uint64_t* trace;           // optional [grid][8] timestamps (diagnostics), null = off
+    int64_t row_ld;            // >= 0: row r starts at r * row_ld (no descriptor read before the first copy)
     int32_t n_rows;
     int32_t n_vocab;
     int32_t tiles_per_row;
@@ -74,6 +76,7 @@ struct StreamArgs {
     int32_t write_back;        // store penalised values into the caller's rows
     int32_t vocab_offset;      // token id of column 0
     float softcap;             // 0 = off
+    int32_t dbg;
 };
 
 size_t stream_kernel_smem_bytes();

@@ -89,6 +89,7 @@ struct fsb_handle {
     bool kept_valid = false;
     float* d_logits_stage = nullptr;   // device copy of host logits, grown on demand
     size_t logits_stage_elems = 0;
+    uint64_t* d_trace = nullptr;       // caller-owned diagnostics buffer, or null
     fsb_batch* own = nullptr;          // the batch behind fsb_sample_batch / fsb_verify_windows
     fsb_counters_t counters{};
     std::string err;
@@ -235,6 +236,8 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.kept_n = keep_kept ? h->d_kept_n : nullptr;
         a.shard_out = nullptr;
         a.shard_n = nullptr;
+        a.trace = h->d_trace;
+        a.row_ld = (b->n_full == 0) ? b->ld : -1;   // descriptors are in row order when every row takes this kernel
         a.n_rows = b->n_cand;
         a.n_vocab = b->n_vocab;
         a.tiles_per_row = b->plan.tiles_per_row;
@@ -244,6 +247,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.write_back = (b->flags & FSB_WRITE_BACK) ? 1 : 0;
         a.vocab_offset = h->vocab_offset;
         a.softcap = h->softcap;
+        a.dbg = getenv("FSB_DEBUG") ? atoi(getenv("FSB_DEBUG")) : 0;
         const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
         const int e = fsb::launch_stream_kernel(a, grid, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
@@ -474,6 +478,12 @@ int fsb_set_softcap(fsb_handle* h, float cap) {
     if (!h) return FSB_ERR_INVALID;
     if (!(cap >= 0.0f) || std::isinf(cap)) return fail(h, FSB_ERR_RANGE, "softcap must be finite and >= 0");
     h->softcap = cap;
+    return FSB_OK;
+}
+
+int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer) {
+    if (!h) return FSB_ERR_INVALID;
+    h->d_trace = static_cast<uint64_t*>(device_buffer);
     return FSB_OK;
 }
 

@@ -86,6 +86,11 @@ FSB_API int fsb_set_cuda_stream(fsb_handle* h, void* cuda_stream);
  * of src/model_gemma4.cpp:520-521).  cap = 0 turns it off (the default: the caller's logits are final). */
 FSB_API int fsb_set_softcap(fsb_handle* h, float cap);
 
+/* Diagnostics: when set to a device buffer of 8 uint64 per CTA (4096 CTAs at most), the streaming kernel writes
+ * time stamps of its phases there: slot 0 the start in %globaltimer ns, slot 7 the start in SM cycles, and in SM
+ * cycles 1 copies issued, 2 first tile landed, 3 first bound set, 4 streaming done, 5 candidates published, 6 exit.  NULL (the default) turns it off.  No reference counterpart. */
+FSB_API int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer);
+
 /* Column offset of this device's vocabulary shard: local column c is token id c + offset (vocab sharding). */
 FSB_API int fsb_set_vocab_offset(fsb_handle* h, int32_t offset);
 
