@@ -149,7 +149,7 @@ __device__ __forceinline__ void for_each_candidate(const u64* myq, int mycnt, co
 // valid admission bound for later candidates.  `out` is kMaxK entries of scratch; dst may be the shared list
 // itself.  All kThreads consumer threads must call.  MSB-first radix descent, starting at the highest bit in
 // which the candidates differ and stopping as soon as a digit bucket is taken whole.
-__device__ __noinline__ int select_topk(const u64* myq, int mycnt, const u64* list, int list_n, int k, u64* out, u64* dst,
+static __device__ __noinline__ int select_topk(const u64* myq, int mycnt, const u64* list, int list_n, int k, u64* out, u64* dst,
                                         SharedCtl* ctl, unsigned* status, u64* L_out) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     u64 mn = ~0ull, mx = 0ull;
@@ -280,7 +280,7 @@ struct TailOut {
 // Selects the k best, orders them, and either hands them out (vocabulary-sharded mode) or finishes the row:
 // softmax over the candidates in fp64, sequential sums in candidate order, min-p, top-p, draw.
 // All threads of the CTA must call it with the same arguments.
-__device__ __noinline__ void finish_row(u64* buf, int total, const RowTail r, u64* out, SharedCtl* ctl, const TailOut o) {
+static __device__ __noinline__ void finish_row(u64* buf, int total, const RowTail r, u64* out, SharedCtl* ctl, const TailOut o) {
     const int tid = threadIdx.x;
     if (total > r.k) total = select_topk(nullptr, 0, buf, total, r.k, out, buf, ctl, o.status, nullptr);
     const int kk = total;

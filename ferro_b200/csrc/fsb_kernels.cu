@@ -44,7 +44,6 @@ constexpr long long kCopyWaitCycles = 2000000000ll;   // about 1 s: a bulk copy 
 constexpr int kWarps = kThreads / 32;
 constexpr int kWTile = kTile / kWarps;          // 512 logits = 2 KiB per bulk copy
 constexpr int kBlockThreads = kThreads + 32;    // consumers + the producer warp
-constexpr int kRefresh = 4;                     // the admission bound is refreshed every kRefresh tiles
 static_assert(kWTile == 512, "a lane owns four float4 of a warp tile");
 static_assert(kLaneQueue >= 4, "a lane must be able to queue one float4 after a re-selection");
 static_assert(kWarps <= 32, "one producer lane per consumer warp");
@@ -244,6 +243,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const S
     int mycnt = 0;    // entries in this lane's queue
     int nkept = 0;    // entries in the survivors' list (the same value in every thread)
     int dbg_events = 0;
+    long long acc[6] = {0, 0, 0, 0, 0, 0}, tq, tn;
 
     for (int it = 0; it < nt; ++it) {
         const int col0 = j * kTile + warp * kWTile;          // first column of this warp's part
@@ -285,6 +285,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const S
 
         // ---- wait for the CTA tile's copy.  A warp that is waiting (or about to) also answers re-selection requests
         // of other warps: a requester sits at the barrier of cta_event, and the ring only moves when every warp does.
+        tq = clock64();
         if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&ctl->need_compact) != 0))
             cta_event(false, d.k, myq, &mycnt, kept, &nkept, out, ctl, a.status, &thr_f, &thr_comp);
         if (a.bulk_ok) {
@@ -310,40 +311,24 @@ __global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const S
             if (SOFTCAP) softcap_tile(st, len, sc.cap, sc.wb_row ? sc.wb_row + col0 : nullptr);
             if (sc.has_pen && !(a.dbg & 8)) patch_tile(st, len, col0, sc, bitmap, bm_lo);
         }
+        tn = clock64(); acc[0] += tn - tq; tq = tn;
         if (it == 0) trace_mark(a, 2);
 
-        // ---- look: the lane's 16 logits go to registers (four independent 16-byte loads), the slot goes back to the
-        // producer at once; logits past the end of a ragged row count as -inf
-        const float4* st4 = reinterpret_cast<const float4*>(st);
-        const float ninf = -__int_as_float(0x7f800000);
-        float4 x0, x1, x2, x3;
-        if (a.dbg & 4) {
-            x0 = x1 = x2 = x3 = make_float4(0.f, 0.f, 0.f, 0.f);
-        } else if (len == kWTile) {
-            x0 = st4[lane];
-            x1 = st4[lane + 32];
-            x2 = st4[lane + 64];
-            x3 = st4[lane + 96];
-        } else {
-            float v[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int e = 4 * (lane + 32 * (i >> 2)) + (i & 3);
-                v[i] = e < len ? st[e] : ninf;
-            }
-            x0 = make_float4(v[0], v[1], v[2], v[3]);
-            x1 = make_float4(v[4], v[5], v[6], v[7]);
-            x2 = make_float4(v[8], v[9], v[10], v[11]);
-            x3 = make_float4(v[12], v[13], v[14], v[15]);
+        // ---- look: the lane's 16 logits go to registers (four independent 16-byte loads); what lies past the end of
+        // a ragged row is made -inf first
+        float4* st4 = reinterpret_cast<float4*>(st);
+        if (len < kWTile) {
+            for (int e = len + lane; e < kWTile; e += 32) st[e] = -__int_as_float(0x7f800000);
+            __syncwarp();
         }
-        __syncwarp();
-        if (lane == 0 && a.bulk_ok) mbar_arrive(&ctl->empty[slot]);
+        float4 x0 = st4[lane], x1 = st4[lane + 32], x2 = st4[lane + 64], x3 = st4[lane + 96];
         const float m0 = fmaxf(max3(x0.x, x0.y, x0.z), x0.w);
         const float m1 = fmaxf(max3(x1.x, x1.y, x1.z), x1.w);
         const float m2 = fmaxf(max3(x2.x, x2.y, x2.z), x2.w);
         const float m3 = fmaxf(max3(x3.x, x3.y, x3.z), x3.w);
         run_max = fmaxf(max3(run_max, m0, m1), fmaxf(m2, m3));
 
+        tn = clock64(); acc[1] += tn - tq; tq = tn;
         // ---- the admission bound: set at the segment's first tile (all warps must have posted: one barrier per
         // segment), then refreshed without a barrier at tiles 1, 2, 4, 8, ... of the segment
         if (new_seg) {
@@ -360,9 +345,11 @@ __global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const S
         }
         ++seg_it;
 
+        tn = clock64(); acc[2] += tn - tq; tq = tn;
         // ---- admit: a lane looks closer only at those of its four float4 that hold a logit at or above the bound
         unsigned pend = (m0 >= thr_f ? 1u : 0u) | (m1 >= thr_f ? 2u : 0u) | (m2 >= thr_f ? 4u : 0u) | (m3 >= thr_f ? 8u : 0u);
         if (!(a.dbg & 1) && __any_sync(0xffffffffu, pend != 0u)) {
+            acc[5] += 1;
             const int id_lane = col0 + 4 * lane + sc.id_base;   // token id of this lane's first logit
             const int lim = len - 4 * lane;                      // logits of the row from there on (ragged tiles)
             // queue the admitted logits of float4 number Q (X), unless the queue may not take four more
@@ -385,17 +372,24 @@ __global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const S
                 // a lane's queue is full: the CTA re-selects, then the float4 still pending are looked at again
                 cta_event(true, d.k, myq, &mycnt, kept, &nkept, out, ctl, a.status, &thr_f, &thr_comp);
                 ++dbg_events;
+                x0 = st4[lane];   // reloaded rather than kept alive across the call
+                x1 = st4[lane + 32];
+                x2 = st4[lane + 64];
+                x3 = st4[lane + 96];
                 pend &= (m0 >= thr_f ? 1u : 0u) | (m1 >= thr_f ? 2u : 0u) | (m2 >= thr_f ? 4u : 0u) | (m3 >= thr_f ? 8u : 0u);
             }
 #undef FSB_ADMIT_BLOCK
         }
+        __syncwarp();
+        if (lane == 0 && a.bulk_ok) mbar_arrive(&ctl->empty[slot]);   // hand the slot back to the producer
+        tn = clock64(); acc[3] += tn - tq;
 
         const bool seg_end = (it == nt - 1) || (j == T - 1);
         if (seg_end) {
             while (cta_event(false, d.k, myq, &mycnt, kept, &nkept, out, ctl, a.status, &thr_f, &thr_comp)) {
             }
             if (it == nt - 1) trace_mark(a, 4);
-            if (it == nt - 1 && a.trace) { const int tot = __reduce_add_sync(0xffffffffu, mycnt); if (lane == 0) { atomicAdd((unsigned long long*)(a.trace + 4096 * 8 + (size_t)blockIdx.x * 8), (unsigned long long)tot); atomicAdd((unsigned long long*)(a.trace + 4096 * 8 + (size_t)blockIdx.x * 8 + 1), (unsigned long long)dbg_events); if (warp == 0) { a.trace[4096 * 8 + (size_t)blockIdx.x * 8 + 2] = (uint64_t)nkept; a.trace[4096 * 8 + (size_t)blockIdx.x * 8 + 3] = (uint64_t)__float_as_uint(thr_f); } } }
+            if (it == nt - 1 && a.trace) { const int tot = __reduce_add_sync(0xffffffffu, mycnt); if (lane == 0) { atomicAdd((unsigned long long*)(a.trace + 4096 * 8 + (size_t)blockIdx.x * 8), (unsigned long long)tot); atomicAdd((unsigned long long*)(a.trace + 4096 * 8 + (size_t)blockIdx.x * 8 + 1), (unsigned long long)dbg_events); if (warp == 0) { uint64_t* t3 = a.trace + 4096 * 16 + (size_t)blockIdx.x * 8; for (int q = 0; q < 6; ++q) t3[q] = (uint64_t)acc[q]; a.trace[4096 * 8 + (size_t)blockIdx.x * 8 + 2] = (uint64_t)nkept; a.trace[4096 * 8 + (size_t)blockIdx.x * 8 + 3] = (uint64_t)__float_as_uint(thr_f); } } }
             // the segment's k best (or all, if fewer) go to the survivors' list, contiguous
             const int c = select_topk(myq, mycnt, kept, nkept, d.k, out, kept, ctl, a.status, nullptr);
             const int first_cta = (row * T) / Q, last_cta = (row * T + T - 1) / Q;

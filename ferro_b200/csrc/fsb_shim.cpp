@@ -89,6 +89,8 @@ struct fsb_handle {
     bool kept_valid = false;
     float* d_logits_stage = nullptr;   // device copy of host logits, grown on demand
     size_t logits_stage_elems = 0;
+    uint64_t* d_weights = nullptr;     // fixed-point weights of the full-row kernel, grown on demand
+    size_t weights_elems = 0;
     uint64_t* d_trace = nullptr;       // caller-owned diagnostics buffer, or null
     fsb_batch* own = nullptr;          // the batch behind fsb_sample_batch / fsb_verify_windows
     fsb_counters_t counters{};
@@ -209,9 +211,6 @@ int finalize_batch(fsb_handle* h, fsb_batch* b, std::vector<fsb::RowDesc>& descs
     b->n_full = (int)full.size();
     b->kmax = kmax;
     b->plan = make_plan(h, std::max(n_cand, 1), b->n_vocab, kmax);
-    if (b->n_full > 0)
-        return fail(h, FSB_ERR_CAPACITY, "rows with an effective top_k above %d need the full-row kernel, which this build lacks",
-                    fsb::kMaxK);
     return FSB_OK;
 }
 
@@ -251,6 +250,23 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
         const int e = fsb::launch_stream_kernel(a, grid, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+        h->counters.kernel_launches++;
+    }
+    if (b->n_full > 0) {   // rows whose candidate set does not fit on chip: the multi-pass full-row kernel
+        const size_t need = (size_t)b->n_full * (size_t)b->n_vocab;
+        if (need > h->weights_elems) {
+            FSB_CUDA(h, cudaStreamSynchronize(h->stream));
+            if (h->d_weights) cudaFree(h->d_weights);
+            h->d_weights = nullptr;
+            h->weights_elems = 0;
+            FSB_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->d_weights), need * sizeof(uint64_t)));
+            h->weights_elems = need;
+        }
+        const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, b->d_hist(), h->d_weights, b->d_tokens,
+                                                  keep_kept ? h->d_kept_ids : nullptr, keep_kept ? h->d_kept_pr : nullptr,
+                                                  keep_kept ? h->d_kept_n : nullptr, h->d_status, b->n_vocab, h->vocab_offset,
+                                                  (b->flags & FSB_WRITE_BACK) ? 1 : 0, h->softcap, h->stream);
+        if (e != 0) return fail(h, FSB_ERR_CUDA, "full-row kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         h->counters.kernel_launches++;
     }
     b->launched = true;
@@ -425,6 +441,7 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
     if (prop.major < 10) return bail(FSB_ERR_NO_DEVICE);   // kernels are built for sm_100a only
     h->sm_count = prop.multiProcessorCount;
     if (fsb::prepare_device_kernels(&h->ctas_per_sm) != 0 || h->ctas_per_sm <= 0) return bail(FSB_ERR_CUDA);
+    if (fsb::prepare_full_row_kernel(max_vocab) != 0) return bail(FSB_ERR_CUDA);
     if (cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(FSB_ERR_CUDA);
     h->own_stream = true;
     const size_t ctr_words = 2 * (size_t)max_rows + 1;
@@ -457,6 +474,7 @@ int fsb_destroy(fsb_handle* h) {
     if (h->d_kept_pr) cudaFree(h->d_kept_pr);
     if (h->d_kept_n) cudaFree(h->d_kept_n);
     if (h->d_logits_stage) cudaFree(h->d_logits_stage);
+    if (h->d_weights) cudaFree(h->d_weights);
     if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
     delete h;
     return FSB_OK;
