@@ -3,8 +3,9 @@
 //  * order-preserving 64-bit candidate keys ("composites"): (logit descending, token id ascending) becomes plain
 //    unsigned descending order, with -0.0f and +0.0f mapped to the same key - the order of the reference's
 //    comparator `a.first > b.first || (a.first == b.first && a.second < b.second)` (src/sampler.cpp:31,34);
-//  * mbarrier + 1-D bulk asynchronous copy (global -> this CTA's shared memory) wrappers with bounded waits;
-//  * a CTA-wide radix selection of the k largest composites held in shared memory;
+//  * mbarrier + 1-D bulk asynchronous copy (global -> this CTA's shared memory) wrappers; streaming 16-byte
+//    loads and the programmatic-dependent-launch controls;
+//  * a CTA-wide selection of the k largest composites by bisection with counting barriers;
 //  * the per-row epilogue: softmax in fp64 with the reference's sequential sums, min-p, top-p and the draw
 //    (src/sampler.cpp:37-49).
 #pragma once
@@ -68,9 +69,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned by
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
-// One poll of a barrier phase.  The suspend-time hint lets the hardware park the thread until the phase completes
-// (or the hint runs out) instead of re-polling: idle warps then stay out of the shared-memory pipeline that the
-// working warps need.
+// One poll of a barrier phase, with a suspend-time hint (the hardware may park the thread until the phase completes).
 __device__ __forceinline__ bool mbar_try_wait(u64* bar, unsigned parity) {
     unsigned ok;
     asm volatile(
@@ -92,72 +91,71 @@ __device__ __forceinline__ bool mbar_test_wait(u64* bar, unsigned parity) {
                  : "memory");
     return ok != 0;
 }
+// ---------------------------------------------------------------------------------------------- loads, launch order
+// 16-byte load of logits that are read exactly once: read-only path, no L1 allocation.
+__device__ __forceinline__ float4 ldg_stream(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p));
+    return v;
+}
+// Programmatic dependent launch: let the next launch in the stream begin as resources free up, and wait for the
+// previous launch to be complete (and its memory visible) before touching anything it wrote.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ u64 global_timer_ns() {
     u64 t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: gives up after limit_cycles SM clocks and reports false; the caller records the failure and
-// carries on.  (The SM cycle counter is read, not %globaltimer: a read of the global timer costs about a
-// microsecond, which would be paid on every tile.)
-__device__ __forceinline__ bool mbar_wait_bounded(u64* bar, unsigned parity, long long limit_cycles) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 16; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > limit_cycles) return false;
-    }
-}
 
 // ---------------------------------------------------------------------------------------------- shared control block
-constexpr int kNumWarps = kThreads / 32;   // consumer warps of a CTA
+constexpr int kNumWarps = kThreads / 32;
 
 // Barrier of the kThreads consumer threads of a CTA (named barrier 1).  The streaming kernel has one more warp,
 // the copy producer, which never takes part in it; kernels with only kThreads threads use it like __syncthreads().
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
+// What the streaming kernel knows about the segment it is working on (written once per segment by one thread).
+struct SegCtx {
+    const float* row;   // the row's logits
+    float pen;          // repetition penalty of the row
+    float cap;          // softcap, 0 = off
+    int has_pen;
+    int id_base;        // token id of column 0
+    int seg_lo;         // first column of the segment (= column of bit 0 of the bitmap)
+    int n_vocab;
+    int vec_ok;         // rows start on 16-byte boundaries
+    int k;              // the row's candidate count
+    int final_in_mem;   // write-back mode: the row in global memory already holds the transformed logits
+};
+
 struct SharedCtl {
     u64 full[kStages];                // "tile landed": completed by the copy (or by the producer for tiny tails)
     u64 empty[kStages];               // "tile consumed": every consumer warp hands the ring slot back
-    u64 red[16];                      // cross-warp reduction scratch
+    u64 red[2 * kNumWarps];           // cross-warp reduction scratch
     double dsum;
-    unsigned hist[256];
-    float wbound[kNumWarps];          // per-warp admission bounds (see the streaming kernel)
+    alignas(16) float wbound[kNumWarps];   // per-warp admission bounds (see the streaming kernel); read with 16-byte loads
+    int wcount[kNumWarps];            // cells queued by each warp, posted at a rendez-vous
+    int sum[3];                       // rotating counters of the selection steps
     int out_cnt;
-    int sel_digit, sel_above, sel_count;
     int base, last;
     int imax, imin1, imin2;
-    int abort;
-    int need_compact;                 // a lane found its candidate queue full
+    int need_compact;                 // a lane's queue is nearly full: the CTA must re-select
+    int abort;                        // a copy did not land in time
+    int fill;                         // cells gathered into the flat list
+    int unfinished;                   // lanes that still hold queued cells during a gather
+    u64 ev_bound;                     // composite bound of the latest re-selection (0: nothing was dropped)
+    SegCtx seg;
 };
 
-// The candidates a selection looks at: this thread's own queue (entries myq[s * 32], s < mycnt) plus a list of
-// composites shared by the CTA (list[i], i < list_n, dealt to the threads).  Calls f(c) for every candidate once.
-template <class F>
-__device__ __forceinline__ void for_each_candidate(const u64* myq, int mycnt, const u64* list, int list_n, F f) {
-#pragma unroll 1
-    for (int s = 0; s < mycnt; ++s) f(myq[s * 32]);
-#pragma unroll 1
-    for (int i = threadIdx.x; i < list_n; i += kThreads) f(list[i]);
-}
-
 // ---------------------------------------------------------------------------------------------- top-k selection
-// Writes the k largest candidates (all of them when there are no more than k) to dst, unordered, and returns how
-// many.  *L_out receives a bound L with: chosen == { c : c >= L } (0 when everything was taken), so L is also a
-// valid admission bound for later candidates.  `out` is kMaxK entries of scratch; dst may be the shared list
-// itself.  All kThreads consumer threads must call.  MSB-first radix descent, starting at the highest bit in
-// which the candidates differ and stopping as soon as a digit bucket is taken whole.
-static __device__ __noinline__ int select_topk(const u64* myq, int mycnt, const u64* list, int list_n, int k, u64* out, u64* dst,
-                                        SharedCtl* ctl, unsigned* status, u64* L_out) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    u64 mn = ~0ull, mx = 0ull;
-    for_each_candidate(myq, mycnt, list, list_n, [&](u64 c) {
-        mn = min(mn, c);
-        mx = max(mx, c);
-    });
-    int cnt = __reduce_add_sync(0xffffffffu, mycnt);
+// Smallest and largest of the composites the threads hold (each thread passes the extremes of its own; threads
+// with nothing pass ~0 and 0).  All threads of the CTA must call.
+__device__ __forceinline__ void cta_minmax(u64& mn, u64& mx, SharedCtl* ctl) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
         mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
@@ -165,95 +163,80 @@ static __device__ __noinline__ int select_topk(const u64* myq, int mycnt, const 
     }
     if (lane == 0) {
         ctl->red[warp] = mn;
-        ctl->red[8 + warp] = mx;
-        ctl->hist[warp] = (unsigned)cnt;
+        ctl->red[kNumWarps + warp] = mx;
     }
     consumer_sync();
     mn = ctl->red[0];
-    mx = ctl->red[8];
-    cnt = list_n + (int)ctl->hist[0];
+    mx = ctl->red[kNumWarps];
 #pragma unroll
     for (int w = 1; w < kNumWarps; ++w) {
         mn = min(mn, ctl->red[w]);
-        mx = max(mx, ctl->red[8 + w]);
-        cnt += (int)ctl->hist[w];
+        mx = max(mx, ctl->red[kNumWarps + w]);
     }
-    consumer_sync();   // hist is reused below
-    u64 mask = 0ull, pfx = 0ull;
-    if (cnt > k) {
-        int need = k;
-        if (mx != mn) {
-            int hb = 63 - __clzll((long long)(mx ^ mn));
-            mask = (hb == 63) ? 0ull : (~0ull << (hb + 1));
-            pfx = mx & mask;
-            for (;;) {
-                const int w = hb + 1 < 8 ? hb + 1 : 8, lo = hb + 1 - w;
-                const unsigned dmask = (1u << w) - 1u;
-                ctl->hist[tid] = 0u;
-                consumer_sync();
-                for_each_candidate(myq, mycnt, list, list_n, [&](u64 c) {
-                    if ((c & mask) == pfx) atomicAdd(&ctl->hist[(unsigned)(c >> lo) & dmask], 1u);
-                });
-                consumer_sync();
-                if (warp == 0) {
-                    unsigned h[8], s = 0u;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        h[j] = ctl->hist[lane * 8 + j];
-                        s += h[j];
-                    }
-                    unsigned suf = s;   // inclusive suffix sum: this lane's bins and all higher ones
-#pragma unroll
-                    for (int o = 1; o < 32; o <<= 1) {
-                        const unsigned t = __shfl_down_sync(0xffffffffu, suf, o);
-                        if (lane + o < 32) suf += t;
-                    }
-                    const unsigned above = suf - s;
-                    if (above < (unsigned)need && suf >= (unsigned)need) {
-                        unsigned acc = above;
-                        int d = 7;
-                        for (; d > 0; --d) {
-                            if (acc + h[d] >= (unsigned)need) break;
-                            acc += h[d];
-                        }
-                        ctl->sel_digit = lane * 8 + d;
-                        ctl->sel_above = (int)acc;
-                        ctl->sel_count = (int)h[d];
-                    }
-                }
-                consumer_sync();
-                const int d = ctl->sel_digit, sc = ctl->sel_count;
-                need -= ctl->sel_above;
-                pfx |= (u64)(unsigned)d << lo;
-                mask |= (u64)dmask << lo;
-                if (sc == need) break;
-                if (lo == 0) {   // equal composites: cannot happen for distinct token ids
-                    if (tid == 0) atomicOr(status, kStatusBadTie);
-                    break;
-                }
-                hb = lo - 1;
-            }
-        } else if (tid == 0) {
-            atomicOr(status, kStatusBadTie);
-        }
+    consumer_sync();   // the scratch may be written again
+}
+
+// Bound L of the k largest among n > k distinct composites held by the threads of the CTA: exactly k composites
+// are >= L.  count_ge(t) = how many of this thread's composites are >= t.  MSB-first bisection from the highest bit
+// in which the composites differ: every step is one warp reduction, one shared-memory add per warp and one
+// barrier, and the search stops as soon as a trial bound is passed by exactly k composites.
+template <class Count>
+__device__ __forceinline__ u64 bisect_bound(int k, u64 mn, u64 mx, SharedCtl* ctl, Count count_ge) {
+    if (mx == mn) return mn;
+    const int tid = threadIdx.x;
+    const int hb = 63 - __clzll((long long)(mx ^ mn));
+    u64 pfx = (hb == 63) ? 0ull : (mx & (~0ull << (hb + 1)));
+    if (tid == 0) ctl->sum[0] = 0;
+    consumer_sync();
+    int step = 0;
+#pragma unroll 1
+    for (int b = hb; b >= 0; --b, ++step) {
+        const u64 trial = pfx | (1ull << b);
+        const int wsum = __reduce_add_sync(0xffffffffu, count_ge(trial));
+        if ((tid & 31) == 0 && wsum) atomicAdd(&ctl->sum[step % 3], wsum);
+        if (tid == 0) ctl->sum[(step + 1) % 3] = 0;   // last read two barriers ago
+        consumer_sync();
+        const int total = ctl->sum[step % 3];
+        if (total >= k) pfx = trial;
+        if (total == k) break;
     }
-    const int kk = cnt < k ? cnt : k;
+    return pfx;
+}
+
+// Keeps the k largest of list[0..n) (distinct composites in shared memory) in list[0..k), unordered, and returns
+// min(n, k).  `tmp` is scratch for k composites outside the list.  All threads of the CTA must call.
+static __device__ __noinline__ int select_list_topk(u64* list, int n, int k, u64* tmp, SharedCtl* ctl) {
+    if (n <= k) return n;
+    const int tid = threadIdx.x;
+    u64 mn = ~0ull, mx = 0ull;
+#pragma unroll 1
+    for (int i = tid; i < n; i += kThreads) {
+        const u64 c = list[i];
+        mn = min(mn, c);
+        mx = max(mx, c);
+    }
+    cta_minmax(mn, mx, ctl);
+    const u64 L = bisect_bound(k, mn, mx, ctl, [&](u64 t) {
+        int c = 0;
+#pragma unroll 1
+        for (int i = tid; i < n; i += kThreads) c += list[i] >= t ? 1 : 0;
+        return c;
+    });
     if (tid == 0) ctl->out_cnt = 0;
     consumer_sync();
-    for_each_candidate(myq, mycnt, list, list_n, [&](u64 c) {
-        if ((c & mask) >= pfx) {
-            const int p = atomicAdd(&ctl->out_cnt, 1);
-            if (p < kk) out[p] = c;
-        }
-    });
-    consumer_sync();
-    if (dst != out) {
 #pragma unroll 1
-        for (int i = tid; i < kk; i += kThreads) dst[i] = out[i];
-        consumer_sync();
+    for (int i = tid; i < n; i += kThreads) {
+        const u64 c = list[i];
+        if (c >= L) {
+            const int p = atomicAdd(&ctl->out_cnt, 1);
+            if (p < k) tmp[p] = c;
+        }
     }
-    if (L_out) *L_out = pfx;
-    return kk;
+    consumer_sync();
+#pragma unroll 1
+    for (int i = tid; i < k; i += kThreads) list[i] = tmp[i];
+    consumer_sync();
+    return k;
 }
 
 // ---------------------------------------------------------------------------------------------- row epilogue
@@ -276,17 +259,89 @@ struct TailOut {
     unsigned* status;
 };
 
-// buf[0..total) holds a superset of the row's top-k composites (total <= kMergeCap, buf has kCap entries).
-// Selects the k best, orders them, and either hands them out (vocabulary-sharded mode) or finishes the row:
-// softmax over the candidates in fp64, sequential sums in candidate order, min-p, top-p, draw.
-// All threads of the CTA must call it with the same arguments.
-static __device__ __noinline__ void finish_row(u64* buf, int total, const RowTail r, u64* out, SharedCtl* ctl, const TailOut o) {
+// Bitonic sort, descending, of 32 * S values held by one warp: value i sits in slot i / 32 of lane i % 32.
+template <int S>
+__device__ __forceinline__ void warp_sort_desc(u64 (&v)[S]) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int k2 = 2; k2 <= 32 * S; k2 <<= 1) {
+        // exchanges between register slots (partner distance >= 32); the direction of a block depends on the slot only
+#pragma unroll
+        for (int j = k2 >> 1; j >= 32; j >>= 1) {
+#pragma unroll
+            for (int q = 0; q < S; ++q) {
+                const int q2 = q ^ (j >> 5);
+                if (q < q2) {
+                    const bool up = ((q * 32) & k2) == 0;
+                    const u64 hi = max(v[q], v[q2]), lo = min(v[q], v[q2]);
+                    v[q] = up ? hi : lo;
+                    v[q2] = up ? lo : hi;
+                }
+            }
+        }
+        // exchanges between lanes
+#pragma unroll 1
+        for (int j = (k2 >> 1) < 16 ? (k2 >> 1) : 16; j > 0; j >>= 1) {
+#pragma unroll
+            for (int q = 0; q < S; ++q) {
+                const u64 o = __shfl_xor_sync(0xffffffffu, v[q], j);
+                const bool up = ((q * 32 + lane) & k2) == 0;
+                const bool lower = (lane & j) == 0;
+                v[q] = (up == lower) ? max(v[q], o) : min(v[q], o);
+            }
+        }
+    }
+}
+
+// Orders the k largest of buf[0..n) (distinct composites in shared memory; fewer if n < k) into out[0..kk),
+// descending, and returns kk = min(n, k).  Long lists are first cut down to k by bisection.  What is left (at most
+// kMaxK entries) is cut into runs of 32: warp w sorts run w in registers and puts it back; then the thread that
+// holds entry i of a run finds by binary search how many entries of every other run are larger - the sum, plus i,
+// is the entry's rank.  buf is overwritten (with room for the last run's padding: 32 * ceil(n / 32) entries); `out`
+// has room for kMaxK composites and must not overlap buf.  All consumer threads must call, after a barrier that
+// made buf visible; out is visible to all on return.
+static __device__ __noinline__ int topk_sorted(u64* buf, int n, int k, u64* out, SharedCtl* ctl) {
+    static_assert(kMaxK <= 32 * kNumWarps, "one run per warp");
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (n > kMaxK) n = select_list_topk(buf, n, k, out, ctl);
+    const int runs = (n + 31) >> 5;
+    u64 c = 0ull;   // 0 is below every composite: padding sorts to the end of the last run
+    if (warp < runs) {
+        u64 v[1];
+        v[0] = tid < n ? buf[tid] : 0ull;
+        warp_sort_desc<1>(v);
+        c = v[0];
+        buf[tid] = c;
+    }
+    consumer_sync();
+    if (c != 0ull) {
+        int rank = lane;
+#pragma unroll
+        for (int r2 = 0; r2 < kNumWarps; ++r2) {
+            if (r2 < runs && r2 != warp) {
+                const u64* run = buf + 32 * r2;   // descending: count its entries above c
+                int lo = 0;
+#pragma unroll
+                for (int step = 16; step > 0; step >>= 1)
+                    if (run[lo + step - 1] > c) lo += step;
+                if (run[lo] > c) ++lo;
+                rank += lo;
+            }
+        }
+        if (rank < k) out[rank] = c;
+    }
+    consumer_sync();
+    return n < k ? n : k;
+}
+
+// srt[0..kk) holds the row's candidates in order (largest first).  Either hands them out (vocabulary-sharded mode)
+// or finishes the row: softmax over the candidates in fp64, sequential sums in candidate order, min-p, top-p,
+// draw.  `work` is scratch for 2 * kMaxK doubles that does not overlap srt.  All consumer threads must call it with
+// the same arguments.
+static __device__ __noinline__ void row_epilogue(const u64* srt, int kk, const RowTail r, double* work, SharedCtl* ctl, const TailOut o) {
     const int tid = threadIdx.x;
-    if (total > r.k) total = select_topk(nullptr, 0, buf, total, r.k, out, buf, ctl, o.status, nullptr);
-    const int kk = total;
-    u64* srt = buf + kMaxK;
-    double* e = reinterpret_cast<double*>(buf + 2 * kMaxK);
-    double* P = reinterpret_cast<double*>(buf + 3 * kMaxK);
+    double* e = work;
+    double* P = work + kMaxK;
     if (kk <= 0) {   // nothing but NaNs in the row
         if (tid == 0) {
             atomicOr(o.status, kStatusEmptyRow);
@@ -296,19 +351,9 @@ static __device__ __noinline__ void finish_row(u64* buf, int total, const RowTai
         }
         return;
     }
-    // order by rank counting: composites are distinct, so ranks are a permutation of 0..kk-1
-    if (tid < kk) {
-        const u64 c = buf[tid];
-        int rank = 0;
-#pragma unroll 4
-        for (int j = 0; j < kk; ++j) rank += (buf[j] > c) ? 1 : 0;
-        srt[rank] = c;
-    }
-    consumer_sync();
     if (o.shard_out) {
         if (tid < kk) o.shard_out[(size_t)r.out_index * kMaxK + tid] = srt[tid];
         if (tid == 0) o.shard_n[r.out_index] = kk;
-        consumer_sync();
         return;
     }
     if (r.flags & kRowGreedy) {   // first index of the maximum (src/sampler.cpp:19-23)
@@ -316,40 +361,37 @@ static __device__ __noinline__ void finish_row(u64* buf, int total, const RowTai
             o.tokens[r.out_index] = comp_id(srt[0]);
             if (o.kept_n) o.kept_n[r.out_index] = 0;
         }
-        consumer_sync();
         return;
     }
     // pr[i] = exp((double)(x_i - x_0) / T)   (fp32 subtraction, fp64 division, src/sampler.cpp:40)
     const float mx = comp_value(srt[0]);
     if (tid < kk) e[tid] = exp(__ddiv_rn((double)__fsub_rn(comp_value(srt[tid]), mx), (double)r.temperature));
     consumer_sync();
+    // The reference adds in candidate order, one after the other: one thread runs the chain (the loads do not depend
+    // on it, so they run ahead).  The cumulative sums P[i] = pr[0] + ... + pr[i] serve the top-p walk, `tot` and the
+    // draw walk alike: the reference adds the same numbers in the same order in all three.
     if (tid == 0) {
         double s = 0.0;
-#pragma unroll 4
-        for (int i = 0; i < kk; ++i) s = __dadd_rn(s, e[i]);   // sequential, candidate order
+#pragma unroll 8
+        for (int i = 0; i < kk; ++i) s = __dadd_rn(s, e[i]);
         ctl->dsum = s;
         ctl->imax = 0;
         ctl->imin1 = 0x7fffffff;
         ctl->imin2 = 0x7fffffff;
     }
     consumer_sync();
-    const double sum = ctl->dsum;
-    double pr = 0.0;
-    if (tid < kk) {
-        pr = __ddiv_rn(e[tid], sum);
-        e[tid] = pr;
-    }
+    if (tid < kk) e[tid] = __ddiv_rn(e[tid], ctl->dsum);
     consumer_sync();
-    // cumulative sums P[i] = pr[0] + ... + pr[i], sequential: the top-p walk, `tot` and the draw walk of the
-    // reference all add the same numbers in the same order, so one array serves the three of them
     if (tid == 0) {
         double c = 0.0;
-#pragma unroll 4
+#pragma unroll 8
         for (int i = 0; i < kk; ++i) {
             c = __dadd_rn(c, e[i]);
             P[i] = c;
         }
     }
+    consumer_sync();
+    const double pr = tid < kk ? e[tid] : 0.0;
     if (r.min_p > 0.0f && tid < kk) {   // keep = 1 + last index whose probability is not below pr[0] * min_p
         const double thr = __dmul_rn(e[0], (double)r.min_p);
         if (!(pr < thr)) atomicMax(&ctl->imax, tid);

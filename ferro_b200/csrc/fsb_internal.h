@@ -6,12 +6,14 @@ namespace fsb {
 
 // ---- compile-time geometry of the streaming kernel ---------------------------------------------------------
 constexpr int kThreads = 256;                 // consumer threads per CTA (8 warps); the streaming kernel adds one producer warp
-constexpr int kTile = 4096;                   // fp32 logits per tile (16 KiB, one bulk copy)
+constexpr int kTile = 4096;                   // fp32 logits per CTA tile (16 KiB, one bulk copy; 512 logits per warp)
 constexpr int kStages = 4;                    // tiles in flight per CTA
 constexpr int kMaxK = 256;                    // largest k of the candidate path (== FSB_MAX_CANDIDATE_K)
-constexpr int kLaneQueue = 16;                // candidates each lane can queue between two re-selections
-constexpr int kCap = kLaneQueue * kThreads;   // candidate buffer entries of a CTA (32 KiB)
-constexpr int kMergeCap = kCap;               // most candidates one row may gather from all of its segments
+constexpr int kLaneQueue = 16;                // cells (4-byte entries) a lane can note before it must drop stale ones
+constexpr int kFlatCells = 960;               // cells (float4 + token id) gathered for one selection round
+constexpr int kCellBytes = 20;
+constexpr int kMergeCap = kFlatCells * kCellBytes / 8;   // 2400: candidates one row may gather from all its segments
+                                                          // (the gathered cells' memory seen as a list of composites)
 constexpr int kBitmapSpan = 65536;            // columns one penalty bitmap covers (one segment never spans more)
 constexpr int kBitmapWords = kBitmapSpan / 32;
 constexpr int kMaxTilesPerCta = kBitmapSpan / kTile;
@@ -76,7 +78,6 @@ struct StreamArgs {
     int32_t write_back;        // store penalised values into the caller's rows
     int32_t vocab_offset;      // token id of column 0
     float softcap;             // 0 = off
-    int32_t dbg;
 };
 
 size_t stream_kernel_smem_bytes();

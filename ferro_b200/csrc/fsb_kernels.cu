@@ -4,17 +4,7 @@
 //   repetition penalty (src/sampler.cpp:11-18) -> greedy argmax (:19-23) or top-k candidates (:25-35)
 //   -> fp64 softmax (:37-41) -> min-p (:43) -> top-p (:44) -> seeded draw (:45-49).
 // (reference paths are relative to the paragontasx/ferro project root)
-//
-// Work decomposition.  The [rows][n_vocab] matrix is cut into tiles of kTile logits; the flat list of tiles is
-// dealt to CTAs in equal contiguous ranges, so every CTA streams the same number of bytes whatever the row
-// count.  The part of a row that one CTA owns is a "segment".  Each logit is read from HBM exactly once, by a
-// 1-D bulk asynchronous copy into a ring of kStages shared-memory tiles.  A segment keeps only the logits that
-// can still belong to the row's top-k: a running admission bound (first taken from the per-thread maxima of the
-// segment's first tile, later tightened by an exact radix selection whenever the candidate buffer fills) filters
-// the stream with one float compare per logit.  When a segment ends it emits its k best candidates to a per-row
-// scratch area and draws a ticket; the CTA that draws the row's last ticket merges the candidates and runs the
-// row epilogue.  Nobody spins on another CTA: the only device-side wait is for this CTA's own bulk copies, and
-// it is bounded.
+// How it works is described above SegCtx below.
 #include <cuda_runtime.h>
 
 #include "fsb_device.cuh"
@@ -22,39 +12,77 @@
 namespace fsb {
 namespace {
 
+constexpr int kWarps = kThreads / 32;
+constexpr int kWTile = kTile / kWarps;          // 512 logits: a warp's part of a CTA tile
+constexpr int kBlockThreads = kThreads + 32;    // consumers + the producer warp
+constexpr int kMaxJ = (kFlatCells + kMaxK + kThreads - 1) / kThreads;   // cells one thread may hold in a re-selection
+
 constexpr size_t kSmemStage = (size_t)kStages * kTile * sizeof(float);
-constexpr size_t kSmemBuf = (size_t)kCap * sizeof(u64);
-constexpr size_t kSmemKept = (size_t)kMaxK * sizeof(u64);
-constexpr size_t kSmemOut = (size_t)kMaxK * sizeof(u64);
+constexpr size_t kSmemQueue = (size_t)kLaneQueue * kThreads * sizeof(unsigned);   // the lanes' queues of noted cells
+constexpr size_t kSmemCells = (size_t)kFlatCells * kCellBytes;                     // gathered cells; a list of composites otherwise
+constexpr size_t kSmemKept = (size_t)kMaxK * kCellBytes;                           // cells that survived a re-selection; selection scratch
 constexpr size_t kSmemBitmap = (size_t)kBitmapWords * sizeof(unsigned);
-constexpr size_t kSmemTotal = kSmemStage + kSmemBuf + kSmemKept + kSmemOut + kSmemBitmap + sizeof(SharedCtl);
-static_assert(kSmemTotal <= 115 * 1024, "two CTAs must fit into one SM's shared memory");
-static_assert(kCap >= 4 * kMaxK, "the epilogue arrays alias the candidate buffer");
-static_assert(kThreads == 256, "selection histogram assumes 256 threads");
+constexpr size_t kSmemTotal = kSmemStage + kSmemQueue + kSmemCells + kSmemKept + kSmemBitmap + sizeof(SharedCtl);
+static_assert(kSmemTotal <= 113 * 1024, "two CTAs must fit into one SM's shared memory");
+static_assert(kSmemCells >= (size_t)kMergeCap * sizeof(u64), "the element list lives in the gathered cells' memory");
+static_assert(kMergeCap >= 4 * kMaxK, "the logits of kMaxK surviving cells must fit into the element list");
+static_assert(kMergeCap >= 2 * kMaxK, "the epilogue's arrays live in the list's memory");
+static_assert(kSmemKept >= (size_t)kMaxK * sizeof(u64), "the ordered candidates live in the survivors' memory");
+static_assert(kWTile == 512, "a lane owns four float4 of a warp tile");
+static_assert(kMaxTilesPerCta <= 64, "a location is one byte: the tile number above two bits");
+static_assert(kSmemTotal <= 115712, "two CTAs per SM: 228 KiB less 1 KiB reserved per CTA");
+static_assert(kFlatCells >= 3 * kThreads, "a capped gather round takes three cells per thread");
+static_assert(kLaneQueue % 4 == 0 && kLaneQueue >= 8, "lanes look at four cells per tile");
 
 constexpr long long kCopyWaitCycles = 2000000000ll;   // about 1 s: a bulk copy that has not landed by then is reported, not awaited
 
-// A CTA tile of kTile logits is cut into one warp tile of kWTile logits per consumer warp; warp w owns the w-th
-// of every CTA tile of its CTA.  One extra warp, the producer, brings the CTA tiles into a ring of kStages
-// shared-memory slots, one bulk copy per tile; a consumer warp waits for a tile to land, works on its part on its
-// own and hands the slot back.  Consumer warps therefore only meet at the ring (at most kStages tiles apart),
-// never at a barrier while streaming, and never issue a copy themselves.
-// Lane l of a consumer warp owns float4 number l + 32 * q (q = 0..3) of a warp tile; the candidates it admits go
-// to a queue of kLaneQueue entries that only this lane writes, so admitting needs no atomics and no warp-wide step.
-constexpr int kWarps = kThreads / 32;
-constexpr int kWTile = kTile / kWarps;          // 512 logits = 2 KiB per bulk copy
-constexpr int kBlockThreads = kThreads + 32;    // consumers + the producer warp
-static_assert(kWTile == 512, "a lane owns four float4 of a warp tile");
-static_assert(kLaneQueue >= 4, "a lane must be able to queue one float4 after a re-selection");
-static_assert(kWarps <= 32, "one producer lane per consumer warp");
+// How the streaming kernel works.
+// The [rows][n_vocab] matrix is cut into CTA tiles of kTile logits; the flat list of tiles is dealt to the CTAs in
+// equal contiguous ranges, and the part of a row that one CTA owns is a "segment".  One extra warp, the producer,
+// brings the CTA tiles into a ring of kStages shared-memory slots, one 1-D bulk copy per tile, so every logit is
+// read from HBM exactly once; the eight consumer warps each own one eighth (a warp tile of kWTile logits) of every
+// tile, wait for it to land, look at it and hand the slot back - they meet at the ring, never at a barrier.
+// Lane l owns float4 number l + 32 * q (q = 0..3) of a warp tile: a "cell" of four consecutive logits.  While
+// streaming a lane does not look at single logits: it takes the maximum of each cell, and where that reaches the
+// admission bound it notes the cell's location (one predicated 4-byte store into a queue only this lane writes).
+// At the end of a segment the noted cells are read again (from L2, as a rule), their logits that reach the final
+// bound are ranked, and the segment's k best go to the row's scratch area; the CTA that draws the row's last
+// ticket merges and finishes the row.  Nobody spins on another CTA; waits for this CTA's own copies are bounded.
 
-struct SegCtx {
-    float pen;        // repetition penalty of the row
-    float cap;        // softcap, 0 = off
-    int has_pen;
-    int id_base;      // token id of column 0
-    float* wb_row;    // row base for write-back, or null
+// The shared memory of a CTA.  The gathered cells' memory doubles as a list of composites (elements, merging),
+// the survivors' memory as the ordered candidates of the epilogue.
+struct Smem {
+    float* stage;       // [kStages][kTile] ring of CTA tiles
+    unsigned* queue;    // [kLaneQueue][kThreads] cells noted by each lane: truncated maximum | location
+    float4* cells;      // [kFlatCells] gathered cells ...
+    int* ids;           // [kFlatCells] ... and their first token ids
+    float4* kcells;     // [kMaxK] survivors of re-selections
+    int* kids;          // [kMaxK]
+    u64* list;          // = cells
+    u64* sorted;        // = kcells
+    unsigned* bitmap;
+    SharedCtl* ctl;
 };
+__device__ __forceinline__ Smem smem_view() {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Smem m;
+    unsigned char* p = smem_raw;
+    m.stage = reinterpret_cast<float*>(p);
+    p += kSmemStage;
+    m.queue = reinterpret_cast<unsigned*>(p);
+    p += kSmemQueue;
+    m.cells = reinterpret_cast<float4*>(p);
+    m.ids = reinterpret_cast<int*>(p + (size_t)kFlatCells * sizeof(float4));
+    m.list = reinterpret_cast<u64*>(p);
+    p += kSmemCells;
+    m.kcells = reinterpret_cast<float4*>(p);
+    m.kids = reinterpret_cast<int*>(p + (size_t)kMaxK * sizeof(float4));
+    m.sorted = reinterpret_cast<u64*>(p);
+    p += kSmemKept;
+    m.bitmap = reinterpret_cast<unsigned*>(p);
+    m.ctl = reinterpret_cast<SharedCtl*>(p + kSmemBitmap);
+    return m;
+}
 
 // Final-logit softcap over a warp tile, in place (src/model_gemma4.cpp:521).  Only the softcap build calls it.
 __device__ __noinline__ void softcap_tile(float* st, int len, float cap, float* wb) {
@@ -69,57 +97,61 @@ __device__ __noinline__ void softcap_tile(float* st, int len, float cap, float* 
 // Repetition penalty on the penalised columns of a warp tile, in place in shared memory (src/sampler.cpp:17).
 // The tile's bits of the segment bitmap are one word per 32 columns; each of the first lanes owns one word and
 // patches the columns whose bits are set.  A bit is set once however often an id occurs in the window.
-__device__ __forceinline__ void patch_tile(float* st, int len, int col0, const SegCtx& sc, const unsigned* bitmap, int bm_lo) {
+__device__ __forceinline__ void patch_tile(float* st, int len, int col0, int seg_lo, float pen, const unsigned* bitmap, float* wb_row) {
     const int lane = threadIdx.x & 31;
     const int nw = (len + 31) >> 5;
-    unsigned w = (lane < nw) ? bitmap[((col0 - bm_lo) >> 5) + lane] : 0u;
+    unsigned w = (lane < nw) ? bitmap[((col0 - seg_lo) >> 5) + lane] : 0u;
     if (__ballot_sync(0xffffffffu, w != 0u) == 0u) return;
     while (w) {
         const int off = 32 * lane + __ffs(w) - 1;
         w &= w - 1u;
         const float x = st[off];
-        const float y = x > 0.0f ? __fdiv_rn(x, sc.pen) : __fmul_rn(x, sc.pen);
+        const float y = x > 0.0f ? __fdiv_rn(x, pen) : __fmul_rn(x, pen);
         st[off] = y;
-        if (sc.wb_row) sc.wb_row[col0 + off] = y;
+        if (wb_row) wb_row[col0 + off] = y;
     }
     __syncwarp();
 }
 
-// Admission test of one logit: at or above the float bound and, once a re-selection has set a composite bound,
-// not a tie at the bound that loses on token id.
-__device__ __forceinline__ bool admitted(float x, int id, float thr_f, u64 thr_comp) {
-    return x >= thr_f && (thr_comp == 0ull || make_comp(x, id) >= thr_comp);
-}
-
-// r-th largest of the 32 lane values of a warp (r in 1..32): r rounds of "warp maximum, strike one holder".
-// -inf when fewer than r lanes hold a value above the filler.
-__device__ __forceinline__ float warp_rth_largest(float v, int r) {
+// The r-th largest (r = 1..32) of the 32 lane values of a warp: a bitonic sort across the lanes.
+__device__ __forceinline__ unsigned warp_rth_largest(unsigned v, int r) {
     const int lane = threadIdx.x & 31;
-    unsigned cur = (v == v) ? float_key(v) : 0u;   // 0 ranks below every real logit
-    unsigned top = 0u;
-#pragma unroll 1
-    for (int i = 0; i < r; ++i) {
-        top = __reduce_max_sync(0xffffffffu, cur);
-        const unsigned who = __ballot_sync(0xffffffffu, cur == top);
-        if (lane == __ffs(who) - 1) cur = 0u;
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const unsigned o = __shfl_xor_sync(0xffffffffu, v, j);
+            const bool up = (lane & k) == 0;   // k == 32: every lane, the final order is ascending
+            const bool low = (lane & j) == 0;
+            v = (up == low) ? min(v, o) : max(v, o);
+        }
     }
-    return top == 0u ? -__int_as_float(0x7f800000) : key_float(top);
+    return __shfl_sync(0xffffffffu, v, 32 - r);
 }
 
-// Admission bound of the CTA from the per-lane running maxima: with r = ceil(k / warps), at least r logits of a
-// warp's stream reach the r-th largest of its lanes' running maxima, so at least k logits of the segment reach
-// the smallest of those values over the warps: no logit below it can be among the segment's k best.  Each warp
-// posts its value; values only grow, so a reader may use another warp's older value without a barrier.
+// A bound that at least r = min(32, ceil(k / warps)) logits of this warp's stream reach: the r-th largest of the
+// lanes' running maxima (each is a logit of its own).
+__device__ __forceinline__ float warp_bound(float run_max, int k) {
+    const int r = min(32, (k + kWarps - 1) / kWarps);
+    const unsigned key = warp_rth_largest(float_key(run_max), r);
+    return key_float(key);
+}
+
+// Admission bound of the CTA: at least k logits of the segment reach the smallest of the warps' bounds (eight
+// warps, at least ceil(k / 8) logits each, or 32 * 8 >= kMaxK), so no logit below it is among the segment's k
+// best.  Each warp posts its value; values only grow, so a reader may use another warp's older value without a
+// barrier.
+__device__ __forceinline__ float min_warp_bounds(SharedCtl* ctl) {
+    float4 lo, hi;   // volatile: re-read on every call
+    asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w) : "r"(smem_u32(&ctl->wbound[0])));
+    asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w) : "r"(smem_u32(&ctl->wbound[4])));
+    return fminf(fminf(fminf(lo.x, lo.y), fminf(lo.z, lo.w)), fminf(fminf(hi.x, hi.y), fminf(hi.z, hi.w)));
+}
 __device__ __forceinline__ float refresh_bound(float run_max, int k, SharedCtl* ctl) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float wb = warp_rth_largest(run_max, (k + kWarps - 1) / kWarps);
-    volatile float* vb = ctl->wbound;
-    if (lane == 0) vb[warp] = wb;
+    const float wb = warp_bound(run_max, k);
+    if ((threadIdx.x & 31) == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[threadIdx.x >> 5]) = wb;
     __syncwarp();
-    float t = vb[0];
-#pragma unroll
-    for (int w = 1; w < kWarps; ++w) t = fminf(t, vb[w]);
-    return t;
+    return min_warp_bounds(ctl);
 }
 
 // Diagnostics: slot 0 takes the global timer (ns) once, the others the SM cycle counter (cheap to read).
@@ -130,27 +162,265 @@ __device__ __forceinline__ void trace_mark(const StreamArgs& a, int slot) {
     }
 }
 
-// One rendez-vous of all consumer warps of the CTA.  A warp comes here either because one of its lanes had no room
-// left in its queue (overflowed) or because it has finished its part of the segment.  If any warp overflowed, the
-// CTA keeps the k best candidates (they move to the shared survivors' list, the queues become empty), tightens
-// the admission bound, and the function returns true; it returns false when every warp had finished.  Every warp
-// reaches one of the two call sites in bounded time on its own (while streaming, a consumer depends on nothing
-// but its own copies), so the barrier cannot deadlock.
-__device__ __noinline__ bool cta_event(bool overflowed, int k, const u64* myq, int* mycnt, u64* kept, int* nkept, u64* out,
-                                       SharedCtl* ctl, unsigned* status, float* thr_f, u64* thr_comp) {
-    if (overflowed) *reinterpret_cast<volatile int*>(&ctl->need_compact) = 1;
-    consumer_sync();
-    if (*reinterpret_cast<volatile int*>(&ctl->need_compact) == 0) return false;
-    u64 L = 0ull;
-    *nkept = select_topk(myq, *mycnt, kept, *nkept, k, out, kept, ctl, status, &L);
-    *mycnt = 0;
-    if (L != 0ull) {
-        *thr_comp = L;
-        *thr_f = fmaxf(*thr_f, comp_floor_value(L));
+// Composite of a cell: (largest of its four logits, first token id).  A logit of the k best of a set of cells
+// always lies in one of the k cells with the largest composites.
+__device__ __forceinline__ u64 cell_comp(float4 x, int id0) { return make_comp(fmaxf(max3(x.x, x.y, x.z), x.w), id0); }
+
+// A queue entry: the cell's maximum with its low eight bits cleared (rounded toward zero) | the cell's location,
+// (tile of the segment << 2) | q.  For any a >= b, entry_value of a's entry >= truncated(b): testing entries
+// against a truncated bound never drops a cell whose maximum reaches the bound.
+__device__ __forceinline__ unsigned make_entry(float mx, unsigned loc) { return (__float_as_uint(mx) & 0xFFFFFF00u) | loc; }
+__device__ __forceinline__ float entry_value(unsigned e) { return __uint_as_float(e & 0xFFFFFF00u); }
+__device__ __forceinline__ float truncated(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFFF00u); }
+
+// Drops the entries of this lane's queue whose cell maximum cannot reach `thr` any more; returns the new length.
+__device__ __forceinline__ int drop_stale(unsigned* myq, int qn, float thr) {
+    const float t = truncated(thr);
+    int w = 0;
+    for (int i = 0; i < qn; ++i) {
+        const unsigned e = myq[i * kThreads];
+        if (entry_value(e) >= t) myq[(w++) * kThreads] = e;
     }
-    if (threadIdx.x == 0) ctl->need_compact = 0;
+    return w;
+}
+
+// Column of the cell a queue entry of this thread names.
+__device__ __forceinline__ int loc_column(unsigned loc, const SegCtx& sc) {
+    loc &= 0xFFu;
+    return sc.seg_lo + (int)(loc >> 2) * kTile + (int)(threadIdx.x >> 5) * kWTile + 4 * ((int)(threadIdx.x & 31) + 32 * (int)(loc & 3u));
+}
+
+// The cell at column `col` of the row, as loaded (no transformation).  Columns past the end of the row are NaN.
+__device__ __forceinline__ float4 load_cell(const SegCtx& sc, int col) {
+    if (sc.vec_ok && col + 4 <= sc.n_vocab) return __ldcg(reinterpret_cast<const float4*>(sc.row + col));
+    const float qnan = __int_as_float(0x7fc00000);
+    float4 t;
+    t.x = (col < sc.n_vocab) ? __ldcg(sc.row + col) : qnan;
+    t.y = (col + 1 < sc.n_vocab) ? __ldcg(sc.row + col + 1) : qnan;
+    t.z = (col + 2 < sc.n_vocab) ? __ldcg(sc.row + col + 2) : qnan;
+    t.w = (col + 3 < sc.n_vocab) ? __ldcg(sc.row + col + 3) : qnan;
+    return t;
+}
+
+// Softcap, then penalty, as the streaming pass applied them to the cell at column `col`.
+template <bool SOFTCAP>
+__device__ __forceinline__ float4 transform_cell(float4 t, const SegCtx& sc, const unsigned* bitmap, int col) {
+    if (sc.final_in_mem) return t;
+    if (SOFTCAP) {
+        t.x = __fmul_rn(sc.cap, tanhf(__fdiv_rn(t.x, sc.cap)));
+        t.y = __fmul_rn(sc.cap, tanhf(__fdiv_rn(t.y, sc.cap)));
+        t.z = __fmul_rn(sc.cap, tanhf(__fdiv_rn(t.z, sc.cap)));
+        t.w = __fmul_rn(sc.cap, tanhf(__fdiv_rn(t.w, sc.cap)));
+    }
+    if (sc.has_pen) {
+        const int b = col - sc.seg_lo;   // a multiple of four: the four bits lie in one word
+        const unsigned bits = (bitmap[b >> 5] >> (b & 31)) & 0xFu;
+        if (bits) {
+            if (bits & 1u) t.x = t.x > 0.0f ? __fdiv_rn(t.x, sc.pen) : __fmul_rn(t.x, sc.pen);
+            if (bits & 2u) t.y = t.y > 0.0f ? __fdiv_rn(t.y, sc.pen) : __fmul_rn(t.y, sc.pen);
+            if (bits & 4u) t.z = t.z > 0.0f ? __fdiv_rn(t.z, sc.pen) : __fmul_rn(t.z, sc.pen);
+            if (bits & 8u) t.w = t.w > 0.0f ? __fdiv_rn(t.w, sc.pen) : __fmul_rn(t.w, sc.pen);
+        }
+    }
+    return t;
+}
+
+// Exclusive prefix sum of one int per consumer thread over the CTA (thread order) and the total.  Contains two
+// barriers; uses ctl->red.
+struct ScanResult {
+    int before;
+    int total;
+};
+__device__ __forceinline__ ScanResult cta_scan(int v, SharedCtl* ctl) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) reinterpret_cast<int*>(ctl->red)[warp] = inc;
     consumer_sync();
-    return true;
+    int before = inc - v, total = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const int s = reinterpret_cast<int*>(ctl->red)[w];
+        if (w < warp) before += s;
+        total += s;
+    }
+    consumer_sync();   // the scratch may be written again
+    return ScanResult{before, total};
+}
+
+// Re-selection over the nq gathered cells (flat arrays) and the nkept survivors: the k cells with the largest
+// composites become the survivors' list.  Returns their number and the composite bound they passed (0: nothing was
+// dropped).  All consumer threads must call, after a barrier that made the gathered cells visible.
+struct SelectResult {
+    int count;
+    u64 bound;
+};
+__device__ __noinline__ SelectResult select_cells(int nq, int nkept, int k) {
+    const Smem cs = smem_view();
+    SharedCtl* ctl = cs.ctl;
+    const int tid = threadIdx.x;
+    const int n = nq + nkept;
+    float4 cx[kMaxJ];
+    int cid[kMaxJ];
+    u64 cc[kMaxJ];
+#pragma unroll
+    for (int j = 0; j < kMaxJ; ++j) {
+        const int f = tid + j * kThreads;
+        cc[j] = 0ull;
+        cid[j] = 0;
+        cx[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (f < n) {
+            cx[j] = f < nq ? cs.cells[f] : cs.kcells[f - nq];
+            cid[j] = f < nq ? cs.ids[f] : cs.kids[f - nq];
+            cc[j] = cell_comp(cx[j], cid[j]);
+        }
+    }
+    consumer_sync();   // every cell is in registers: the survivors' memory may be rewritten
+    u64 L = 0ull;
+    if (n > k) {
+        u64 mn = ~0ull, mx = 0ull;
+#pragma unroll
+        for (int j = 0; j < kMaxJ; ++j) {
+            if (cc[j] != 0ull) {
+                mn = min(mn, cc[j]);
+                mx = max(mx, cc[j]);
+            }
+        }
+        cta_minmax(mn, mx, ctl);
+        L = bisect_bound(k, mn, mx, ctl, [&](u64 t) {
+            int c = 0;
+#pragma unroll
+            for (int j = 0; j < kMaxJ; ++j) c += cc[j] >= t ? 1 : 0;   // empty slots hold 0, t is never 0
+            return c;
+        });
+    }
+    if (tid == 0) ctl->out_cnt = 0;
+    consumer_sync();
+#pragma unroll
+    for (int j = 0; j < kMaxJ; ++j) {
+        if (cc[j] != 0ull && cc[j] >= L) {
+            const int p = atomicAdd(&ctl->out_cnt, 1);
+            if (p < kMaxK) {
+                cs.kcells[p] = cx[j];
+                cs.kids[p] = cid[j];
+            }
+        }
+    }
+    consumer_sync();
+    return SelectResult{min(ctl->out_cnt, kMaxK), L};
+}
+
+// One rendez-vous of all consumer warps of the CTA.  A warp comes here because it saw a request for a re-selection
+// (a lane's queue is nearly full), or because it has finished its part of the segment.  Every warp posts its
+// bound and the number of cells its lanes hold.  If a re-selection was asked for, the queued cells are read again
+// and the CTA keeps the k best cells (they become the survivors' list, all queues become empty), and `happened`
+// is set; otherwise every warp had finished and the posted values describe the whole segment.  Warps depend on
+// nothing but their own copies while streaming and look out for requests at every tile and in every wait, so
+// every warp gets here in bounded time.
+// Returns (happened) | (survivors << 1); the composite bound of a re-selection is left in ctl->ev_bound and the
+// warps' bounds in ctl->wbound.
+__device__ __forceinline__ int event_happened(int ev) { return ev & 1; }
+__device__ __forceinline__ int event_nkept(int ev) { return (ev >> 1) & 1023; }
+template <bool SOFTCAP>
+__device__ __noinline__ int cta_event(int qn, int nkept, float run_max, float thr_f) {
+    const Smem m = smem_view();
+    SharedCtl* ctl = m.ctl;
+    const SegCtx& sc = ctl->seg;
+    const int k = sc.k;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float wb = warp_bound(run_max, k);
+    if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
+    if (tid == 0) ctl->out_cnt = 0;
+    consumer_sync();
+    if (*reinterpret_cast<volatile int*>(&ctl->need_compact) == 0) return nkept << 1;
+    u64 bound = 0ull;
+    // every lane first drops what the bound has overtaken; then gather rounds: everything at once if it fits, else
+    // three cells per thread and round
+    qn = drop_stale(m.queue + tid, qn, fmaxf(thr_f, min_warp_bounds(ctl)));
+    int cap = kLaneQueue;
+    if (cta_scan(qn, ctl).total > kFlatCells) cap = kFlatCells / kThreads;
+    for (;;) {
+        const int cnt = min(qn, cap);
+        const ScanResult sr = cta_scan(cnt, ctl);
+        if (sr.total == 0) break;
+        for (int i0 = 0; i0 < cnt; i0 += 4) {   // four loads in flight
+            float4 c[4];
+            int col[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                col[u] = -1;
+                if (i0 + u < cnt) {
+                    col[u] = loc_column(m.queue[(size_t)(qn - 1 - i0 - u) * kThreads + tid], sc);
+                    c[u] = load_cell(sc, col[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (col[u] >= 0) {
+                    m.cells[sr.before + i0 + u] = transform_cell<SOFTCAP>(c[u], sc, m.bitmap, col[u]);
+                    m.ids[sr.before + i0 + u] = col[u] + sc.id_base;
+                }
+            }
+        }
+        qn -= cnt;
+        consumer_sync();
+        const SelectResult r = select_cells(sr.total, nkept, k);
+        nkept = r.count;
+        bound = max(bound, r.bound);
+    }
+    if (tid == 0) {
+        ctl->need_compact = 0;
+        ctl->ev_bound = bound;
+    }
+    consumer_sync();
+    return 1 | (nkept << 1);
+}
+
+// Appends to the element list the logits of up to N cells of this thread that reach `thr` (NaNs and columns past
+// the end of the row take no part).  A warp reserves its part of the list with one atomic.  All lanes of the warp
+// must call; ncell = 0 contributes nothing.  Entries past the list's capacity are counted but not written.
+template <int N>
+__device__ __forceinline__ void append_elements(const float4 (&c)[N], const int (&id0)[N], int ncell, float thr, int id_end, u64* list,
+                                                SharedCtl* ctl) {
+    static_assert(N <= 8, "one mask bit per logit");
+    const int lane = threadIdx.x & 31;
+    unsigned mask = 0u;
+#pragma unroll
+    for (int u = 0; u < N; ++u) {
+        if (u < ncell) {
+            const float xs[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (xs[e] >= thr && id0[u] + e < id_end) mask |= 1u << (4 * u + e);
+        }
+    }
+    const int mine = __popc(mask);
+    int inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    const int wtotal = __shfl_sync(0xffffffffu, inc, 31);
+    if (wtotal == 0) return;
+    int base = 0;
+    if (lane == 31) base = atomicAdd(&ctl->out_cnt, wtotal);
+    base = __shfl_sync(0xffffffffu, base, 31);
+    int p = base + inc - mine;
+#pragma unroll
+    for (int u = 0; u < N; ++u) {
+        const float xs[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (mask & (1u << (4 * u + e))) {
+                if (p < kMergeCap) list[p] = make_comp(xs[e], id0[u] + e);
+                ++p;
+            }
+    }
 }
 
 // The producer: one lane brings the CTA tiles in, one 1-D bulk copy per tile (large copies: the copy engine's cost
@@ -164,12 +434,11 @@ __device__ __forceinline__ void producer_loop(const StreamArgs& a, float* stage,
     while (i < nt) {
         const int slot = i % kStages;
         // the first kStages tiles find their slots free; later ones wait for the consumers' hand-back
-        if (i >= kStages && !mbar_test_wait(&ctl->empty[slot], (unsigned)((i / kStages - 1) & 1))) {
+        if (i >= kStages && !mbar_try_wait(&ctl->empty[slot], (unsigned)((i / kStages - 1) & 1))) {
             if (clock64() - t_last > kCopyWaitCycles) {   // the consumers never came back: report and stop
                 atomicOr(a.status, kStatusCopyTimeout);
                 return;
             }
-            __nanosleep(32);
             continue;
         }
         const int col0 = ij * kTile;
@@ -194,20 +463,124 @@ __device__ __forceinline__ void producer_loop(const StreamArgs& a, float* stage,
     }
 }
 
+// The end of a segment.  All consumer threads call it once they have looked at their last tile of the segment:
+// re-selections that were still asked for, the rendez-vous of the finished warps, the element list, the segment's
+// k best logits in order, and - in the CTA that draws the row's last ticket - the merge and the row's epilogue.
 template <bool SOFTCAP>
-__global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const StreamArgs a) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    float* stage = reinterpret_cast<float*>(smem_raw);
-    u64* buf = reinterpret_cast<u64*>(smem_raw + kSmemStage);   // kCap entries: the lanes' queues; contiguous list when merging
-    u64* kept = buf + kCap;                                     // kMaxK entries: survivors of re-selections
-    u64* out = kept + kMaxK;                                    // kMaxK entries: selection scratch
-    unsigned* bitmap = reinterpret_cast<unsigned*>(out + kMaxK);
-    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(bitmap + kBitmapWords);
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+__device__ __noinline__ void segment_end(const StreamArgs& a, int row, int qn, int nkept, float thr_f, float run_max, bool mark) {
+    const Smem m = smem_view();
+    SharedCtl* ctl = m.ctl;
+    const SegCtx& sc = ctl->seg;
+    const int tid = threadIdx.x;
     const int T = a.tiles_per_row, V = a.n_vocab, Q = a.tiles_per_cta;
-    const int t_begin = blockIdx.x * Q;
-    const int t_end = min(t_begin + Q, a.total_tiles);
+    const RowDesc d = a.rows[row];
+    unsigned* myq = m.queue + tid;
+    const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
+    float thr_final;
+    int n_el;
+    for (;;) {
+        for (;;) {   // re-selections that were still asked for, then the rendez-vous of the finished warps
+            const int ev = cta_event<SOFTCAP>(qn, nkept, run_max, thr_f);
+            if (!event_happened(ev)) break;
+            qn = 0;
+            nkept = event_nkept(ev);
+        }
+        thr_final = fmaxf(thr_f, min_warp_bounds(ctl));
+        if (mark) trace_mark(a, 4);
+        // ---- the logits of the noted cells that reach the final bound become the element list
+        const int id_end = V + sc.id_base;
+        if (nkept > 0) {
+            float4 c[1];
+            int id0[1];
+            c[0] = m.kcells[min(tid, nkept - 1)];
+            id0[0] = m.kids[min(tid, nkept - 1)];
+            append_elements<1>(c, id0, tid < nkept ? 1 : 0, thr_final, id_end, m.list, ctl);
+        }
+        qn = drop_stale(myq, qn, thr_final);   // most noted cells have been overtaken by the bound
+        // a thread reads up to four of its cells per round (lanes rarely hold more that the bound has not overtaken)
+        const int rounds = (__reduce_max_sync(0xffffffffu, qn) + 3) >> 2;
+#pragma unroll 1
+        for (int rd = 0; rd < rounds; ++rd) {
+            float4 c[4];
+            int id0[4];
+            const int n = max(0, min(4, qn - 4 * rd));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                id0[u] = 0;
+                c[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (u < n) {
+                    id0[u] = loc_column(myq[(4 * rd + u) * kThreads], sc);
+                    c[u] = load_cell(sc, id0[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (u < n) {
+                    c[u] = transform_cell<SOFTCAP>(c[u], sc, m.bitmap, id0[u]);
+                    id0[u] += sc.id_base;
+                }
+            }
+            append_elements<4>(c, id0, n, thr_final, id_end, m.list, ctl);
+        }
+        consumer_sync();
+        n_el = ctl->out_cnt;
+        if (n_el <= kMergeCap) break;
+        // more logits reach the bound than the list can take (many equal values): keep the k best cells first
+        consumer_sync();
+        *reinterpret_cast<volatile int*>(&ctl->need_compact) = 1;
+    }
+    if (mark) trace_mark(a, 2);
+    // the segment's k best logits (or all, if fewer), in order; in the CTA that draws the last ticket of a row that
+    // has several segments, a second pass does the same with everything the segments have published
+    const int first_cta = (row * T) / Q, last_cta = (row * T + T - 1) / Q;
+    const int nseg = last_cta - first_cta + 1;
+    bool merge_here = true;
+    int kk = 0;
+    for (int pass = 0;; ++pass) {
+        kk = topk_sorted(m.list, n_el, d.k, m.sorted, ctl);
+        if (nseg == 1 || pass == 1) break;
+        if (tid == 0) ctl->base = (int)atomicAdd(&a.fill[row], (unsigned)kk);
+        consumer_sync();
+        const int base = ctl->base;
+        u64* dst = reinterpret_cast<u64*>(a.scratch) + (size_t)row * kMergeCap;
+        if (base + kk <= kMergeCap) {
+            for (int i = tid; i < kk; i += kThreads) dst[base + i] = m.sorted[i];
+        } else if (tid == 0) {
+            atomicOr(a.status, kStatusMergeOverflow);
+        }
+        __threadfence();
+        consumer_sync();
+        if (tid == 0) ctl->last = (atomicAdd(&a.ticket[row], 1u) == (unsigned)(nseg - 1)) ? 1 : 0;
+        consumer_sync();
+        merge_here = ctl->last != 0;
+        if (!merge_here) break;
+        // all segments of the row have published: gather them (L2 reads, never L1)
+        __threadfence();
+        n_el = min((int)__ldcg(&a.fill[row]), kMergeCap);
+        for (int i = tid; i < n_el; i += kThreads) m.list[i] = __ldcg(dst + i);
+        consumer_sync();
+        if (tid == 0) {   // leave the counters ready for the next launch
+            a.fill[row] = 0u;
+            a.ticket[row] = 0u;
+        }
+    }
+    if (mark) trace_mark(a, 5);
+    if (merge_here) {
+        const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index};
+        row_epilogue(m.sorted, kk, rt, reinterpret_cast<double*>(m.list), ctl, tout);
+    }
+    consumer_sync();
+    if (mark) trace_mark(a, 6);
+}
+
+template <bool SOFTCAP>
+__global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const __grid_constant__ StreamArgs a) {
+    const Smem m = smem_view();
+    SharedCtl* ctl = m.ctl;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int T = a.tiles_per_row, V = a.n_vocab;
+    const int t_begin = blockIdx.x * a.tiles_per_cta;
+    const int t_end = min(t_begin + a.tiles_per_cta, a.total_tiles);
     const int nt = t_end - t_begin;
     if (nt <= 0) return;
     trace_mark(a, 0);
@@ -223,220 +596,168 @@ __global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const S
     }
     __syncthreads();   // the only barrier the producer warp takes part in
     if (warp == kWarps) {
-        if (a.bulk_ok) producer_loop(a, stage, ctl, t_begin, nt);
+        if (a.bulk_ok) producer_loop(a, m.stage, ctl, t_begin, nt);
         return;
     }
     trace_mark(a, 1);
 
     // ------------------------------------------------------------------------------------------ consumers
-    int row = t_begin / T, j = t_begin - row * T;
-    u64* myq = buf + (size_t)warp * (32 * kLaneQueue) + lane;   // this lane's queue: entry s at myq[s * 32]
-
-    const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
-    unsigned phase_bits = 0u;
-    int cur_row = -1;
-    RowDesc d;
-    SegCtx sc;
-    float thr_f = 0.0f, run_max = 0.0f;
-    u64 thr_comp = 0ull;
-    int bm_lo = 0, seg_it = 0;
-    int mycnt = 0;    // entries in this lane's queue
-    int nkept = 0;    // entries in the survivors' list (the same value in every thread)
-    int dbg_events = 0;
-    long long acc[6] = {0, 0, 0, 0, 0, 0}, tq, tn;
-
-    for (int it = 0; it < nt; ++it) {
-        const int col0 = j * kTile + warp * kWTile;          // first column of this warp's part
-        const int len = max(0, min(kWTile, V - col0));
-        const int slot = it % kStages;
-        float* st = stage + (size_t)slot * kTile + warp * kWTile;   // this warp's part of the CTA tile
-        const bool new_seg = (row != cur_row);
-
-        if (new_seg) {   // ---- a new segment starts (all consumer warps are here together: kernel start or after a segment end)
-            cur_row = row;
-            d = a.rows[row];
-            const int seg_lo_col = j * kTile;
-            const int f_last = min(t_end, (row + 1) * T) - 1;
-            const int seg_hi_col = min(V, (f_last - row * T + 1) * kTile);
-            sc.pen = d.penalty;
+    // The loop over a segment's tiles contains no call: everything rare (re-selections, the end of the segment)
+    // happens outside it, so that the loop's state stays in registers.
+    const float ninf = -__int_as_float(0x7f800000);
+    unsigned* myq = m.queue + tid;   // entry i of this lane's queue is myq[i * kThreads]
+    int it = 0;                            // tiles of this CTA looked at so far (the position in the ring)
+    for (int tile = t_begin; tile < t_end;) {
+        // ---- a new segment starts (all consumer warps are here together: kernel start or after a segment end)
+        const int row = tile / T, j0 = tile - row * T;
+        const int seg_nt = min(t_end - tile, T - j0);
+        const int seg_lo = j0 * kTile;
+        const int seg_hi = min(V, (j0 + seg_nt) * kTile);
+        const RowDesc d = a.rows[row];
+        const float* row_ptr = a.logits + d.logits_off;
+        float* wb_row = a.write_back ? const_cast<float*>(row_ptr) : nullptr;
+        const float pen = d.penalty;
+        const int row_k = d.k;
+        const bool has_pen = (d.flags & kRowPenalty) != 0;
+        if (tid == 0) {   // what the rendez-vous code needs to know about the segment
+            SegCtx& sc = ctl->seg;
+            sc.row = row_ptr;
+            sc.pen = pen;
             sc.cap = a.softcap;
-            sc.has_pen = (d.flags & kRowPenalty) ? 1 : 0;
+            sc.has_pen = has_pen ? 1 : 0;
             sc.id_base = a.vocab_offset;
-            sc.wb_row = a.write_back ? const_cast<float*>(a.logits) + d.logits_off : nullptr;
-            bm_lo = seg_lo_col;
-            if (sc.has_pen) {   // bitmap of the penalised columns of this segment
-                const int words = (seg_hi_col - seg_lo_col + 31) >> 5;
-                for (int i = tid; i < words; i += kThreads) bitmap[i] = 0u;
-                consumer_sync();
-                const int32_t* h = a.hist + d.hist_begin;
-                for (int i = tid; i < d.hist_len; i += kThreads) {
-                    const int c = h[i] - a.vocab_offset;
-                    if (c >= seg_lo_col && c < seg_hi_col) atomicOr(&bitmap[(c - seg_lo_col) >> 5], 1u << ((c - seg_lo_col) & 31));
-                }
-            }
-            mycnt = 0;
-            nkept = 0;
-            thr_comp = 0ull;
-            thr_f = -__int_as_float(0x7f800000);
-            run_max = -__int_as_float(0x7f800000);
-            seg_it = 0;
-            consumer_sync();
+            sc.seg_lo = seg_lo;
+            sc.n_vocab = V;
+            sc.vec_ok = a.bulk_ok;
+            sc.k = row_k;
+            sc.final_in_mem = a.write_back;
         }
+        if (has_pen) {   // bitmap of the penalised columns of this segment
+            const int words = (seg_hi - seg_lo + 31) >> 5;
+            for (int i = tid; i < words; i += kThreads) m.bitmap[i] = 0u;
+            consumer_sync();
+            const int32_t* h = a.hist + d.hist_begin;
+            for (int i = tid; i < d.hist_len; i += kThreads) {
+                const int c = h[i] - a.vocab_offset;
+                if (c >= seg_lo && c < seg_hi) atomicOr(&m.bitmap[(c - seg_lo) >> 5], 1u << ((c - seg_lo) & 31));
+            }
+        }
+        consumer_sync();
 
-        // ---- wait for the CTA tile's copy.  A warp that is waiting (or about to) also answers re-selection requests
-        // of other warps: a requester sits at the barrier of cta_event, and the ring only moves when every warp does.
-        tq = clock64();
-        if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&ctl->need_compact) != 0))
-            cta_event(false, d.k, myq, &mycnt, kept, &nkept, out, ctl, a.status, &thr_f, &thr_comp);
-        if (a.bulk_ok) {
-            const unsigned par = (phase_bits >> slot) & 1u;
-            const long long lim = ctl->abort ? 2000ll : kCopyWaitCycles;
-            const long long t0 = clock64();
-            while (!mbar_try_wait(&ctl->full[slot], par)) {
-                if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&ctl->need_compact) != 0)) {
-                    cta_event(false, d.k, myq, &mycnt, kept, &nkept, out, ctl, a.status, &thr_f, &thr_comp);
-                } else if (clock64() - t0 > lim) {   // the copy never landed: report, carry on with what is there
-                    ctl->abort = 1;
-                    atomicOr(a.status, kStatusCopyTimeout);
+        float thr_f = ninf, run_max = ninf;
+        u64 thr_comp = 0ull;
+        int qn = 0;       // cells in this lane's queue
+        int nkept = 0;    // cells in the survivors' list (the same value in every thread)
+        int s = 0;        // tiles of the segment this warp has looked at
+        int col0 = seg_lo + warp * kWTile;   // first column of this warp's part of tile s
+
+        for (;;) {
+            int reason = 0;   // why the loop over the tiles was left: 0 = segment done, 1 = a queue of this warp is nearly full,
+                              // 2 = another warp asked for a re-selection while this one was waiting for a copy
+            for (; s < seg_nt; ++s, ++it, col0 += kTile) {
+                if (__any_sync(0xffffffffu, qn > kLaneQueue - 4)) {
+                    reason = 1;
                     break;
                 }
-            }
-            phase_bits ^= 1u << slot;
-        } else if (len > 0) {   // rows not on 16-byte boundaries: the warp loads its tile itself
-            const float* src = a.logits + d.logits_off + col0;
-            for (int e = lane; e < len; e += 32) st[e] = src[e];
-            __syncwarp();
-        }
-        if (len > 0) {
-            if (SOFTCAP) softcap_tile(st, len, sc.cap, sc.wb_row ? sc.wb_row + col0 : nullptr);
-            if (sc.has_pen && !(a.dbg & 8)) patch_tile(st, len, col0, sc, bitmap, bm_lo);
-        }
-        tn = clock64(); acc[0] += tn - tq; tq = tn;
-        if (it == 0) trace_mark(a, 2);
-
-        // ---- look: the lane's 16 logits go to registers (four independent 16-byte loads); what lies past the end of
-        // a ragged row is made -inf first
-        float4* st4 = reinterpret_cast<float4*>(st);
-        if (len < kWTile) {
-            for (int e = len + lane; e < kWTile; e += 32) st[e] = -__int_as_float(0x7f800000);
-            __syncwarp();
-        }
-        float4 x0 = st4[lane], x1 = st4[lane + 32], x2 = st4[lane + 64], x3 = st4[lane + 96];
-        const float m0 = fmaxf(max3(x0.x, x0.y, x0.z), x0.w);
-        const float m1 = fmaxf(max3(x1.x, x1.y, x1.z), x1.w);
-        const float m2 = fmaxf(max3(x2.x, x2.y, x2.z), x2.w);
-        const float m3 = fmaxf(max3(x3.x, x3.y, x3.z), x3.w);
-        run_max = fmaxf(max3(run_max, m0, m1), fmaxf(m2, m3));
-
-        tn = clock64(); acc[1] += tn - tq; tq = tn;
-        // ---- the admission bound: set at the segment's first tile (all warps must have posted: one barrier per
-        // segment), then refreshed without a barrier at tiles 1, 2, 4, 8, ... of the segment
-        if (new_seg) {
-            const float wb = warp_rth_largest(run_max, (d.k + kWarps - 1) / kWarps);
-            if (lane == 0) ctl->wbound[warp] = wb;
-            consumer_sync();
-            float t = ctl->wbound[0];
-#pragma unroll
-            for (int w = 1; w < kWarps; ++w) t = fminf(t, ctl->wbound[w]);
-            thr_f = t;
-            if (it == 0) trace_mark(a, 3);
-        } else if ((seg_it & (seg_it - 1)) == 0 && !(a.dbg & 2)) {
-            thr_f = fmaxf(thr_f, refresh_bound(run_max, d.k, ctl));
-        }
-        ++seg_it;
-
-        tn = clock64(); acc[2] += tn - tq; tq = tn;
-        // ---- admit: a lane looks closer only at those of its four float4 that hold a logit at or above the bound
-        unsigned pend = (m0 >= thr_f ? 1u : 0u) | (m1 >= thr_f ? 2u : 0u) | (m2 >= thr_f ? 4u : 0u) | (m3 >= thr_f ? 8u : 0u);
-        if (!(a.dbg & 1) && __any_sync(0xffffffffu, pend != 0u)) {
-            acc[5] += 1;
-            const int id_lane = col0 + 4 * lane + sc.id_base;   // token id of this lane's first logit
-            const int lim = len - 4 * lane;                      // logits of the row from there on (ragged tiles)
-            // queue the admitted logits of float4 number Q (X), unless the queue may not take four more
-#define FSB_ADMIT_BLOCK(Q, X)                                                                      \
-    if ((pend >> (Q)) & 1u) {                                                                      \
-        if (mycnt + 4 <= kLaneQueue) {                                                             \
-            pend &= ~(1u << (Q));                                                                  \
-            if (0 + 128 * (Q) < lim && admitted((X).x, id_lane + 128 * (Q) + 0, thr_f, thr_comp)) myq[32 * mycnt++] = make_comp((X).x, id_lane + 128 * (Q) + 0); \
-            if (1 + 128 * (Q) < lim && admitted((X).y, id_lane + 128 * (Q) + 1, thr_f, thr_comp)) myq[32 * mycnt++] = make_comp((X).y, id_lane + 128 * (Q) + 1); \
-            if (2 + 128 * (Q) < lim && admitted((X).z, id_lane + 128 * (Q) + 2, thr_f, thr_comp)) myq[32 * mycnt++] = make_comp((X).z, id_lane + 128 * (Q) + 2); \
-            if (3 + 128 * (Q) < lim && admitted((X).w, id_lane + 128 * (Q) + 3, thr_f, thr_comp)) myq[32 * mycnt++] = make_comp((X).w, id_lane + 128 * (Q) + 3); \
-        }                                                                                          \
-    }
-            for (;;) {
-                FSB_ADMIT_BLOCK(0, x0)
-                FSB_ADMIT_BLOCK(1, x1)
-                FSB_ADMIT_BLOCK(2, x2)
-                FSB_ADMIT_BLOCK(3, x3)
-                if (!__any_sync(0xffffffffu, pend != 0u)) break;
-                // a lane's queue is full: the CTA re-selects, then the float4 still pending are looked at again
-                cta_event(true, d.k, myq, &mycnt, kept, &nkept, out, ctl, a.status, &thr_f, &thr_comp);
-                ++dbg_events;
-                x0 = st4[lane];   // reloaded rather than kept alive across the call
-                x1 = st4[lane + 32];
-                x2 = st4[lane + 64];
-                x3 = st4[lane + 96];
-                pend &= (m0 >= thr_f ? 1u : 0u) | (m1 >= thr_f ? 2u : 0u) | (m2 >= thr_f ? 4u : 0u) | (m3 >= thr_f ? 8u : 0u);
-            }
-#undef FSB_ADMIT_BLOCK
-        }
-        __syncwarp();
-        if (lane == 0 && a.bulk_ok) mbar_arrive(&ctl->empty[slot]);   // hand the slot back to the producer
-        tn = clock64(); acc[3] += tn - tq;
-
-        const bool seg_end = (it == nt - 1) || (j == T - 1);
-        if (seg_end) {
-            while (cta_event(false, d.k, myq, &mycnt, kept, &nkept, out, ctl, a.status, &thr_f, &thr_comp)) {
-            }
-            if (it == nt - 1) trace_mark(a, 4);
-            if (it == nt - 1 && a.trace) { const int tot = __reduce_add_sync(0xffffffffu, mycnt); if (lane == 0) { atomicAdd((unsigned long long*)(a.trace + 4096 * 8 + (size_t)blockIdx.x * 8), (unsigned long long)tot); atomicAdd((unsigned long long*)(a.trace + 4096 * 8 + (size_t)blockIdx.x * 8 + 1), (unsigned long long)dbg_events); if (warp == 0) { uint64_t* t3 = a.trace + 4096 * 16 + (size_t)blockIdx.x * 8; for (int q = 0; q < 6; ++q) t3[q] = (uint64_t)acc[q]; a.trace[4096 * 8 + (size_t)blockIdx.x * 8 + 2] = (uint64_t)nkept; a.trace[4096 * 8 + (size_t)blockIdx.x * 8 + 3] = (uint64_t)__float_as_uint(thr_f); } } }
-            // the segment's k best (or all, if fewer) go to the survivors' list, contiguous
-            const int c = select_topk(myq, mycnt, kept, nkept, d.k, out, kept, ctl, a.status, nullptr);
-            const int first_cta = (row * T) / Q, last_cta = (row * T + T - 1) / Q;
-            const int nseg = last_cta - first_cta + 1;
-            int total = c;
-            bool merge_here = true;
-            if (nseg > 1) {
-                if (tid == 0) ctl->base = (int)atomicAdd(&a.fill[row], (unsigned)c);
-                consumer_sync();
-                const int base = ctl->base;
-                u64* dst = reinterpret_cast<u64*>(a.scratch) + (size_t)row * kMergeCap;
-                if (base + c <= kMergeCap) {
-                    for (int i = tid; i < c; i += kThreads) dst[base + i] = kept[i];
-                } else if (tid == 0) {
-                    atomicOr(a.status, kStatusMergeOverflow);
-                }
-                __threadfence();
-                consumer_sync();
-                if (tid == 0) ctl->last = (atomicAdd(&a.ticket[row], 1u) == (unsigned)(nseg - 1)) ? 1 : 0;
-                consumer_sync();
-                merge_here = ctl->last != 0;
-                if (merge_here) {   // all segments of the row have published: gather them (L2 reads, never L1)
-                    __threadfence();
-                    total = min((int)__ldcg(&a.fill[row]), kMergeCap);
-                    for (int i = tid; i < total; i += kThreads) buf[i] = __ldcg(dst + i);
-                    consumer_sync();
-                    if (tid == 0) {   // leave the counters ready for the next launch
-                        a.fill[row] = 0u;
-                        a.ticket[row] = 0u;
+                const int slot = it % kStages;
+                float* st = m.stage + (size_t)slot * kTile + warp * kWTile;   // this warp's part of the CTA tile
+                const int len = min(kWTile, V - col0);                        // may be <= 0 in a row's last tile
+                if (a.bulk_ok) {
+                    // ---- wait for the CTA tile's copy.  A warp that has to wait also answers re-selection requests of
+                    // other warps: a requester sits at the barrier of cta_event, and the ring only moves when every warp does.
+                    const unsigned par = (unsigned)(it / kStages) & 1u;
+                    bool landed = mbar_try_wait(&ctl->full[slot], par);
+                    if (!landed) {
+                        const long long lim = ctl->abort ? 2000ll : kCopyWaitCycles;
+                        const long long t0 = clock64();
+                        for (;;) {
+                            if (mbar_try_wait(&ctl->full[slot], par)) {
+                                landed = true;
+                                break;
+                            }
+                            if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&ctl->need_compact) != 0)) break;
+                            if (clock64() - t0 > lim) {   // the copy never landed: report, carry on with what is there
+                                ctl->abort = 1;
+                                atomicOr(a.status, kStatusCopyTimeout);
+                                landed = true;
+                                break;
+                            }
+                        }
+                        if (!landed) {
+                            reason = 2;
+                            break;
+                        }
                     }
+                } else if (len > 0) {   // rows not on 16-byte boundaries: the warp loads its tile itself
+                    const float* src = row_ptr + col0;
+                    for (int e = lane; e < len; e += 32) st[e] = src[e];
+                    __syncwarp();
                 }
-            } else {
-                for (int i = tid; i < c; i += kThreads) buf[i] = kept[i];
-                consumer_sync();
+                if (SOFTCAP) {
+                    if (len > 0) softcap_tile(st, len, a.softcap, wb_row ? wb_row + col0 : nullptr);
+                }
+                if (has_pen && len > 0) patch_tile(st, len, col0, seg_lo, pen, m.bitmap, wb_row);
+                if (len < kWTile) {   // what lies past the end of a ragged row is made NaN: never a maximum, never reaches a bound
+                    for (int e = max(len, 0) + lane; e < kWTile; e += 32) st[e] = __int_as_float(0x7fc00000);
+                    __syncwarp();
+                }
+                // ---- look: the lane's four cells go to registers (four independent 16-byte loads)
+                const float4* st4 = reinterpret_cast<const float4*>(st);
+                const float4 x0 = st4[lane], x1 = st4[lane + 32], x2 = st4[lane + 64], x3 = st4[lane + 96];
+                const float m0 = fmaxf(max3(x0.x, x0.y, x0.z), x0.w);
+                const float m1 = fmaxf(max3(x1.x, x1.y, x1.z), x1.w);
+                const float m2 = fmaxf(max3(x2.x, x2.y, x2.z), x2.w);
+                const float m3 = fmaxf(max3(x3.x, x3.y, x3.z), x3.w);
+                run_max = fmaxf(max3(run_max, m0, m1), fmaxf(m2, m3));
+                __syncwarp();
+                if (lane == 0 && a.bulk_ok) mbar_arrive(&ctl->empty[slot]);   // the slot goes back to the producer
+
+                // ---- the admission bound: set at the segment's first tile (all warps must have posted: one barrier per
+                // segment), then refreshed without a barrier at tiles 1, 2, 4, 8, ... of the segment
+                if (s == 0) {
+                    const float wb = warp_bound(run_max, row_k);
+                    if (lane == 0) ctl->wbound[warp] = wb;
+                    consumer_sync();
+                    thr_f = min_warp_bounds(ctl);
+                } else if ((s & (s - 1)) == 0) {
+                    thr_f = fmaxf(thr_f, refresh_bound(run_max, row_k, ctl));
+                }
+
+                // ---- note the cells whose maximum reaches the bound (padding past the end of a row never does)
+                bool p0 = m0 >= thr_f, p1 = m1 >= thr_f, p2 = m2 >= thr_f, p3 = m3 >= thr_f;
+                if (thr_comp != 0ull) {   // after a re-selection: ties at the bound are settled by token id
+                    const int id_lane = col0 + 4 * lane + a.vocab_offset;
+                    p0 = p0 && make_comp(m0, id_lane) >= thr_comp;
+                    p1 = p1 && make_comp(m1, id_lane + 128) >= thr_comp;
+                    p2 = p2 && make_comp(m2, id_lane + 256) >= thr_comp;
+                    p3 = p3 && make_comp(m3, id_lane + 384) >= thr_comp;
+                }
+                const unsigned loc = (unsigned)s << 2;
+                if (p0) myq[(qn++) * kThreads] = make_entry(m0, loc);
+                if (p1) myq[(qn++) * kThreads] = make_entry(m1, loc | 1u);
+                if (p2) myq[(qn++) * kThreads] = make_entry(m2, loc | 2u);
+                if (p3) myq[(qn++) * kThreads] = make_entry(m3, loc | 3u);
             }
-            if (it == nt - 1) trace_mark(a, 5);
-            if (merge_here) {
-                const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index};
-                finish_row(buf, total, rt, out, ctl, tout);
+            if (reason == 0) break;
+            // ---- a re-selection: the CTA keeps the k best of the cells noted so far, every queue becomes empty
+            if (reason == 1) {   // first drop what the bound has overtaken: that alone makes room, as a rule
+                qn = drop_stale(myq, qn, thr_f);
+                if (!__any_sync(0xffffffffu, qn > kLaneQueue - 4)) continue;
+                *reinterpret_cast<volatile int*>(&ctl->need_compact) = 1;
             }
-            consumer_sync();
-            if (it == nt - 1) trace_mark(a, 6);
+            const int ev = cta_event<SOFTCAP>(qn, nkept, run_max, thr_f);
+            if (event_happened(ev)) {
+                qn = 0;
+                nkept = event_nkept(ev);
+                const u64 eb = ctl->ev_bound;
+                if (eb) {
+                    thr_comp = max(thr_comp, eb);
+                    thr_f = fmaxf(thr_f, comp_floor_value(eb));
+                }
+            }
         }
-        if (++j == T) {
-            j = 0;
-            ++row;
-        }
+        segment_end<SOFTCAP>(a, row, qn, nkept, thr_f, run_max, tile + seg_nt >= t_end);
+        tile += seg_nt;
     }
 }
 
@@ -447,7 +768,7 @@ __global__ void __launch_bounds__(kThreads, 2) merge_lists_kernel(const u64* lis
                                                                  double* kept_pr, int32_t* kept_n, unsigned* status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     u64* buf = reinterpret_cast<u64*>(smem_raw);
-    u64* out = buf + kCap;
+    u64* out = buf + kMergeCap;
     SharedCtl* ctl = reinterpret_cast<SharedCtl*>(out + kMaxK);
     const int row = blockIdx.x, tid = threadIdx.x;
     if (row >= n_rows) return;
@@ -456,7 +777,7 @@ __global__ void __launch_bounds__(kThreads, 2) merge_lists_kernel(const u64* lis
     for (int g = 0; g < n_lists; ++g) {
         const int n = min(list_n[(size_t)g * n_rows + row], kMaxK);
         const u64* src = lists + ((size_t)g * n_rows + row) * kMaxK;
-        if (total + n <= kCap) {
+        if (total + n <= kMergeCap) {
             for (int i = tid; i < n; i += kThreads) buf[total + i] = src[i];
             total += n;
         } else if (tid == 0) {
@@ -466,14 +787,15 @@ __global__ void __launch_bounds__(kThreads, 2) merge_lists_kernel(const u64* lis
     consumer_sync();
     const TailOut tout{tokens, kept_ids, kept_pr, kept_n, nullptr, nullptr, status};
     const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index};
-    finish_row(buf, total, rt, out, ctl, tout);
+    const int kk = topk_sorted(buf, total, d.k, out, ctl);
+    row_epilogue(out, kk, rt, reinterpret_cast<double*>(buf), ctl, tout);
 }
 
 }  // namespace
 
 size_t stream_kernel_smem_bytes() { return kSmemTotal; }
 
-constexpr size_t kSmemMerge = kSmemBuf + kSmemOut + sizeof(SharedCtl);   // candidate list, selection scratch, control
+constexpr size_t kSmemMerge = (size_t)(kMergeCap + kMaxK) * sizeof(u64) + sizeof(SharedCtl);   // candidate list, ordered candidates, control
 
 // Per-device set-up (the current device): opt in to the large dynamic shared memory; report resident CTAs per SM.
 int prepare_device_kernels(int* ctas_per_sm) {

@@ -138,6 +138,14 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
     const int q_min = (pl.tiles_per_row + (max_seg - 1) - 1) / (max_seg - 1);
     q = std::max(q, q_min);
     q = std::max(1, std::min(q, fsb::kMaxTilesPerCta));
+    // a CTA whose range holds a row boundary pays the end-of-segment work twice: prefer the next q that divides the
+    // row (or is a multiple of it) when that costs at most a quarter more tiles per CTA
+    for (int c = q; c <= std::min(fsb::kMaxTilesPerCta, q + q / 4 + 1); ++c) {
+        if (pl.tiles_per_row % c == 0 || c % pl.tiles_per_row == 0) {
+            q = c;
+            break;
+        }
+    }
     pl.tiles_per_cta = q;
     pl.grid = (pl.total_tiles + q - 1) / q;
     return pl;
@@ -246,7 +254,6 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.write_back = (b->flags & FSB_WRITE_BACK) ? 1 : 0;
         a.vocab_offset = h->vocab_offset;
         a.softcap = h->softcap;
-        a.dbg = getenv("FSB_DEBUG") ? atoi(getenv("FSB_DEBUG")) : 0;
         const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
         const int e = fsb::launch_stream_kernel(a, grid, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
