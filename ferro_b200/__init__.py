@@ -38,7 +38,7 @@ PARAMS_DTYPE = np.dtype(
 )
 
 API_SYMBOLS = [
-    "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset",
+    "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap",
     "fsb_set_trace_buffer",
     "fsb_params_default", "fsb_params_validate", "fsb_stream_open", "fsb_stream_close", "fsb_stream_params",
     "fsb_stream_state_get", "fsb_stream_state_set", "fsb_sample_batch", "fsb_verify_windows", "fsb_last_kept",
@@ -86,6 +86,7 @@ def load_library(build_if_missing: bool = True):
     L.fsb_set_cuda_stream.argtypes = [vp, vp]
     L.fsb_set_softcap.argtypes = [vp, C.c_float]
     L.fsb_set_vocab_offset.argtypes = [vp, C.c_int32]
+    L.fsb_set_launch_overlap.argtypes = [vp, C.c_int]
     L.fsb_set_trace_buffer.argtypes = [vp, vp]
     L.fsb_params_default.argtypes = [vp]
     L.fsb_params_default.restype = None
@@ -213,6 +214,10 @@ class Engine:
 
     def set_trace_buffer(self, device_ptr: int):
         self._check(self.lib.fsb_set_trace_buffer(self._h, C.c_void_p(int(device_ptr)) if device_ptr else None))
+
+    def set_launch_overlap(self, on: bool):
+        """Let consecutive launches overlap (see fsb_set_launch_overlap in the C header for when that is safe)."""
+        self._check(self.lib.fsb_set_launch_overlap(self._h, 1 if on else 0))
 
     def set_vocab_offset(self, offset: int):
         self._check(self.lib.fsb_set_vocab_offset(self._h, int(offset)))

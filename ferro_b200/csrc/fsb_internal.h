@@ -78,6 +78,7 @@ struct StreamArgs {
     int32_t write_back;        // store penalised values into the caller's rows
     int32_t vocab_offset;      // token id of column 0
     float softcap;             // 0 = off
+    int32_t overlap;           // launch with programmatic stream serialization (see fsb_set_launch_overlap)
 };
 
 size_t stream_kernel_smem_bytes();

@@ -530,6 +530,7 @@ __device__ __noinline__ void segment_end(const StreamArgs& a, int row, int qn, i
         *reinterpret_cast<volatile int*>(&ctl->need_compact) = 1;
     }
     if (mark) trace_mark(a, 2);
+    pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
     // the segment's k best logits (or all, if fewer), in order; in the CTA that draws the last ticket of a row that
     // has several segments, a second pass does the same with everything the segments have published
     const int first_cta = (row * T) / Q, last_cta = (row * T + T - 1) / Q;
@@ -582,8 +583,12 @@ __global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const _
     const int t_begin = blockIdx.x * a.tiles_per_cta;
     const int t_end = min(t_begin + a.tiles_per_cta, a.total_tiles);
     const int nt = t_end - t_begin;
+    // With launch overlap on, the next launch in the stream may start as soon as this one leaves room; like this one
+    // it waits for its predecessor before it writes anything (segment_end), so only the reading of logits overlaps.
+    pdl_launch_dependents();
     if (nt <= 0) return;
     trace_mark(a, 0);
+    if (a.write_back) pdl_wait_prior();   // this launch stores into the logits while it streams
 
     if (tid == 0) {   // one thread initialises every barrier, then makes the initialisation visible to the copy engine
         for (int s = 0; s < kStages; ++s) {
@@ -813,9 +818,18 @@ int prepare_device_kernels(int* ctas_per_sm) {
 }
 
 int launch_stream_kernel(const StreamArgs& a, int grid, void* stream) {
-    if (a.softcap != 0.0f) stream_select_kernel<true><<<grid, kBlockThreads, kSmemTotal, static_cast<cudaStream_t>(stream)>>>(a);
-    else stream_select_kernel<false><<<grid, kBlockThreads, kSmemTotal, static_cast<cudaStream_t>(stream)>>>(a);
-    return (int)cudaGetLastError();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kBlockThreads);
+    cfg.dynamicSmemBytes = kSmemTotal;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.attrs = attr;
+    cfg.numAttrs = a.overlap ? 1 : 0;
+    if (a.softcap != 0.0f) return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<true>, a);
+    return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<false>, a);
 }
 
 int launch_merge_lists(const void* lists, const int32_t* list_n, int n_lists, int n_rows, const RowDesc* rows, int32_t* tokens,

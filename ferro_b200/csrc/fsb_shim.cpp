@@ -76,6 +76,7 @@ struct fsb_handle {
     bool own_stream = false;
     float softcap = 0.0f;
     int32_t vocab_offset = 0;
+    int launch_overlap = 0;
     std::vector<Stream> streams;
     std::vector<int> free_ids;
     // device scratch shared by all batches of this handle
@@ -254,6 +255,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.write_back = (b->flags & FSB_WRITE_BACK) ? 1 : 0;
         a.vocab_offset = h->vocab_offset;
         a.softcap = h->softcap;
+        a.overlap = h->launch_overlap;
         const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
         const int e = fsb::launch_stream_kernel(a, grid, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
@@ -509,6 +511,12 @@ int fsb_set_softcap(fsb_handle* h, float cap) {
 int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer) {
     if (!h) return FSB_ERR_INVALID;
     h->d_trace = static_cast<uint64_t*>(device_buffer);
+    return FSB_OK;
+}
+
+int fsb_set_launch_overlap(fsb_handle* h, int on) {
+    if (!h) return FSB_ERR_INVALID;
+    h->launch_overlap = on ? 1 : 0;
     return FSB_OK;
 }
 

@@ -91,6 +91,14 @@ FSB_API int fsb_set_softcap(fsb_handle* h, float cap);
  * cycles 1 copies issued, 2 first tile landed, 3 first bound set, 4 streaming done, 5 candidates published, 6 exit.  NULL (the default) turns it off.  No reference counterpart. */
 FSB_API int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer);
 
+/* Overlap of consecutive launches (off by default).  When on, fsb_batch_launch starts the streaming kernel with
+ * programmatic stream serialization: its CTAs may begin to read logits while the previous kernel in the stream is
+ * still finishing, and every write of the launch (tokens, kept sets, scratch) waits for that kernel to be complete.
+ * Turn it on only if the logits of a launch are complete before the previous kernel in the stream starts (for
+ * instance logits that alternate between buffers filled well ahead); batches with FSB_WRITE_BACK wait before they
+ * read anything, so they gain nothing.  No reference counterpart. */
+FSB_API int fsb_set_launch_overlap(fsb_handle* h, int on);
+
 /* Column offset of this device's vocabulary shard: local column c is token id c + offset (vocab sharding). */
 FSB_API int fsb_set_vocab_offset(fsb_handle* h, int32_t offset);
 

@@ -165,3 +165,37 @@ def test_errors_are_reported_not_fatal(engine):
     assert e.value.code == -2
     assert int(engine.sample_batch([sid], lg[:1], [[]])[0]) == 0     # the engine still works; all-equal row: lowest id
     engine.close_stream(sid)
+
+
+@pytest.mark.parametrize("shape", [(24, 65536), (8, 262144), (40, 20000)])
+def test_overlapping_launches_give_the_same_tokens(engine, oracle, shape):
+    """Launch overlap (programmatic stream serialization) changes when a launch may start, never what it writes:
+    a train of launches over rotating device buffers ends with the tokens of the oracle, and with the tokens the
+    same train gives without overlap.  (24, 65536) and (40, 20000) split rows over several CTAs, so the rows'
+    scratch counters are reused from launch to launch."""
+    import torch
+    B, V = shape
+    rng = np.random.default_rng(101)
+    lgs = [(rng.standard_normal((B, V)) * 3).astype(np.float32) for _ in range(3)]
+    devs = [torch.from_numpy(x).cuda() for x in lgs]
+    p = fb.make_params(B, temperature=0.9, top_k=50, top_p=0.9, repetition_penalty=1.2)
+    p["temperature"][::5] = 0.0
+    p["seed"] = 1000 + np.arange(B)
+    hists = [rng.integers(0, V, size=100).astype(np.int32) for _ in range(B)]
+    ref = oracle.sample_rows(p, oracle.new_rngs(p["seed"]), lgs[10 % 3].copy(), hists, cap=fb.MAX_CANDIDATE_K)
+    outs = []
+    for overlap in (False, True):
+        sids = engine.open_streams(p)
+        engine.set_launch_overlap(overlap)
+        try:
+            batch = engine.prepare_batch(sids, hists, V)
+            for i in range(11):
+                batch.launch(devs[i % 3].data_ptr())
+            outs.append(batch.tokens().copy())
+            batch.free()
+        finally:
+            engine.set_launch_overlap(False)
+            for s in sids:
+                engine.close_stream(int(s))
+    assert np.array_equal(outs[0], outs[1])
+    assert np.array_equal(outs[1], ref["tokens"])
