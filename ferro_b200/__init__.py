@@ -38,7 +38,7 @@ PARAMS_DTYPE = np.dtype(
 )
 
 API_SYMBOLS = [
-    "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap",
+    "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap", "fsb_batch_shard_launch", "fsb_batch_merge_launch",
     "fsb_set_trace_buffer",
     "fsb_params_default", "fsb_params_validate", "fsb_stream_open", "fsb_stream_close", "fsb_stream_params",
     "fsb_stream_state_get", "fsb_stream_state_set", "fsb_sample_batch", "fsb_verify_windows", "fsb_last_kept",
@@ -103,6 +103,8 @@ def load_library(build_if_missing: bool = True):
     L.fsb_batch_redraw.argtypes = [vp, vp]
     L.fsb_batch_launch.argtypes = [vp, vp, vp]
     L.fsb_batch_tokens.argtypes = [vp, vp, vp]
+    L.fsb_batch_shard_launch.argtypes = [vp, vp, vp, vp, vp]
+    L.fsb_batch_merge_launch.argtypes = [vp, vp, vp, vp, i32]
     L.fsb_batch_kernel_count.argtypes = [vp]
     L.fsb_batch_free.argtypes = [vp, vp]
     L.fsb_counters.argtypes = [vp, C.POINTER(_Counters)]
@@ -162,6 +164,16 @@ class Batch:
 
     def launch(self, logits_dev_ptr: int):
         self.engine._check(self.engine.lib.fsb_batch_launch(self.engine._h, self._ptr, C.c_void_p(int(logits_dev_ptr))))
+
+    def shard_launch(self, logits_shard_dev_ptr: int, lists_out_dev_ptr: int, counts_out_dev_ptr: int):
+        """Vocabulary-sharded first half: this device's best k candidates per row (``fsb_batch_shard_launch``)."""
+        self.engine._check(self.engine.lib.fsb_batch_shard_launch(self.engine._h, self._ptr, C.c_void_p(int(logits_shard_dev_ptr)),
+                                                                  C.c_void_p(int(lists_out_dev_ptr)), C.c_void_p(int(counts_out_dev_ptr))))
+
+    def merge_launch(self, lists_dev_ptr: int, counts_dev_ptr: int, n_lists: int):
+        """Vocabulary-sharded second half: merge the gathered lists of all shards and finish the rows."""
+        self.engine._check(self.engine.lib.fsb_batch_merge_launch(self.engine._h, self._ptr, C.c_void_p(int(lists_dev_ptr)),
+                                                                  C.c_void_p(int(counts_dev_ptr)), int(n_lists)))
 
     def tokens(self) -> np.ndarray:
         out = np.zeros(self.n_rows, dtype=np.int32)

@@ -228,7 +228,10 @@ int upload_batch(fsb_handle* h, fsb_batch* b) {
     return FSB_OK;
 }
 
-int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep_kept) {
+int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep_kept, uint64_t* shard_out = nullptr,
+                 int32_t* shard_n = nullptr) {
+    if (shard_out && b->n_full > 0)
+        return fail(h, FSB_ERR_RANGE, "rows whose candidate count exceeds %d (top_k = 0 or large) cannot be sharded by vocabulary", fsb::kMaxK);
     if (b->n_cand > 0) {
         fsb::StreamArgs a{};
         a.logits = logits_dev;
@@ -242,8 +245,8 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.kept_ids = keep_kept ? h->d_kept_ids : nullptr;
         a.kept_pr = keep_kept ? h->d_kept_pr : nullptr;
         a.kept_n = keep_kept ? h->d_kept_n : nullptr;
-        a.shard_out = nullptr;
-        a.shard_n = nullptr;
+        a.shard_out = shard_out;
+        a.shard_n = shard_n;
         a.trace = h->d_trace;
         a.row_ld = (b->n_full == 0) ? b->ld : -1;   // descriptors are in row order when every row takes this kernel
         a.n_rows = b->n_cand;
@@ -798,6 +801,26 @@ int fsb_batch_launch(fsb_handle* h, fsb_batch* b, const float* logits_dev) {
     return launch_batch(h, b, logits_dev, (b->flags & FSB_KEEP_KEPT_SET) != 0);
 }
 
+int fsb_batch_shard_launch(fsb_handle* h, fsb_batch* b, const float* logits_shard_dev, uint64_t* lists_out_dev, int32_t* counts_out_dev) {
+    if (!h || !b || !logits_shard_dev || !lists_out_dev || !counts_out_dev) return FSB_ERR_INVALID;
+    cudaSetDevice(h->device);
+    return launch_batch(h, b, logits_shard_dev, false, lists_out_dev, counts_out_dev);
+}
+int fsb_batch_merge_launch(fsb_handle* h, fsb_batch* b, const uint64_t* lists_dev, const int32_t* counts_dev, int n_lists) {
+    if (!h || !b || !lists_dev || !counts_dev) return FSB_ERR_INVALID;
+    if (n_lists < 1 || (int64_t)n_lists * fsb::kMaxK > fsb::kMergeCap)
+        return fail(h, FSB_ERR_RANGE, "between 1 and %d candidate lists can be merged", fsb::kMergeCap / fsb::kMaxK);
+    if (b->n_full > 0) return fail(h, FSB_ERR_RANGE, "the batch has rows that cannot be sharded by vocabulary");
+    cudaSetDevice(h->device);
+    const bool keep_kept = (b->flags & FSB_KEEP_KEPT_SET) != 0;
+    const int e = fsb::launch_merge_lists(lists_dev, counts_dev, n_lists, b->n_cand, b->d_rows(), b->d_tokens, keep_kept ? h->d_kept_ids : nullptr,
+                                          keep_kept ? h->d_kept_pr : nullptr, keep_kept ? h->d_kept_n : nullptr, h->d_status, h->stream);
+    if (e != 0) return fail(h, FSB_ERR_CUDA, "merge kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+    h->counters.kernel_launches++;
+    b->launched = true;
+    h->kept_valid = keep_kept;
+    return FSB_OK;
+}
 int fsb_batch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out) {
     if (!h || !b || !tokens_out) return FSB_ERR_INVALID;
     if (!b->launched) return fail(h, FSB_ERR_INVALID, "the batch has not been launched");

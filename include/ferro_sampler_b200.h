@@ -160,6 +160,19 @@ FSB_API int fsb_batch_redraw(fsb_handle* h, fsb_batch* b);
 FSB_API int fsb_batch_launch(fsb_handle* h, fsb_batch* b, const float* logits_dev);
 /* Wait for the last launch of `b` and copy its tokens (n_rows int32) to host memory. */
 FSB_API int fsb_batch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out);
+/* Vocabulary sharding: this device holds columns [offset, offset + n_vocab) of every row (fsb_set_vocab_offset gives
+ * the offset; history ids stay global).  fsb_batch_shard_launch runs the streaming kernel on the shard and leaves,
+ * per row, the shard's best k candidates in descending order: `lists_out_dev` is [n_rows][FSB_MAX_CANDIDATE_K]
+ * 64-bit keys (order-preserving value key << 32 | 0xFFFFFFFF - global token id), `counts_out_dev` [n_rows] how many
+ * are valid.  The caller brings the lists of all shards into this device's memory (an all-gather: [n_lists][n_rows]
+ * [FSB_MAX_CANDIDATE_K] and [n_lists][n_rows]) and calls fsb_batch_merge_launch, which finishes every row exactly
+ * as the unsharded launch would (the best k of the whole row are among the shards' best k); fsb_batch_tokens then
+ * returns the tokens.  Every rank must have opened the same streams in the same state, so that all ranks draw the
+ * same engine outputs.  Rows with top_k = 0 or k > FSB_MAX_CANDIDATE_K are refused (FSB_ERR_RANGE): shard those by
+ * rows.  At most 9 lists.  Both calls are asynchronous on the engine's stream.  No reference counterpart. */
+FSB_API int fsb_batch_shard_launch(fsb_handle* h, fsb_batch* b, const float* logits_shard_dev, uint64_t* lists_out_dev,
+                                   int32_t* counts_out_dev);
+FSB_API int fsb_batch_merge_launch(fsb_handle* h, fsb_batch* b, const uint64_t* lists_dev, const int32_t* counts_dev, int n_lists);
 /* Number of kernels one fsb_batch_launch enqueues (for launch accounting). */
 FSB_API int fsb_batch_kernel_count(const fsb_batch* b);
 FSB_API int fsb_batch_free(fsb_handle* h, fsb_batch* b);

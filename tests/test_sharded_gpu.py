@@ -1,0 +1,77 @@
+"""Vocabulary sharding on one GPU: G engines stand in for G ranks (same streams, same seeds, different column
+offsets); their candidate lists are stacked as an all-gather would leave them and merged.  The tokens must be those
+of the oracle and of the unsharded launch."""
+import numpy as np
+import pytest
+
+import ferro_b200 as fb
+from ferro_b200 import sharded
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("shape", [(16, 262144, 4), (9, 70001, 3), (4, 65536, 8)])
+def test_sharded_candidates_merge_to_the_unsharded_result(engine, oracle, shape):
+    import torch
+    B, V, G = shape
+    rng = np.random.default_rng(31 + G)
+    lg = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+    lg[:, ::7] = np.round(lg[:, ::7])                      # ties that straddle shard boundaries
+    p = fb.make_params(B, temperature=0.8, top_k=40, top_p=0.9, min_p=0.02, repetition_penalty=1.3)
+    p["temperature"][::4] = 0.0
+    p["top_k"][1::3] = 256
+    p["seed"] = 500 + np.arange(B)
+    hists = [rng.integers(0, V, size=200).astype(np.int32) for _ in range(B)]
+    ref = oracle.sample_rows(p, oracle.new_rngs(p["seed"]), lg.copy(), hists, cap=fb.MAX_CANDIDATE_K)
+    dev = torch.from_numpy(lg).cuda()
+    parts = sharded.vocab_partition(V, G)
+    lists = torch.zeros((G, B, sharded.MAX_K), dtype=torch.int64, device="cuda")
+    counts = torch.zeros((G, B), dtype=torch.int32, device="cuda")
+    engines, batches = [], []
+    try:
+        for g, (lo, hi) in enumerate(parts):
+            eng = fb.Engine(device=0, max_rows=B, max_vocab=hi - lo, max_hist_ids=B * 200 + 16)
+            engines.append(eng)
+            eng.set_vocab_offset(lo)
+            sids = eng.open_streams(p)
+            b = eng.prepare_batch(sids, hists, hi - lo, ld=V, flags=fb.KEEP_KEPT_SET)
+            batches.append(b)
+            b.shard_launch(dev.data_ptr() + 4 * lo, lists[g].data_ptr(), counts[g].data_ptr())
+        torch.cuda.synchronize()
+        batches[0].merge_launch(lists.data_ptr(), counts.data_ptr(), G)
+        tok = batches[0].tokens()
+        assert np.array_equal(tok, ref["tokens"])
+        for i in range(B):
+            if p["temperature"][i] > 0:
+                ids, pr, n = engines[0].last_kept(i)
+                assert n == ref["n_keep"][i] and np.array_equal(ids, ref["kept_ids"][i, :n])
+                assert np.abs(pr - ref["kept_pr"][i, :n]).max() <= 1e-6
+    finally:
+        for b in batches:
+            b.free()
+        for eng in engines:
+            eng.close()
+    # the unsharded launch on the same inputs
+    sids = engine.open_streams(p)
+    try:
+        assert np.array_equal(engine.sample_batch(sids, lg.copy(), hists), tok)
+    finally:
+        for s in sids:
+            engine.close_stream(int(s))
+
+
+def test_full_vocabulary_rows_are_refused_by_the_sharded_launch(engine):
+    import torch
+    p = fb.make_params(2, temperature=1.0, top_k=0)
+    p["seed"] = [3, 4]
+    sids = engine.open_streams(p)
+    try:
+        b = engine.prepare_batch(sids, [np.zeros(0, np.int32)] * 2, 4096)
+        lists = torch.zeros((2, sharded.MAX_K), dtype=torch.int64, device="cuda")
+        counts = torch.zeros(2, dtype=torch.int32, device="cuda")
+        with pytest.raises(fb.SamplerError):
+            b.shard_launch(torch.zeros(2, 4096, device="cuda").data_ptr(), lists.data_ptr(), counts.data_ptr())
+        b.free()
+    finally:
+        for s in sids:
+            engine.close_stream(int(s))
