@@ -75,3 +75,51 @@ def test_full_vocabulary_rows_are_refused_by_the_sharded_launch(engine):
     finally:
         for s in sids:
             engine.close_stream(int(s))
+
+
+def _nccl_rank(rank, world, port, B, V, out_dir):
+    import os
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        rng = np.random.default_rng(77)
+        lg = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+        p = fb.make_params(B, temperature=0.9, top_k=50, top_p=0.95, repetition_penalty=1.1)
+        p["temperature"][::3] = 0.0
+        p["seed"] = 900 + np.arange(B)
+        hists = [rng.integers(0, V, size=64).astype(np.int32) for _ in range(B)]
+        eng = fb.Engine(device=rank, max_rows=B, max_vocab=V, max_hist_ids=B * 64 + 16)
+        vs = sharded.VocabShardedSampler(eng, V, rank, world)
+        lo, hi = vs.columns
+        shard = torch.from_numpy(np.ascontiguousarray(lg[:, lo:hi])).cuda()
+        sids = eng.open_streams(p)
+        tok = vs.sample(sids, shard, hists)
+        np.save(os.path.join(out_dir, f"tok{rank}.npy"), tok)
+        eng.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpus_vocabulary_sharded_over_nccl(oracle, tmp_path):
+    import socket
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    B, V, world = 32, 262144, 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_nccl_rank, args=(world, port, B, V, str(tmp_path)), nprocs=world, join=True)
+    rng = np.random.default_rng(77)
+    lg = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+    p = fb.make_params(B, temperature=0.9, top_k=50, top_p=0.95, repetition_penalty=1.1)
+    p["temperature"][::3] = 0.0
+    p["seed"] = 900 + np.arange(B)
+    hists = [rng.integers(0, V, size=64).astype(np.int32) for _ in range(B)]
+    ref = oracle.sample_rows(p, oracle.new_rngs(p["seed"]), lg, hists)
+    t0, t1 = np.load(tmp_path / "tok0.npy"), np.load(tmp_path / "tok1.npy")
+    assert np.array_equal(t0, t1) and np.array_equal(t0, ref["tokens"])
