@@ -27,6 +27,8 @@ LOGITS_ON_HOST = 1
 WRITE_BACK = 2
 KEEP_KEPT_SET = 4
 MAX_CANDIDATE_K = 256
+STATIC_MAX_ROWS = 64   # FSB_STATIC_MAX_ROWS
+STATIC_WAIT = 1        # FSB_STATIC_WAIT
 
 PARAMS_DTYPE = np.dtype(
     {
@@ -38,7 +40,7 @@ PARAMS_DTYPE = np.dtype(
 )
 
 API_SYMBOLS = [
-    "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap", "fsb_batch_shard_launch", "fsb_batch_merge_launch",
+    "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap", "fsb_batch_shard_launch", "fsb_batch_merge_launch", "fsb_argmax_rows_static",
     "fsb_set_trace_buffer",
     "fsb_params_default", "fsb_params_validate", "fsb_stream_open", "fsb_stream_close", "fsb_stream_params",
     "fsb_stream_state_get", "fsb_stream_state_set", "fsb_sample_batch", "fsb_verify_windows", "fsb_last_kept",
@@ -108,6 +110,7 @@ def load_library(build_if_missing: bool = True):
     L.fsb_batch_kernel_count.argtypes = [vp]
     L.fsb_batch_free.argtypes = [vp, vp]
     L.fsb_counters.argtypes = [vp, C.POINTER(_Counters)]
+    L.fsb_argmax_rows_static.argtypes = [C.c_int, vp, i64, i32, i32, vp, vp, u32]
     for name in API_SYMBOLS:
         if name not in ("fsb_last_error", "fsb_params_default"):
             getattr(L, name).restype = i32
@@ -319,6 +322,16 @@ class Engine:
 
 
 _default_engines: dict = {}
+
+
+def argmax_rows_static(logits_dev_ptr: int, ld: int, n_rows: int, n_vocab: int, tokens_dev_ptr: int, device: int = 0,
+                       cuda_stream: int = 0, wait: bool = True) -> None:
+    """Greedy tokens of device rows through ``fsb_argmax_rows_static``: no handle and no allocation; at most
+    ``STATIC_MAX_ROWS`` rows; all calls on a device share one scratch array (see the C header)."""
+    rc = load_library().fsb_argmax_rows_static(int(device), C.c_void_p(int(logits_dev_ptr)), int(ld), int(n_rows), int(n_vocab),
+                                               C.c_void_p(int(tokens_dev_ptr)), C.c_void_p(int(cuda_stream)), STATIC_WAIT if wait else 0)
+    if rc != 0:
+        raise SamplerError(rc, f"fsb_argmax_rows_static: {STATUS_NAMES.get(rc, rc)}")
 
 
 def default_engine(device: int = 0) -> Engine:

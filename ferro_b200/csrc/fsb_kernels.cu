@@ -7,6 +7,7 @@
 // How it works is described above SegCtx below.
 #include <cuda_runtime.h>
 
+#include "../../include/ferro_sampler_b200.h"
 #include "fsb_device.cuh"
 
 namespace fsb {
@@ -840,3 +841,111 @@ int launch_merge_lists(const void* lists, const int32_t* list_n, int n_lists, in
 }
 
 }  // namespace fsb
+
+// ---------------------------------------------------------------------------------------------- fsb_argmax_rows_static
+// Greedy tokens of device-resident rows with no allocation at all: the streaming kernel above, run with every piece
+// of device memory it needs taken from one array that is part of this library's image.
+namespace fsb {
+namespace {
+
+constexpr int kStaticMaxRows = FSB_STATIC_MAX_ROWS;
+constexpr size_t kStaticRowsOff = 0;                                                       // RowDesc[kStaticMaxRows]
+constexpr size_t kStaticFillOff = kStaticRowsOff + sizeof(RowDesc) * kStaticMaxRows;       // fill[], ticket[]: zero between calls
+constexpr size_t kStaticStatusOff = kStaticFillOff + 2 * sizeof(uint32_t) * kStaticMaxRows;   // status word: zero between calls
+constexpr size_t kStaticScratchOff = 8192;                                                 // [kStaticMaxRows][kMergeCap] candidates
+constexpr size_t kStaticBytes = kStaticScratchOff + sizeof(u64) * (size_t)kMergeCap * kStaticMaxRows;
+static_assert(kStaticStatusOff + sizeof(uint32_t) <= kStaticScratchOff, "descriptors, counters and status fit below the candidates");
+
+// Zero when the library is loaded (static storage); the kernel leaves the counters at zero when it finishes.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+constexpr int kStaticMaxDevices = 64;
+struct StaticDevice {
+    void* base = nullptr;   // device address of g_static_scratch on this device
+    int slots = 0;          // CTAs of the streaming kernel that fit on the device at once
+};
+StaticDevice g_static_dev[kStaticMaxDevices];
+
+// Row descriptors of plain greedy rows (no penalty window): row r starts at r * ld, its token goes to tokens[r].
+__global__ void static_greedy_rows_kernel(RowDesc* rows, int n_rows, int64_t ld) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    RowDesc d{};
+    d.logits_off = (int64_t)r * ld;
+    d.k = 1;
+    d.temperature = 0.0f;
+    d.top_p = 1.0f;
+    d.penalty = 1.0f;
+    d.flags = kRowGreedy;
+    d.out_index = r;
+    rows[r] = d;
+}
+
+}  // namespace
+}  // namespace fsb
+
+extern "C" int fsb_argmax_rows_static(int device, const float* logits_dev, int64_t ld, int n_rows, int n_vocab, int32_t* tokens_dev,
+                                      void* cuda_stream, unsigned flags) {
+    using namespace fsb;
+    if (!logits_dev || !tokens_dev || n_rows < 0 || n_vocab <= 0 || ld < n_vocab || (flags & ~FSB_STATIC_WAIT)) return FSB_ERR_INVALID;
+    if (n_rows > kStaticMaxRows) return FSB_ERR_CAPACITY;   // the static array holds FSB_STATIC_MAX_ROWS rows of scratch, no more
+    if (device < 0 || device >= kStaticMaxDevices) return FSB_ERR_NO_DEVICE;
+    if (n_rows == 0) return FSB_OK;
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) return FSB_ERR_NO_DEVICE;
+    if (cudaSetDevice(device) != cudaSuccess) return FSB_ERR_NO_DEVICE;
+    int rc = FSB_OK;
+    StaticDevice& sd = g_static_dev[device];
+    if (!sd.base) {   // first call on this device (it is current): where the array lives, how many CTAs fit
+        void* p = nullptr;
+        int per_sm = 0, sms = 0;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) rc = FSB_ERR_CUDA;
+        if (rc == FSB_OK && prepare_device_kernels(&per_sm) != 0) rc = FSB_ERR_CUDA;
+        if (rc == FSB_OK && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) rc = FSB_ERR_CUDA;
+        if (rc == FSB_OK) {
+            sd.slots = (sms > 0 ? sms : 1) * (per_sm > 0 ? per_sm : 1);
+            sd.base = p;
+        }
+    }
+    if (rc == FSB_OK) {
+        unsigned char* base = static_cast<unsigned char*>(sd.base);
+        cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+        RowDesc* rows = reinterpret_cast<RowDesc*>(base + kStaticRowsOff);
+        static_greedy_rows_kernel<<<(n_rows + 63) / 64, 64, 0, st>>>(rows, n_rows, ld);
+        StreamArgs a{};
+        a.logits = logits_dev;
+        a.rows = rows;
+        a.hist = nullptr;
+        a.scratch = reinterpret_cast<uint64_t*>(base + kStaticScratchOff);
+        a.fill = reinterpret_cast<uint32_t*>(base + kStaticFillOff);
+        a.ticket = a.fill + kStaticMaxRows;
+        a.tokens = tokens_dev;
+        a.status = reinterpret_cast<uint32_t*>(base + kStaticStatusOff);
+        a.row_ld = ld;
+        a.n_rows = n_rows;
+        a.n_vocab = n_vocab;
+        a.tiles_per_row = (n_vocab + kTile - 1) / kTile;
+        a.total_tiles = n_rows * a.tiles_per_row;
+        int q = (a.total_tiles + sd.slots - 1) / sd.slots;   // equal contiguous ranges of tiles, one per resident CTA
+        q = q < 1 ? 1 : (q > kMaxTilesPerCta ? kMaxTilesPerCta : q);
+        a.tiles_per_cta = q;
+        a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (ld & 3) == 0) ? 1 : 0;
+        if ((a.tiles_per_row + q - 1) / q + 1 > kMergeCap) {
+            rc = FSB_ERR_CAPACITY;   // more segments per row than a row's scratch has entries (one candidate per segment)
+        } else if (launch_stream_kernel(a, (a.total_tiles + q - 1) / q, st) != 0) {
+            rc = FSB_ERR_CUDA;
+        } else if (flags & FSB_STATIC_WAIT) {
+            uint32_t status = 0;
+            if (cudaMemcpyAsync(&status, a.status, sizeof status, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+                cudaStreamSynchronize(st) != cudaSuccess) {
+                rc = FSB_ERR_CUDA;
+            } else if (status != 0u) {   // put counters and status back to zero for the next call
+                cudaMemsetAsync(base + kStaticFillOff, 0, kStaticScratchOff - kStaticFillOff, st);
+                cudaStreamSynchronize(st);
+                rc = FSB_ERR_DEVICE;
+            }
+        }
+    }
+    if (prev >= 0 && prev != device) cudaSetDevice(prev);
+    return rc;
+}

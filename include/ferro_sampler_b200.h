@@ -189,6 +189,28 @@ typedef struct fsb_counters_t {
 } fsb_counters_t;
 FSB_API int fsb_counters(const fsb_handle* h, fsb_counters_t* out);
 
+/* Greedy tokens (temperature 0: lowest index of the row maximum, src/sampler.cpp:19-23) of up to FSB_STATIC_MAX_ROWS
+ * device-resident rows, for callers that must not allocate: no handle, no cudaMalloc / cudaFree / pinned host memory,
+ * in this call or any earlier one.  That is the situation of a decode loop whose device memory is owned entirely by
+ * the serving engine's own pool, and of code that runs where an allocation would stall the device (a cudaMalloc
+ * waits for running kernels).  All device memory the streaming kernel needs besides the caller's buffers (row
+ * descriptors, the rows' candidate scratch, its counters and status word: about 1.2 MB) is one array inside the
+ * library's own image.  No penalty window, no softcap, no random draw: exactly the rows of a verification window
+ * with repetition_penalty 1 (src/server.cpp:630-636).
+ *   logits_dev [n_rows][ld] fp32 and tokens_dev [n_rows] int32 are device memory of `device`; the kernels are
+ *   enqueued on `cuda_stream` (0 = the default stream).  With FSB_STATIC_WAIT the call waits for them and reports a
+ *   kernel error as FSB_ERR_DEVICE; without it the call returns as soon as the work is enqueued.
+ *   n_rows > FSB_STATIC_MAX_ROWS is refused with FSB_ERR_CAPACITY (the array has room for that many rows).
+ * The first call on a device looks up the array's address and sets the kernel's attributes (with that device
+ * current); make that first call before any stream capture begins.  All calls on a device share the one array: its
+ * counters and status word must be zero when a call starts (they are when the library is loaded, every finished call
+ * leaves them so, and a call that reports FSB_ERR_DEVICE clears them), and two calls whose kernels can run at the
+ * same time - different streams, different threads - race on it.  Not thread-safe.  No reference counterpart. */
+#define FSB_STATIC_MAX_ROWS 64
+#define FSB_STATIC_WAIT 1u
+FSB_API int fsb_argmax_rows_static(int device, const float* logits_dev, int64_t ld, int n_rows, int n_vocab, int32_t* tokens_dev,
+                                   void* cuda_stream, unsigned flags);
+
 #ifdef __cplusplus
 }
 #endif
