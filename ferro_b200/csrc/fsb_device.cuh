@@ -300,7 +300,7 @@ __device__ __forceinline__ void warp_sort_desc(u64 (&v)[S]) {
 // is the entry's rank.  buf is overwritten (with room for the last run's padding: 32 * ceil(n / 32) entries); `out`
 // has room for kMaxK composites and must not overlap buf.  All consumer threads must call, after a barrier that
 // made buf visible; out is visible to all on return.
-static __device__ __noinline__ int topk_sorted(u64* buf, int n, int k, u64* out, SharedCtl* ctl) {
+static __device__ __forceinline__ int topk_sorted(u64* buf, int n, int k, u64* out, SharedCtl* ctl) {
     static_assert(kMaxK <= 32 * kNumWarps, "one run per warp");
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (n > kMaxK) n = select_list_topk(buf, n, k, out, ctl);
@@ -317,7 +317,7 @@ static __device__ __noinline__ int topk_sorted(u64* buf, int n, int k, u64* out,
     if (c != 0ull) {
         int rank = lane;
 #pragma unroll
-        for (int r2 = 0; r2 < kNumWarps; ++r2) {
+        for (int r2 = 0; r2 < kMaxK / 32; ++r2) {
             if (r2 < runs && r2 != warp) {
                 const u64* run = buf + 32 * r2;   // descending: count its entries above c
                 int lo = 0;
@@ -338,7 +338,7 @@ static __device__ __noinline__ int topk_sorted(u64* buf, int n, int k, u64* out,
 // or finishes the row: softmax over the candidates in fp64, sequential sums in candidate order, min-p, top-p,
 // draw.  `work` is scratch for 2 * kMaxK doubles that does not overlap srt.  All consumer threads must call it with
 // the same arguments.
-static __device__ __noinline__ void row_epilogue(const u64* srt, int kk, const RowTail r, double* work, SharedCtl* ctl, const TailOut o) {
+static __device__ __forceinline__ void row_epilogue(const u64* srt, int kk, const RowTail r, double* work, SharedCtl* ctl, const TailOut o) {
     const int tid = threadIdx.x;
     double* e = work;
     double* P = work + kMaxK;

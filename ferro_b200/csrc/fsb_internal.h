@@ -5,8 +5,8 @@
 namespace fsb {
 
 // ---- compile-time geometry of the streaming kernel ---------------------------------------------------------
-constexpr int kThreads = 256;                 // consumer threads per CTA (8 warps); the streaming kernel adds one producer warp
-constexpr int kTile = 4096;                   // fp32 logits per CTA tile (16 KiB, one bulk copy; 512 logits per warp)
+constexpr int kThreads = 512;                 // consumer threads per CTA (16 warps); the streaming kernel adds one producer warp
+constexpr int kTile = 8192;                   // fp32 logits per CTA tile (32 KiB, one bulk copy; 512 logits per warp)
 constexpr int kStages = 4;                    // tiles in flight per CTA
 constexpr int kMaxK = 256;                    // largest k of the candidate path (== FSB_MAX_CANDIDATE_K)
 constexpr int kLaneQueue = 16;                // cells (4-byte entries) a lane can note before it must drop stale ones
@@ -14,7 +14,7 @@ constexpr int kFlatCells = 960;               // cells (float4 + token id) gathe
 constexpr int kCellBytes = 20;
 constexpr int kMergeCap = kFlatCells * kCellBytes / 8;   // 2400: candidates one row may gather from all its segments
                                                           // (the gathered cells' memory seen as a list of composites)
-constexpr int kBitmapSpan = 65536;            // columns one penalty bitmap covers (one segment never spans more)
+constexpr int kBitmapSpan = 131072;           // columns one penalty bitmap covers (one segment never spans more)
 constexpr int kBitmapWords = kBitmapSpan / 32;
 constexpr int kMaxTilesPerCta = kBitmapSpan / kTile;
 

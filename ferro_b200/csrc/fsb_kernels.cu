@@ -24,15 +24,14 @@ constexpr size_t kSmemCells = (size_t)kFlatCells * kCellBytes;                  
 constexpr size_t kSmemKept = (size_t)kMaxK * kCellBytes;                           // cells that survived a re-selection; selection scratch
 constexpr size_t kSmemBitmap = (size_t)kBitmapWords * sizeof(unsigned);
 constexpr size_t kSmemTotal = kSmemStage + kSmemQueue + kSmemCells + kSmemKept + kSmemBitmap + sizeof(SharedCtl);
-static_assert(kSmemTotal <= 113 * 1024, "two CTAs must fit into one SM's shared memory");
+static_assert(kSmemTotal <= 227 * 1024, "one CTA per SM");
 static_assert(kSmemCells >= (size_t)kMergeCap * sizeof(u64), "the element list lives in the gathered cells' memory");
 static_assert(kMergeCap >= 4 * kMaxK, "the logits of kMaxK surviving cells must fit into the element list");
 static_assert(kMergeCap >= 2 * kMaxK, "the epilogue's arrays live in the list's memory");
 static_assert(kSmemKept >= (size_t)kMaxK * sizeof(u64), "the ordered candidates live in the survivors' memory");
 static_assert(kWTile == 512, "a lane owns four float4 of a warp tile");
 static_assert(kMaxTilesPerCta <= 64, "a location is one byte: the tile number above two bits");
-static_assert(kSmemTotal <= 115712, "two CTAs per SM: 228 KiB less 1 KiB reserved per CTA");
-static_assert(kFlatCells >= 3 * kThreads, "a capped gather round takes three cells per thread");
+static_assert(kFlatCells >= kThreads, "a capped gather round takes at least one cell per thread");
 static_assert(kLaneQueue % 4 == 0 && kLaneQueue >= 8, "lanes look at four cells per tile");
 
 constexpr long long kCopyWaitCycles = 2000000000ll;   // about 1 s: a bulk copy that has not landed by then is reported, not awaited
@@ -143,10 +142,14 @@ __device__ __forceinline__ float warp_bound(float run_max, int k) {
 // best.  Each warp posts its value; values only grow, so a reader may use another warp's older value without a
 // barrier.
 __device__ __forceinline__ float min_warp_bounds(SharedCtl* ctl) {
-    float4 lo, hi;   // volatile: re-read on every call
-    asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(lo.x), "=f"(lo.y), "=f"(lo.z), "=f"(lo.w) : "r"(smem_u32(&ctl->wbound[0])));
-    asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(hi.x), "=f"(hi.y), "=f"(hi.z), "=f"(hi.w) : "r"(smem_u32(&ctl->wbound[4])));
-    return fminf(fminf(fminf(lo.x, lo.y), fminf(lo.z, lo.w)), fminf(fminf(hi.x, hi.y), fminf(hi.z, hi.w)));
+    float m = __int_as_float(0x7f800000);
+#pragma unroll
+    for (int w = 0; w < kWarps; w += 4) {
+        float4 v;   // volatile: re-read on every call
+        asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(&ctl->wbound[w])));
+        m = fminf(m, fminf(fminf(v.x, v.y), fminf(v.z, v.w)));
+    }
+    return m;
 }
 __device__ __forceinline__ float refresh_bound(float run_max, int k, SharedCtl* ctl) {
     const float wb = warp_bound(run_max, k);
@@ -315,29 +318,15 @@ __device__ __noinline__ SelectResult select_cells(int nq, int nkept, int k) {
     return SelectResult{min(ctl->out_cnt, kMaxK), L};
 }
 
-// One rendez-vous of all consumer warps of the CTA.  A warp comes here because it saw a request for a re-selection
-// (a lane's queue is nearly full), or because it has finished its part of the segment.  Every warp posts its
-// bound and the number of cells its lanes hold.  If a re-selection was asked for, the queued cells are read again
-// and the CTA keeps the k best cells (they become the survivors' list, all queues become empty), and `happened`
-// is set; otherwise every warp had finished and the posted values describe the whole segment.  Warps depend on
-// nothing but their own copies while streaming and look out for requests at every tile and in every wait, so
-// every warp gets here in bounded time.
-// Returns (happened) | (survivors << 1); the composite bound of a re-selection is left in ctl->ev_bound and the
-// warps' bounds in ctl->wbound.
-__device__ __forceinline__ int event_happened(int ev) { return ev & 1; }
-__device__ __forceinline__ int event_nkept(int ev) { return (ev >> 1) & 1023; }
+// The re-selection proper (rare): every lane drops the noted cells the bound has overtaken, the rest are read again
+// and the CTA keeps the k best cells.  All consumer threads call it, after the barrier of the rendez-vous.
 template <bool SOFTCAP>
-__device__ __noinline__ int cta_event(int qn, int nkept, float run_max, float thr_f) {
+__device__ __noinline__ int compact_cells(int qn, int nkept, float thr_f) {
     const Smem m = smem_view();
     SharedCtl* ctl = m.ctl;
     const SegCtx& sc = ctl->seg;
     const int k = sc.k;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float wb = warp_bound(run_max, k);
-    if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
-    if (tid == 0) ctl->out_cnt = 0;
-    consumer_sync();
-    if (*reinterpret_cast<volatile int*>(&ctl->need_compact) == 0) return nkept << 1;
+    const int tid = threadIdx.x;
     u64 bound = 0ull;
     // every lane first drops what the bound has overtaken; then gather rounds: everything at once if it fits, else
     // three cells per thread and round
@@ -379,6 +368,32 @@ __device__ __noinline__ int cta_event(int qn, int nkept, float run_max, float th
     }
     consumer_sync();
     return 1 | (nkept << 1);
+}
+
+// One rendez-vous of all consumer warps of the CTA.  A warp comes here because it saw a request for a re-selection
+// (a lane's queue is nearly full), or because it has finished its part of the segment.  Every warp posts its
+// bound and the number of cells its lanes hold.  If a re-selection was asked for, the queued cells are read again
+// and the CTA keeps the k best cells (they become the survivors' list, all queues become empty), and `happened`
+// is set; otherwise every warp had finished and the posted values describe the whole segment.  Warps depend on
+// nothing but their own copies while streaming and look out for requests at every tile and in every wait, so
+// every warp gets here in bounded time.
+// Returns (happened) | (survivors << 1); the composite bound of a re-selection is left in ctl->ev_bound and the
+// warps' bounds in ctl->wbound.
+__device__ __forceinline__ int event_happened(int ev) { return ev & 1; }
+__device__ __forceinline__ int event_nkept(int ev) { return (ev >> 1) & 1023; }
+template <bool SOFTCAP>
+__device__ __forceinline__ int cta_event(int qn, int nkept, float run_max, float thr_f) {
+    const Smem m = smem_view();
+    SharedCtl* ctl = m.ctl;
+    const SegCtx& sc = ctl->seg;
+    const int k = sc.k;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float wb = warp_bound(run_max, k);
+    if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
+    if (tid == 0) ctl->out_cnt = 0;
+    consumer_sync();
+    if (*reinterpret_cast<volatile int*>(&ctl->need_compact) == 0) return nkept << 1;
+    return compact_cells<SOFTCAP>(qn, nkept, thr_f);
 }
 
 // Appends to the element list the logits of up to N cells of this thread that reach `thr` (NaNs and columns past
@@ -468,7 +483,7 @@ __device__ __forceinline__ void producer_loop(const StreamArgs& a, float* stage,
 // re-selections that were still asked for, the rendez-vous of the finished warps, the element list, the segment's
 // k best logits in order, and - in the CTA that draws the row's last ticket - the merge and the row's epilogue.
 template <bool SOFTCAP>
-__device__ __noinline__ void segment_end(const StreamArgs& a, int row, int qn, int nkept, float thr_f, float run_max, bool mark) {
+__device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn, int nkept, float thr_f, float run_max, bool mark) {
     const Smem m = smem_view();
     SharedCtl* ctl = m.ctl;
     const SegCtx& sc = ctl->seg;
@@ -576,7 +591,7 @@ __device__ __noinline__ void segment_end(const StreamArgs& a, int row, int qn, i
 }
 
 template <bool SOFTCAP>
-__global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const __grid_constant__ StreamArgs a) {
     const Smem m = smem_view();
     SharedCtl* ctl = m.ctl;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -769,7 +784,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) stream_select_kernel(const _
 
 // Merge of per-shard candidate lists (vocabulary-sharded mode): one CTA per row gathers n_lists sorted lists of
 // up to kMaxK composites each (already in this device's memory) and runs the row epilogue.
-__global__ void __launch_bounds__(kThreads, 2) merge_lists_kernel(const u64* lists, const int32_t* list_n, int n_lists, int n_rows,
+__global__ void __launch_bounds__(kThreads, 1) merge_lists_kernel(const u64* lists, const int32_t* list_n, int n_lists, int n_rows,
                                                                  const RowDesc* rows, int32_t* tokens, int32_t* kept_ids,
                                                                  double* kept_pr, int32_t* kept_n, unsigned* status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
