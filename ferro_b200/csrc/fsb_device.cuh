@@ -105,6 +105,15 @@ __device__ __forceinline__ float4 ldg_stream(const float4* p) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Ticket counter shared by the CTAs of a row: the add releases this thread's earlier writes - and those of the
+// CTA's other threads that a barrier ordered before it - to the whole device, and acquires what earlier ticket
+// holders released.
+__device__ __forceinline__ unsigned ticket_add_acq_rel(unsigned* p, unsigned v) {
+    unsigned old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+
 __device__ __forceinline__ u64 global_timer_ns() {
     u64 t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -177,6 +177,22 @@ __device__ __forceinline__ unsigned make_entry(float mx, unsigned loc) { return 
 __device__ __forceinline__ float entry_value(unsigned e) { return __uint_as_float(e & 0xFFFFFF00u); }
 __device__ __forceinline__ float truncated(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFFF00u); }
 
+// Notes a cell in this lane's queue if its maximum reaches the bound: a compare, the entry, one predicated store and
+// one predicated increment - no branch.  `q_base` is the shared-memory address of the lane's entry 0; entries of
+// one lane are kThreads * 4 bytes apart.
+__device__ __forceinline__ void note_cell_if(float mx, float thr, unsigned loc, unsigned q_base, int& qn) {
+    const unsigned entry = make_entry(mx, loc);
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .u32 a;\n\t"
+        "setp.ge.f32 p, %2, %3;\n\t"
+        "mad.lo.u32 a, %0, %5, %1;\n\t"
+        "@p st.shared.u32 [a], %4;\n\t"
+        "@p add.s32 %0, %0, 1;\n\t}"
+        : "+r"(qn)
+        : "r"(q_base), "f"(mx), "f"(thr), "r"(entry), "n"(kThreads * 4)
+        : "memory");
+}
+
 // Drops the entries of this lane's queue whose cell maximum cannot reach `thr` any more; returns the new length.
 __device__ __forceinline__ int drop_stale(unsigned* myq, int qn, float thr) {
     const float t = truncated(thr);
@@ -547,38 +563,69 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
     }
     if (mark) trace_mark(a, 2);
     pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
-    // the segment's k best logits (or all, if fewer), in order; in the CTA that draws the last ticket of a row that
-    // has several segments, a second pass does the same with everything the segments have published
+    // the segment's k best logits (or all, if fewer), in order
     const int first_cta = (row * T) / Q, last_cta = (row * T + T - 1) / Q;
     const int nseg = last_cta - first_cta + 1;
     bool merge_here = true;
-    int kk = 0;
-    for (int pass = 0;; ++pass) {
-        kk = topk_sorted(m.list, n_el, d.k, m.sorted, ctl);
-        if (nseg == 1 || pass == 1) break;
-        if (tid == 0) ctl->base = (int)atomicAdd(&a.fill[row], (unsigned)kk);
-        consumer_sync();
-        const int base = ctl->base;
+    int kk = topk_sorted(m.list, n_el, d.k, m.sorted, ctl);
+    if (nseg > 1) {
+        // A row with several segments: segment s publishes its ordered candidates in its own part of the row's
+        // scratch (entries [s * k, s * k + count), the count in entry kMergeCap - 1 - s), then draws a ticket; the
+        // CTA that draws the row's last ticket merges.  The planner keeps nseg * (k + 1) within kMergeCap.
+        const int seg = (int)blockIdx.x - first_cta;
         u64* dst = reinterpret_cast<u64*>(a.scratch) + (size_t)row * kMergeCap;
-        if (base + kk <= kMergeCap) {
-            for (int i = tid; i < kk; i += kThreads) dst[base + i] = m.sorted[i];
+        if ((seg + 1) * d.k + nseg <= kMergeCap) {
+            for (int i = tid; i < kk; i += kThreads) dst[seg * d.k + i] = m.sorted[i];
+            if (tid == 0) dst[kMergeCap - 1 - seg] = (u64)kk;
         } else if (tid == 0) {
             atomicOr(a.status, kStatusMergeOverflow);
         }
-        __threadfence();
-        consumer_sync();
-        if (tid == 0) ctl->last = (atomicAdd(&a.ticket[row], 1u) == (unsigned)(nseg - 1)) ? 1 : 0;
+        consumer_sync();   // orders the CTA's stores before the ticket, whose release publishes them to the device
+        if (tid == 0) ctl->last = (ticket_add_acq_rel(&a.ticket[row], 1u) == (unsigned)(nseg - 1)) ? 1 : 0;
         consumer_sync();
         merge_here = ctl->last != 0;
-        if (!merge_here) break;
-        // all segments of the row have published: gather them (L2 reads, never L1)
-        __threadfence();
-        n_el = min((int)__ldcg(&a.fill[row]), kMergeCap);
-        for (int i = tid; i < n_el; i += kThreads) m.list[i] = __ldcg(dst + i);
-        consumer_sync();
-        if (tid == 0) {   // leave the counters ready for the next launch
-            a.fill[row] = 0u;
-            a.ticket[row] = 0u;
+        if (merge_here) {   // all segments of the row have published (L2 reads, never L1)
+            if (tid == 0) a.ticket[row] = 0u;   // ready for the next launch
+            if (nseg <= kNumWarps) {
+                // few ordered lists: the rank of an entry is its place in its own list plus, for every other list,
+                // the number of entries above it (binary search); the lists keep their places in shared memory
+                // (counts and entries are read in one go; entries past a list's count are stale and ignored below)
+                const int span = nseg * d.k;
+                if (tid < nseg) ctl->wcount[tid] = min((int)__ldcg(dst + kMergeCap - 1 - tid), d.k);
+                for (int e = tid; e < span; e += kThreads) m.list[e] = __ldcg(dst + e);
+                consumer_sync();
+                int total = 0;
+                for (int s2 = 0; s2 < nseg; ++s2) total += ctl->wcount[s2];
+                for (int e = tid; e < span; e += kThreads) {
+                    const int s1 = e / d.k, i1 = e - s1 * d.k;
+                    if (i1 >= ctl->wcount[s1]) continue;
+                    const u64 c = m.list[e];
+                    int rank = i1;
+                    for (int s2 = 0; s2 < nseg; ++s2) {
+                        if (s2 == s1) continue;
+                        const u64* run = m.list + s2 * d.k;   // descending: count its entries above c
+                        int lo = 0, hi = ctl->wcount[s2];
+                        while (lo < hi) {
+                            const int mid = (lo + hi) >> 1;
+                            if (run[mid] > c) lo = mid + 1;
+                            else hi = mid;
+                        }
+                        rank += lo;
+                    }
+                    if (rank < d.k) m.sorted[rank] = c;
+                }
+                kk = min(total, d.k);
+                consumer_sync();
+            } else {   // many short lists: gather them into one list and order that
+                int total = 0;
+                for (int s2 = 0; s2 < nseg; ++s2) {
+                    const int n2 = min((int)__ldcg(dst + kMergeCap - 1 - s2), d.k);
+                    for (int i = tid; i < n2; i += kThreads) m.list[total + i] = __ldcg(dst + s2 * d.k + i);
+                    total += n2;
+                }
+                consumer_sync();
+                kk = topk_sorted(m.list, total, d.k, m.sorted, ctl);
+            }
         }
     }
     if (mark) trace_mark(a, 5);
@@ -627,6 +674,8 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
     // happens outside it, so that the loop's state stays in registers.
     const float ninf = -__int_as_float(0x7f800000);
     unsigned* myq = m.queue + tid;   // entry i of this lane's queue is myq[i * kThreads]
+    const unsigned q_base = smem_u32(myq);
+    float* const st_warp = m.stage + warp * kWTile;
     int it = 0;                            // tiles of this CTA looked at so far (the position in the ring)
     for (int tile = t_begin; tile < t_end;) {
         // ---- a new segment starts (all consumer warps are here together: kernel start or after a segment end)
@@ -675,18 +724,17 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
         for (;;) {
             int reason = 0;   // why the loop over the tiles was left: 0 = segment done, 1 = a queue of this warp is nearly full,
                               // 2 = another warp asked for a re-selection while this one was waiting for a copy
-            for (; s < seg_nt; ++s, ++it, col0 += kTile) {
+            unsigned slot = (unsigned)it % kStages, par = ((unsigned)it / kStages) & 1u;   // ring slot of tile `it` and its phase
+            for (; s < seg_nt; ++s, ++it, col0 += kTile, slot = (slot + 1u) % kStages, par ^= (slot == 0u ? 1u : 0u)) {
                 if (__any_sync(0xffffffffu, qn > kLaneQueue - 4)) {
                     reason = 1;
                     break;
                 }
-                const int slot = it % kStages;
-                float* st = m.stage + (size_t)slot * kTile + warp * kWTile;   // this warp's part of the CTA tile
-                const int len = min(kWTile, V - col0);                        // may be <= 0 in a row's last tile
+                float* st = st_warp + slot * kTile;              // this warp's part of the CTA tile
+                const int len = min(kWTile, V - col0);            // may be <= 0 in a row's last tile
                 if (a.bulk_ok) {
                     // ---- wait for the CTA tile's copy.  A warp that has to wait also answers re-selection requests of
                     // other warps: a requester sits at the barrier of cta_event, and the ring only moves when every warp does.
-                    const unsigned par = (unsigned)(it / kStages) & 1u;
                     bool landed = mbar_try_wait(&ctl->full[slot], par);
                     if (!landed) {
                         const long long lim = ctl->abort ? 2000ll : kCopyWaitCycles;
@@ -735,29 +783,28 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
 
                 // ---- the admission bound: set at the segment's first tile (all warps must have posted: one barrier per
                 // segment), then refreshed without a barrier at tiles 1, 2, 4, 8, ... of the segment
-                if (s == 0) {
+                if ((s & (s - 1)) == 0) {   // s = 0, 1, 2, 4, 8, ...
                     const float wb = warp_bound(run_max, row_k);
-                    if (lane == 0) ctl->wbound[warp] = wb;
-                    consumer_sync();
-                    thr_f = min_warp_bounds(ctl);
-                } else if ((s & (s - 1)) == 0) {
-                    thr_f = fmaxf(thr_f, refresh_bound(run_max, row_k, ctl));
+                    if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
+                    if (s == 0) consumer_sync();
+                    else __syncwarp();
+                    thr_f = fmaxf(thr_f, min_warp_bounds(ctl));
                 }
 
                 // ---- note the cells whose maximum reaches the bound (padding past the end of a row never does)
-                bool p0 = m0 >= thr_f, p1 = m1 >= thr_f, p2 = m2 >= thr_f, p3 = m3 >= thr_f;
-                if (thr_comp != 0ull) {   // after a re-selection: ties at the bound are settled by token id
-                    const int id_lane = col0 + 4 * lane + a.vocab_offset;
-                    p0 = p0 && make_comp(m0, id_lane) >= thr_comp;
-                    p1 = p1 && make_comp(m1, id_lane + 128) >= thr_comp;
-                    p2 = p2 && make_comp(m2, id_lane + 256) >= thr_comp;
-                    p3 = p3 && make_comp(m3, id_lane + 384) >= thr_comp;
-                }
                 const unsigned loc = (unsigned)s << 2;
-                if (p0) myq[(qn++) * kThreads] = make_entry(m0, loc);
-                if (p1) myq[(qn++) * kThreads] = make_entry(m1, loc | 1u);
-                if (p2) myq[(qn++) * kThreads] = make_entry(m2, loc | 2u);
-                if (p3) myq[(qn++) * kThreads] = make_entry(m3, loc | 3u);
+                if (thr_comp == 0ull) {
+                    note_cell_if(m0, thr_f, loc, q_base, qn);
+                    note_cell_if(m1, thr_f, loc | 1u, q_base, qn);
+                    note_cell_if(m2, thr_f, loc | 2u, q_base, qn);
+                    note_cell_if(m3, thr_f, loc | 3u, q_base, qn);
+                } else {   // after a re-selection: ties at the bound are settled by token id
+                    const int id_lane = col0 + 4 * lane + a.vocab_offset;
+                    if (m0 >= thr_f && make_comp(m0, id_lane) >= thr_comp) myq[(qn++) * kThreads] = make_entry(m0, loc);
+                    if (m1 >= thr_f && make_comp(m1, id_lane + 128) >= thr_comp) myq[(qn++) * kThreads] = make_entry(m1, loc | 1u);
+                    if (m2 >= thr_f && make_comp(m2, id_lane + 256) >= thr_comp) myq[(qn++) * kThreads] = make_entry(m2, loc | 2u);
+                    if (m3 >= thr_f && make_comp(m3, id_lane + 384) >= thr_comp) myq[(qn++) * kThreads] = make_entry(m3, loc | 3u);
+                }
             }
             if (reason == 0) break;
             // ---- a re-selection: the CTA keeps the k best of the cells noted so far, every queue becomes empty
@@ -945,7 +992,7 @@ extern "C" int fsb_argmax_rows_static(int device, const float* logits_dev, int64
         q = q < 1 ? 1 : (q > kMaxTilesPerCta ? kMaxTilesPerCta : q);
         a.tiles_per_cta = q;
         a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (ld & 3) == 0) ? 1 : 0;
-        if ((a.tiles_per_row + q - 1) / q + 1 > kMergeCap) {
+        if (2 * ((a.tiles_per_row + q - 1) / q + 1) > kMergeCap) {   // one candidate and one count per segment
             rc = FSB_ERR_CAPACITY;   // more segments per row than a row's scratch has entries (one candidate per segment)
         } else if (launch_stream_kernel(a, (a.total_tiles + q - 1) / q, st) != 0) {
             rc = FSB_ERR_CUDA;

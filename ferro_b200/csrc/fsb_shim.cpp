@@ -134,8 +134,8 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
     pl.total_tiles = n_rows * pl.tiles_per_row;
     const int slots = std::max(1, h->sm_count * std::max(1, h->ctas_per_sm));
     int q = (pl.total_tiles + slots - 1) / slots;
-    // a row may gather at most kMergeCap candidates: segments per row <= kMergeCap / kmax
-    const int max_seg = std::max(2, fsb::kMergeCap / std::max(1, kmax));
+    // a row's scratch holds kMergeCap entries, k candidates and a count per segment
+    const int max_seg = std::max(2, fsb::kMergeCap / (std::max(1, kmax) + 1));   // k entries and a count per segment
     const int q_min = (pl.tiles_per_row + (max_seg - 1) - 1) / (max_seg - 1);
     q = std::max(q, q_min);
     q = std::max(1, std::min(q, fsb::kMaxTilesPerCta));
