@@ -147,15 +147,13 @@ struct SharedCtl {
     u64 red[2 * kNumWarps];           // cross-warp reduction scratch
     double dsum;
     alignas(16) float wbound[kNumWarps];   // per-warp admission bounds (see the streaming kernel); read with 16-byte loads
-    int wcount[kNumWarps];            // cells queued by each warp, posted at a rendez-vous
+    int wcount[kNumWarps];            // lengths of a row's ordered candidate lists while they are merged
     int sum[3];                       // rotating counters of the selection steps
     int out_cnt;
     int base, last;
     int imax, imin1, imin2;
     int need_compact;                 // a lane's queue is nearly full: the CTA must re-select
     int abort;                        // a copy did not land in time
-    int fill;                         // cells gathered into the flat list
-    int unfinished;                   // lanes that still hold queued cells during a gather
     u64 ev_bound;                     // composite bound of the latest re-selection (0: nothing was dropped)
     SegCtx seg;
 };

@@ -22,7 +22,7 @@ constexpr int kMaxTilesPerCta = kBitmapSpan / kTile;
 enum : uint32_t {
     kStatusCopyTimeout = 1u,     // a bulk copy did not land within the wait limit
     kStatusCandOverflow = 2u,    // candidate buffer overflow (cannot happen by construction; checked anyway)
-    kStatusMergeOverflow = 4u,   // a row gathered more candidates than kMergeCap
+    kStatusMergeOverflow = 4u,   // a row has more segments than its scratch has room for (the planner prevents it)
     kStatusEmptyRow = 8u,        // a row produced no candidate (all logits NaN)
     kStatusBadTie = 16u          // duplicate candidate keys met in a selection
 };
@@ -55,8 +55,8 @@ struct StreamArgs {
     const float* logits;       // base of the [rows][ld] matrix
     const RowDesc* rows;       // n_rows descriptors (only rows of the candidate path)
     const int32_t* hist;       // packed penalty-window ids
-    uint64_t* scratch;         // [n_rows][kMergeCap] candidates emitted by the segments of each row
-    uint32_t* fill;            // [n_rows] entries used in scratch (self-resetting)
+    uint64_t* scratch;         // [n_rows][kMergeCap]: per segment of a row k ordered candidates, the counts at the end
+    uint32_t* fill;            // [n_rows] (not used by the current kernels)
     uint32_t* ticket;          // [n_rows] segments that have finished (self-resetting)
     int32_t* tokens;           // output tokens, indexed by RowDesc::out_index
     uint32_t* status;          // one word, OR of kStatus* bits

@@ -87,8 +87,10 @@ FSB_API int fsb_set_cuda_stream(fsb_handle* h, void* cuda_stream);
 FSB_API int fsb_set_softcap(fsb_handle* h, float cap);
 
 /* Diagnostics: when set to a device buffer of 8 uint64 per CTA (4096 CTAs at most), the streaming kernel writes
- * time stamps of its phases there: slot 0 the start in %globaltimer ns, slot 7 the start in SM cycles, and in SM
- * cycles 1 copies issued, 2 first tile landed, 3 first bound set, 4 streaming done, 5 candidates published, 6 exit.  NULL (the default) turns it off.  No reference counterpart. */
+ * time stamps of its phases there: slot 0 the CTA's start in %globaltimer ns, slot 7 the start in SM cycles, and in
+ * SM cycles: 1 barriers set up, 4 streaming done and final bound known (last segment), 2 element list built,
+ * 5 candidates ordered and published or merged, 6 exit.  Slot 3 is unused.  NULL (the default) turns it off.
+ * No reference counterpart. */
 FSB_API int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer);
 
 /* Overlap of consecutive launches (off by default).  When on, fsb_batch_launch starts the streaming kernel with

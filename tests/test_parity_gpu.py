@@ -199,3 +199,18 @@ def test_overlapping_launches_give_the_same_tokens(engine, oracle, shape):
                 engine.close_stream(int(s))
     assert np.array_equal(outs[0], outs[1])
     assert np.array_equal(outs[1], ref["tokens"])
+
+
+@pytest.mark.parametrize("case", [(2, 262144, 40), (1, 200000, 1), (3, 150001, 64)])
+def test_rows_cut_into_many_short_segments(engine, oracle, case):
+    """A small batch of long rows is dealt one tile per CTA: a row then has more segments than a CTA has warps, and
+    its candidates are merged through the gather-and-order path instead of the ordered-list path."""
+    B, V, k = case
+    rng = np.random.default_rng(4242 + V)
+    lg = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+    lg[:, ::11] = np.round(lg[:, ::11])
+    p = fb.make_params(B, temperature=0.0 if k == 1 else 0.9, top_k=k, top_p=0.95, repetition_penalty=1.2)
+    p["seed"] = 77 + np.arange(B)
+    hists = [rng.integers(0, V, size=300).astype(np.int32) for _ in range(B)]
+    tok, ref, hard, near, kept_bad = run_batch(engine, oracle, lg, p, hists)
+    assert not hard and not kept_bad, (hard, near, kept_bad)
