@@ -26,6 +26,7 @@ __all__ = ["Engine", "Sampler", "Batch", "SamplerError", "make_params", "PARAMS_
 LOGITS_ON_HOST = 1
 WRITE_BACK = 2
 KEEP_KEPT_SET = 4
+APPEND_SAMPLED = 8
 MAX_CANDIDATE_K = 256
 STATIC_MAX_ROWS = 64   # FSB_STATIC_MAX_ROWS
 STATIC_WAIT = 1        # FSB_STATIC_WAIT
@@ -40,7 +41,8 @@ PARAMS_DTYPE = np.dtype(
 )
 
 API_SYMBOLS = [
-    "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap", "fsb_batch_shard_launch", "fsb_batch_merge_launch", "fsb_argmax_rows_static",
+    "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap", "fsb_batch_shard_launch", "fsb_batch_merge_launch", "fsb_argmax_rows_static", "fsb_stream_history_set", "fsb_stream_history_append", "fsb_stream_history_len",
+    "fsb_sample_batch_resident",
     "fsb_set_trace_buffer",
     "fsb_params_default", "fsb_params_validate", "fsb_stream_open", "fsb_stream_close", "fsb_stream_params",
     "fsb_stream_state_get", "fsb_stream_state_set", "fsb_sample_batch", "fsb_verify_windows", "fsb_last_kept",
@@ -110,6 +112,10 @@ def load_library(build_if_missing: bool = True):
     L.fsb_batch_kernel_count.argtypes = [vp]
     L.fsb_batch_free.argtypes = [vp, vp]
     L.fsb_counters.argtypes = [vp, C.POINTER(_Counters)]
+    L.fsb_stream_history_set.argtypes = [vp, i32, vp, i64]
+    L.fsb_stream_history_append.argtypes = [vp, i32, vp, i32]
+    L.fsb_stream_history_len.argtypes = [vp, i32, C.POINTER(i64)]
+    L.fsb_sample_batch_resident.argtypes = [vp, i32, vp, vp, i64, i32, vp, u32]
     L.fsb_argmax_rows_static.argtypes = [C.c_int, vp, i64, i32, i32, vp, vp, u32]
     for name in API_SYMBOLS:
         if name not in ("fsb_last_error", "fsb_params_default"):
@@ -306,6 +312,35 @@ class Engine:
         self._check(self.lib.fsb_last_kept(self._h, int(row), cap, ids.ctypes.data, pr.ctypes.data, C.byref(n)))
         m = min(n.value, cap)
         return ids[:m], pr[:m], n.value
+
+    # ---- device-resident histories (fsb_stream_history_*, fsb_sample_batch_resident)
+    def history_set(self, stream_id: int, ids):
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        self._check(self.lib.fsb_stream_history_set(self._h, int(stream_id), a.ctypes.data, len(a)))
+
+    def history_append(self, stream_id: int, ids):
+        a = np.ascontiguousarray(np.atleast_1d(ids), dtype=np.int32)
+        self._check(self.lib.fsb_stream_history_append(self._h, int(stream_id), a.ctypes.data, len(a)))
+
+    def history_len(self, stream_id: int) -> int:
+        n = C.c_int64(0)
+        self._check(self.lib.fsb_stream_history_len(self._h, int(stream_id), C.byref(n)))
+        return int(n.value)
+
+    def sample_batch_resident(self, stream_ids, logits, n_vocab: int | None = None, ld: int | None = None, flags: int = 0) -> np.ndarray:
+        """``fsb_sample_batch`` with every row's history taken from its stream's resident history.  `logits` is a
+        host float32 array (FSB_LOGITS_ON_HOST is added) or an int device pointer (then n_vocab is required)."""
+        sids = np.ascontiguousarray(stream_ids, dtype=np.int32)
+        if isinstance(logits, np.ndarray):
+            assert logits.dtype == np.float32 and logits.ndim == 2 and logits.flags.c_contiguous
+            n_vocab = logits.shape[1] if n_vocab is None else n_vocab
+            ld = logits.shape[1] if ld is None else ld
+            ptr, flags = logits.ctypes.data, flags | LOGITS_ON_HOST
+        else:
+            ptr, ld = int(logits), (n_vocab if ld is None else ld)
+        out = np.zeros(len(sids), dtype=np.int32)
+        self._check(self.lib.fsb_sample_batch_resident(self._h, len(sids), sids.ctypes.data, C.c_void_p(ptr), ld, n_vocab, out.ctypes.data, flags))
+        return out
 
     def prepare_batch(self, stream_ids, histories, n_vocab: int, ld: int | None = None, flags: int = 0) -> Batch:
         sids = np.ascontiguousarray(stream_ids, dtype=np.int32)

@@ -46,7 +46,7 @@ struct RowDesc {
     float penalty;
     int32_t flags;
     int32_t out_index;     // position of the row's token in the output array
-    int32_t pad[2];
+    int32_t pad[2];        // resident histories: pool index (64 bits) where the row's token is appended, or -1
 };
 static_assert(sizeof(RowDesc) == 64, "RowDesc layout");
 
@@ -85,6 +85,7 @@ size_t stream_kernel_smem_bytes();
 // Defined in fsb_kernels.cu.  All return a cudaError_t as int (0 = success).
 int prepare_device_kernels(int* ctas_per_sm);
 int launch_stream_kernel(const StreamArgs& a, int grid, void* stream);
+int launch_append_tokens(const RowDesc* rows, int n_rows, const int32_t* tokens, int32_t* pool, void* stream);
 int launch_merge_lists(const void* lists, const int32_t* list_n, int n_lists, int n_rows, const RowDesc* rows, int32_t* tokens,
                        int32_t* kept_ids, double* kept_pr, int32_t* kept_n, uint32_t* status, void* stream);
 

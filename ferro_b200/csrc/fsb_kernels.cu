@@ -151,13 +151,6 @@ __device__ __forceinline__ float min_warp_bounds(SharedCtl* ctl) {
     }
     return m;
 }
-__device__ __forceinline__ float refresh_bound(float run_max, int k, SharedCtl* ctl) {
-    const float wb = warp_bound(run_max, k);
-    if ((threadIdx.x & 31) == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[threadIdx.x >> 5]) = wb;
-    __syncwarp();
-    return min_warp_bounds(ctl);
-}
-
 // Diagnostics: slot 0 takes the global timer (ns) once, the others the SM cycle counter (cheap to read).
 __device__ __forceinline__ void trace_mark(const StreamArgs& a, int slot) {
     if (a.trace && threadIdx.x == 0) {
@@ -893,6 +886,22 @@ int launch_stream_kernel(const StreamArgs& a, int grid, void* stream) {
     cfg.numAttrs = a.overlap ? 1 : 0;
     if (a.softcap != 0.0f) return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<true>, a);
     return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<false>, a);
+}
+
+// Resident histories: appends every row's new token to its stream's history on the device.  A descriptor's pad
+// words hold the index of the id pool where the token goes (negative: nowhere).
+namespace {
+__global__ void append_tokens_kernel(const RowDesc* rows, int n_rows, const int32_t* tokens, int32_t* pool) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    const int64_t at = ((int64_t)rows[r].pad[1] << 32) | (uint32_t)rows[r].pad[0];
+    if (at >= 0) pool[at] = tokens[rows[r].out_index];
+}
+}  // namespace
+
+int launch_append_tokens(const RowDesc* rows, int n_rows, const int32_t* tokens, int32_t* pool, void* stream) {
+    append_tokens_kernel<<<(n_rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(rows, n_rows, tokens, pool);
+    return (int)cudaGetLastError();
 }
 
 int launch_merge_lists(const void* lists, const int32_t* list_n, int n_lists, int n_rows, const RowDesc* rows, int32_t* tokens,

@@ -32,6 +32,12 @@ struct Stream {
     uint64_t seed_used = 0;
     uint64_t draws = 0;
     bool open = false;
+    // device-resident history (optional): a host mirror, and a region [pool_off, pool_off + 2^pool_class) of the
+    // engine's id pool that holds its first dev_len ids
+    std::vector<int32_t> hist;
+    int64_t pool_off = -1;
+    int pool_class = -1;
+    int64_t dev_len = 0;
 };
 
 struct Plan {
@@ -59,6 +65,7 @@ struct fsb_batch {
     std::vector<int> sid;
     std::vector<unsigned char> stochastic;
     bool launched = false;
+    const int32_t* hist_dev = nullptr;   // where the rows' penalty windows live: the batch's staged copy, or the engine's id pool
 
     fsb::RowDesc* h_rows() const { return reinterpret_cast<fsb::RowDesc*>(h_in); }
     int32_t* h_hist() const { return reinterpret_cast<int32_t*>(h_in + sizeof(fsb::RowDesc) * (size_t)cap_rows); }
@@ -94,6 +101,9 @@ struct fsb_handle {
     size_t weights_elems = 0;
     uint64_t* d_trace = nullptr;       // caller-owned diagnostics buffer, or null
     fsb_batch* own = nullptr;          // the batch behind fsb_sample_batch / fsb_verify_windows
+    int32_t* d_pool = nullptr;         // resident histories: max_hist ids, carved into power-of-two regions
+    int64_t pool_top = 0;              // ids handed out so far (bump pointer)
+    std::vector<std::vector<int64_t>> pool_free;   // freed regions by size class
     fsb_counters_t counters{};
     std::string err;
 };
@@ -236,7 +246,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         fsb::StreamArgs a{};
         a.logits = logits_dev;
         a.rows = b->d_rows();
-        a.hist = b->d_hist();
+        a.hist = b->hist_dev ? b->hist_dev : b->d_hist();
         a.scratch = h->d_scratch;
         a.fill = h->d_fill;
         a.ticket = h->d_fill + h->max_rows;
@@ -274,7 +284,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
             FSB_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->d_weights), need * sizeof(uint64_t)));
             h->weights_elems = need;
         }
-        const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, b->d_hist(), h->d_weights, b->d_tokens,
+        const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, b->hist_dev ? b->hist_dev : b->d_hist(), h->d_weights, b->d_tokens,
                                                   keep_kept ? h->d_kept_ids : nullptr, keep_kept ? h->d_kept_pr : nullptr,
                                                   keep_kept ? h->d_kept_n : nullptr, h->d_status, b->n_vocab, h->vocab_offset,
                                                   (b->flags & FSB_WRITE_BACK) ? 1 : 0, h->softcap, h->stream);
@@ -311,6 +321,56 @@ int check_common(fsb_handle* h, int n_rows, int64_t ld, int n_vocab, const fsb_b
     return FSB_OK;
 }
 
+// ---- resident histories: regions of the engine's id pool, sizes 2^class ids (class >= 8) ----------------------
+void release_region(fsb_handle* h, Stream* s) {
+    if (s->pool_off >= 0) {
+        if ((size_t)s->pool_class >= h->pool_free.size()) h->pool_free.resize((size_t)s->pool_class + 1);
+        h->pool_free[(size_t)s->pool_class].push_back(s->pool_off);
+    }
+    s->pool_off = -1;
+    s->pool_class = -1;
+    s->dev_len = 0;
+}
+
+// Makes sure the stream's region holds at least `need` ids; moves what is already on the device if it must grow.
+int ensure_region(fsb_handle* h, Stream* s, int64_t need) {
+    if (s->pool_off >= 0 && need <= ((int64_t)1 << s->pool_class)) return FSB_OK;
+    int c = 8;
+    while (((int64_t)1 << c) < need) ++c;
+    int64_t off = -1;
+    if ((size_t)c < h->pool_free.size() && !h->pool_free[(size_t)c].empty()) {
+        off = h->pool_free[(size_t)c].back();
+        h->pool_free[(size_t)c].pop_back();
+    } else if (h->pool_top + ((int64_t)1 << c) <= h->max_hist) {
+        off = h->pool_top;
+        h->pool_top += (int64_t)1 << c;
+    } else {
+        return fail(h, FSB_ERR_CAPACITY, "resident histories need %lld more ids than the engine's pool of %lld holds", (long long)((int64_t)1 << c),
+                    (long long)h->max_hist);
+    }
+    if (s->pool_off >= 0 && s->dev_len > 0)
+        FSB_CUDA(h, cudaMemcpyAsync(h->d_pool + off, h->d_pool + s->pool_off, sizeof(int32_t) * (size_t)s->dev_len, cudaMemcpyDeviceToDevice, h->stream));
+    const int64_t kept = s->dev_len;
+    release_region(h, s);
+    s->pool_off = off;
+    s->pool_class = c;
+    s->dev_len = kept;
+    return FSB_OK;
+}
+
+// Brings the device copy of the stream's history up to date with its host mirror.
+int sync_history(fsb_handle* h, Stream* s) {
+    const int64_t n = (int64_t)s->hist.size();
+    if (n <= s->dev_len) return FSB_OK;
+    const int rc = ensure_region(h, s, n);
+    if (rc) return rc;
+    FSB_CUDA(h, cudaMemcpyAsync(h->d_pool + s->pool_off + s->dev_len, s->hist.data() + s->dev_len, sizeof(int32_t) * (size_t)(n - s->dev_len),
+                                cudaMemcpyHostToDevice, h->stream));
+    FSB_CUDA(h, cudaStreamSynchronize(h->stream));   // the source is pageable host memory that may change after return
+    s->dev_len = n;
+    return FSB_OK;
+}
+
 // Stages rows "stream_ids[i] samples row i with history i" into batch b.  Consumes engine outputs.
 int stage_rows(fsb_handle* h, fsb_batch* b, int n_rows, const int* stream_ids, int64_t ld, int n_vocab, const int32_t* hist_flat,
                const int64_t* hist_off, unsigned flags) {
@@ -334,6 +394,7 @@ int stage_rows(fsb_handle* h, fsb_batch* b, int n_rows, const int* stream_ids, i
     b->n_vocab = n_vocab;
     b->ld = ld;
     b->flags = flags;
+    b->hist_dev = nullptr;
     b->sid.assign(stream_ids, stream_ids + n_rows);
     b->stochastic.assign((size_t)n_rows, 0);
     std::vector<fsb::RowDesc> descs((size_t)n_rows);
@@ -463,7 +524,8 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
         cudaMallocHost(reinterpret_cast<void**>(&h->h_status), sizeof(uint32_t)) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_ids), sizeof(int32_t) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_pr), sizeof(double) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&h->d_kept_n), sizeof(int32_t) * (size_t)max_rows) != cudaSuccess)
+        cudaMalloc(reinterpret_cast<void**>(&h->d_kept_n), sizeof(int32_t) * (size_t)max_rows) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_pool), sizeof(int32_t) * (size_t)std::max<int64_t>(max_hist_ids, 1)) != cudaSuccess)
         return bail(FSB_ERR_CUDA);
     h->d_status = h->d_fill + 2 * (size_t)max_rows;
     if (alloc_batch(h, max_rows, max_hist_ids, &h->own) != FSB_OK) return bail(FSB_ERR_CUDA);
@@ -485,6 +547,7 @@ int fsb_destroy(fsb_handle* h) {
     if (h->d_kept_ids) cudaFree(h->d_kept_ids);
     if (h->d_kept_pr) cudaFree(h->d_kept_pr);
     if (h->d_kept_n) cudaFree(h->d_kept_n);
+    if (h->d_pool) cudaFree(h->d_pool);
     if (h->d_logits_stage) cudaFree(h->d_logits_stage);
     if (h->d_weights) cudaFree(h->d_weights);
     if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
@@ -556,6 +619,9 @@ int fsb_stream_close(fsb_handle* h, int stream_id) {
     if (!h) return FSB_ERR_INVALID;
     Stream* s = get_stream(h, stream_id);
     if (!s) return fail(h, FSB_ERR_STREAM_ID, "unknown stream id %d", stream_id);
+    release_region(h, s);
+    s->hist.clear();
+    s->hist.shrink_to_fit();
     s->open = false;
     h->free_ids.push_back(stream_id);
     return FSB_OK;
@@ -615,6 +681,112 @@ int fsb_sample_batch(fsb_handle* h, int n_rows, const int* stream_ids, const flo
             const Stream* s = get_stream(h, stream_ids[i]);
             replay_penalty_on_host(const_cast<float*>(logits) + (int64_t)i * ld, n_vocab, s->p, hist_flat + hist_off[i],
                                    hist_off[i + 1] - hist_off[i], h->vocab_offset);
+        }
+    }
+    count_rows(h, b, 0);
+    return FSB_OK;
+}
+
+int fsb_stream_history_set(fsb_handle* h, int stream_id, const int32_t* ids, int64_t n) {
+    if (!h || n < 0 || (n > 0 && !ids)) return FSB_ERR_INVALID;
+    Stream* s = get_stream(h, stream_id);
+    if (!s) return fail(h, FSB_ERR_STREAM_ID, "unknown stream id %d", stream_id);
+    cudaSetDevice(h->device);
+    s->hist.assign(ids, ids + n);
+    s->dev_len = 0;
+    return sync_history(h, s);
+}
+
+int fsb_stream_history_append(fsb_handle* h, int stream_id, const int32_t* ids, int n) {
+    if (!h || n < 0 || (n > 0 && !ids)) return FSB_ERR_INVALID;
+    Stream* s = get_stream(h, stream_id);
+    if (!s) return fail(h, FSB_ERR_STREAM_ID, "unknown stream id %d", stream_id);
+    cudaSetDevice(h->device);
+    s->hist.insert(s->hist.end(), ids, ids + n);
+    return sync_history(h, s);
+}
+
+int fsb_stream_history_len(const fsb_handle* h, int stream_id, int64_t* n) {
+    if (!h || !n) return FSB_ERR_INVALID;
+    Stream* s = get_stream(const_cast<fsb_handle*>(h), stream_id);
+    if (!s) return FSB_ERR_STREAM_ID;
+    *n = (int64_t)s->hist.size();
+    return FSB_OK;
+}
+
+int fsb_sample_batch_resident(fsb_handle* h, int n_rows, const int* stream_ids, const float* logits, int64_t ld, int n_vocab,
+                              int32_t* tokens_out, unsigned flags) {
+    if (!h) return FSB_ERR_INVALID;
+    if (!logits || !tokens_out || !stream_ids) return fail(h, FSB_ERR_INVALID, "null logits, stream_ids or tokens_out");
+    cudaSetDevice(h->device);
+    fsb_batch* b = h->own;
+    int rc = check_common(h, n_rows, ld, n_vocab, b);
+    if (rc) return rc;
+    const bool append = (flags & FSB_APPEND_SAMPLED) != 0;
+    // validate first, without touching any engine: known streams, each at most once, room for the new ids
+    for (int i = 0; i < n_rows; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        if (!s) return fail(h, FSB_ERR_STREAM_ID, "row %d: unknown stream id %d", i, stream_ids[i]);
+        for (int j = 0; j < i; ++j)
+            if (stream_ids[j] == stream_ids[i]) return fail(h, FSB_ERR_INVALID, "stream %d appears twice in one resident batch", stream_ids[i]);
+    }
+    for (int i = 0; i < n_rows; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        rc = sync_history(h, s);
+        if (rc == FSB_OK && append) rc = ensure_region(h, s, (int64_t)s->hist.size() + 1);
+        if (rc) return rc;
+    }
+    b->n_rows = n_rows;
+    b->n_vocab = n_vocab;
+    b->ld = ld;
+    b->flags = flags & ~FSB_APPEND_SAMPLED;
+    b->hist_dev = h->d_pool;
+    b->hist_ids = 0;
+    b->sid.assign(stream_ids, stream_ids + n_rows);
+    b->stochastic.assign((size_t)n_rows, 0);
+    std::vector<fsb::RowDesc> descs((size_t)n_rows);
+    for (int i = 0; i < n_rows; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        const int64_t len = (int64_t)s->hist.size();
+        const int64_t wb = window_begin(s->p, len), wl = len - wb;
+        uint64_t word = 0;
+        if (!is_greedy(s->p)) {
+            word = s->rng();
+            s->draws++;
+            b->stochastic[(size_t)i] = 1;
+        }
+        fill_desc(descs[(size_t)i], s->p, n_vocab, (int64_t)i * ld, wl > 0 ? s->pool_off + wb : 0, wl, word, i);
+        const int64_t at = append ? s->pool_off + len : -1;
+        descs[(size_t)i].pad[0] = (int32_t)(uint32_t)(at & 0xFFFFFFFFll);
+        descs[(size_t)i].pad[1] = (int32_t)(at >> 32);
+    }
+    rc = finalize_batch(h, b, descs);
+    if (rc) return rc;
+    const bool on_host = (flags & FSB_LOGITS_ON_HOST) != 0;
+    if (on_host) b->flags &= ~FSB_WRITE_BACK;
+    rc = upload_batch(h, b);
+    if (rc) return rc;
+    const float* dev = logits;
+    if (on_host) {
+        rc = stage_host_logits(h, logits, n_rows, ld, n_vocab, &dev);
+        if (rc) return rc;
+    }
+    rc = launch_batch(h, b, dev, (flags & FSB_KEEP_KEPT_SET) != 0);
+    if (rc) return rc;
+    if (append) {
+        const int e = fsb::launch_append_tokens(b->d_rows(), n_rows, b->d_tokens, h->d_pool, h->stream);
+        if (e != 0) return fail(h, FSB_ERR_CUDA, "append kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+        h->counters.kernel_launches++;
+    }
+    rc = fetch_tokens(h, b, tokens_out);
+    if (rc) return rc;
+    for (int i = 0; i < n_rows; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        if (on_host && (flags & FSB_WRITE_BACK))
+            replay_penalty_on_host(const_cast<float*>(logits) + (int64_t)i * ld, n_vocab, s->p, s->hist.data(), (int64_t)s->hist.size(), h->vocab_offset);
+        if (append) {   // the device copy already holds the token
+            s->hist.push_back(tokens_out[i]);
+            s->dev_len = (int64_t)s->hist.size();
         }
     }
     count_rows(h, b, 0);

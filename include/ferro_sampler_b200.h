@@ -62,7 +62,8 @@ enum {
     FSB_LOGITS_ON_HOST = 1u, /* `logits` is a host pointer (staged to the device inside the call); default: device pointer */
     FSB_WRITE_BACK = 2u,     /* store the penalised logits back into the caller's rows, the reference's in-place side
                                 effect ("logits: [n_vocab], modified in place", src/sampler.h:26) */
-    FSB_KEEP_KEPT_SET = 4u   /* record every row's kept set (ids + probabilities) for fsb_last_kept */
+    FSB_KEEP_KEPT_SET = 4u,  /* record every row's kept set (ids + probabilities) for fsb_last_kept */
+    FSB_APPEND_SAMPLED = 8u  /* fsb_sample_batch_resident only: append every row's token to its stream's resident history */
 };
 
 /* Largest effective k (after the reference's clamp k = (0 < top_k < n_vocab) ? top_k : n_vocab) that
@@ -131,6 +132,23 @@ FSB_API int fsb_stream_state_set(fsb_handle* h, int stream_id, uint64_t seed, ui
  * in tokens_out (host) on return.  The history is not modified (the caller appends, src/server.cpp:342). */
 FSB_API int fsb_sample_batch(fsb_handle* h, int n_rows, const int* stream_ids, const float* logits, int64_t ld, int n_vocab,
                      const int32_t* hist_flat, const int64_t* hist_off, int32_t* tokens_out, unsigned flags);
+
+/* Device-resident histories.  The reference's scheduler keeps one growing token history per request and hands the
+ * whole of it to every sample() call (src/server.cpp:605 with g.hist, appended by gen_token at :342).  With these
+ * calls a stream keeps its history in the engine (a host mirror and a device copy in a pool of max_hist_ids ids,
+ * regions of power-of-two size), so that a decode step moves one token id per stream instead of the whole window.
+ *   fsb_stream_history_set     replaces the stream's history (the prompt, at request start);
+ *   fsb_stream_history_append  adds ids (tokens produced elsewhere: accepted drafts, a forced token);
+ *   fsb_sample_batch_resident  is fsb_sample_batch with history_i = the resident history of stream_ids[i]; with
+ *                              FSB_APPEND_SAMPLED every sampled token is appended to its stream's history (on the
+ *                              device by a small kernel, in the mirror after the read-back), which is what
+ *                              gen_token does next anyway.  A stream may appear once per call.
+ * Closing a stream frees its region.  FSB_ERR_CAPACITY when the pool cannot hold a region. */
+FSB_API int fsb_stream_history_set(fsb_handle* h, int stream_id, const int32_t* ids, int64_t n);
+FSB_API int fsb_stream_history_append(fsb_handle* h, int stream_id, const int32_t* ids, int n);
+FSB_API int fsb_stream_history_len(const fsb_handle* h, int stream_id, int64_t* n);
+FSB_API int fsb_sample_batch_resident(fsb_handle* h, int n_rows, const int* stream_ids, const float* logits, int64_t ld, int n_vocab,
+                                      int32_t* tokens_out, unsigned flags);
 
 /* Speculative verification windows (the accept loop of src/server.cpp:626-645) for n_streams streams.
  * Stream i owns rows row_off[i] .. row_off[i+1]) of `logits`; rows_flat holds, per stream, [last token, draft_1 ..
