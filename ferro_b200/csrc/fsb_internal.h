@@ -14,7 +14,7 @@ constexpr int kFlatCells = 960;               // cells (float4 + token id) gathe
 constexpr int kCellBytes = 20;
 constexpr int kMergeCap = kFlatCells * kCellBytes / 8;   // 2400: candidates one row may gather from all its segments
                                                           // (the gathered cells' memory seen as a list of composites)
-constexpr int kBitmapSpan = 131072;           // columns one penalty bitmap covers (one segment never spans more)
+constexpr int kBitmapSpan = 262144;           // columns one penalty bitmap covers (one segment never spans more)
 constexpr int kBitmapWords = kBitmapSpan / 32;
 constexpr int kMaxTilesPerCta = kBitmapSpan / kTile;
 

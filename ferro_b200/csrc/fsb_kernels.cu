@@ -30,7 +30,7 @@ static_assert(kMergeCap >= 4 * kMaxK, "the logits of kMaxK surviving cells must 
 static_assert(kMergeCap >= 2 * kMaxK, "the epilogue's arrays live in the list's memory");
 static_assert(kSmemKept >= (size_t)kMaxK * sizeof(u64), "the ordered candidates live in the survivors' memory");
 static_assert(kWTile == 512, "a lane owns four float4 of a warp tile");
-static_assert(kMaxTilesPerCta <= 64, "a location is one byte: the tile number above two bits");
+static_assert(kMaxTilesPerCta <= 32, "a location is seven bits: the tile number above two bits (bit 7 is free)");
 static_assert(kFlatCells >= kThreads, "a capped gather round takes at least one cell per thread");
 static_assert(kLaneQueue % 4 == 0 && kLaneQueue >= 8, "lanes look at four cells per tile");
 

@@ -149,12 +149,18 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
     const int q_min = (pl.tiles_per_row + (max_seg - 1) - 1) / (max_seg - 1);
     q = std::max(q, q_min);
     q = std::max(1, std::min(q, fsb::kMaxTilesPerCta));
-    // a CTA whose range holds a row boundary pays the end-of-segment work twice: prefer the next q that divides the
-    // row (or is a multiple of it) when that costs at most a quarter more tiles per CTA
-    for (int c = q; c <= std::min(fsb::kMaxTilesPerCta, q + q / 4 + 1); ++c) {
-        if (pl.tiles_per_row % c == 0 || c % pl.tiles_per_row == 0) {
-            q = c;
-            break;
+    if (pl.tiles_per_row <= fsb::kMaxTilesPerCta && n_rows >= 2 * slots) {
+        // plenty of rows: one CTA per row.  Every CTA pays its start and its end-of-segment work once per row
+        // instead of once per piece, and no row has to be merged.
+        q = pl.tiles_per_row;
+    } else {
+        // a CTA whose range holds a row boundary pays the end-of-segment work twice: prefer the next q that divides
+        // the row (or is a multiple of it) when that costs at most a quarter more tiles per CTA
+        for (int c = q; c <= std::min(fsb::kMaxTilesPerCta, q + q / 4 + 1); ++c) {
+            if (pl.tiles_per_row % c == 0 || c % pl.tiles_per_row == 0) {
+                q = c;
+                break;
+            }
         }
     }
     pl.tiles_per_cta = q;
