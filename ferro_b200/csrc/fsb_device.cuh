@@ -105,6 +105,24 @@ __device__ __forceinline__ float4 ldg_stream(const float4* p) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Thread-block clusters (pairs of CTAs that share a row): rank in the cluster, the address of a shared-memory
+// location in another CTA of the cluster, stores to it, and the cluster's barrier (arrive releases this thread's
+// stores to the cluster, wait acquires the others').
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned cluster_map_shared(unsigned local_addr, unsigned rank) {
+    unsigned a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void cluster_store_u64(unsigned addr, u64 v) { asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory"); }
+__device__ __forceinline__ void cluster_store_u32(unsigned addr, unsigned v) { asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 // Ticket counter shared by the CTAs of a row: the add releases this thread's earlier writes - and those of the
 // CTA's other threads that a barrier ordered before it - to the whole device, and acquires what earlier ticket
 // holders released.
@@ -155,6 +173,7 @@ struct SharedCtl {
     int need_compact;                 // a lane's queue is nearly full: the CTA must re-select
     int abort;                        // a copy did not land in time
     u64 ev_bound;                     // composite bound of the latest re-selection (0: nothing was dropped)
+    int recv_n;                       // paired CTAs: candidates the other CTA of the pair has put into the receive buffer
     SegCtx seg;
 };
 

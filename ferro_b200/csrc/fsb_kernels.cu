@@ -23,7 +23,8 @@ constexpr size_t kSmemQueue = (size_t)kLaneQueue * kThreads * sizeof(unsigned); 
 constexpr size_t kSmemCells = (size_t)kFlatCells * kCellBytes;                     // gathered cells; a list of composites otherwise
 constexpr size_t kSmemKept = (size_t)kMaxK * kCellBytes;                           // cells that survived a re-selection; selection scratch
 constexpr size_t kSmemBitmap = (size_t)kBitmapWords * sizeof(unsigned);
-constexpr size_t kSmemTotal = kSmemStage + kSmemQueue + kSmemCells + kSmemKept + kSmemBitmap + sizeof(SharedCtl);
+constexpr size_t kSmemRecv = (size_t)kMaxK * sizeof(u64);   // paired CTAs: the other CTA's ordered candidates arrive here
+constexpr size_t kSmemTotal = kSmemStage + kSmemQueue + kSmemCells + kSmemKept + kSmemBitmap + kSmemRecv + sizeof(SharedCtl);
 static_assert(kSmemTotal <= 227 * 1024, "one CTA per SM");
 static_assert(kSmemCells >= (size_t)kMergeCap * sizeof(u64), "the element list lives in the gathered cells' memory");
 static_assert(kMergeCap >= 4 * kMaxK, "the logits of kMaxK surviving cells must fit into the element list");
@@ -61,6 +62,7 @@ struct Smem {
     u64* list;          // = cells
     u64* sorted;        // = kcells
     unsigned* bitmap;
+    u64* recv;          // [kMaxK] receive buffer of a paired CTA
     SharedCtl* ctl;
 };
 __device__ __forceinline__ Smem smem_view() {
@@ -80,7 +82,9 @@ __device__ __forceinline__ Smem smem_view() {
     m.sorted = reinterpret_cast<u64*>(p);
     p += kSmemKept;
     m.bitmap = reinterpret_cast<unsigned*>(p);
-    m.ctl = reinterpret_cast<SharedCtl*>(p + kSmemBitmap);
+    p += kSmemBitmap;
+    m.recv = reinterpret_cast<u64*>(p);
+    m.ctl = reinterpret_cast<SharedCtl*>(p + kSmemRecv);
     return m;
 }
 
@@ -561,7 +565,42 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
     const int nseg = last_cta - first_cta + 1;
     bool merge_here = true;
     int kk = topk_sorted(m.list, n_el, d.k, m.sorted, ctl);
-    if (nseg > 1) {
+    if (a.pair) {
+        // The row's two CTAs are a cluster: CTA 1 puts its ordered candidates into CTA 0's receive buffer, both
+        // arrive at the cluster's barrier (the only phase of it in this kernel: the producer warps arrived when they
+        // finished), and CTA 0 merges.  No global memory, no ticket.
+        const unsigned rank = cluster_cta_rank();
+        if (rank != 0u) {
+            const unsigned remote = cluster_map_shared(smem_u32(m.recv), 0u);
+            for (int i = tid; i < kk; i += kThreads) cluster_store_u64(remote + 8u * (unsigned)i, m.sorted[i]);
+            if (tid == 0) cluster_store_u32(cluster_map_shared(smem_u32(&ctl->recv_n), 0u), (unsigned)kk);
+        }
+        __syncwarp();
+        cluster_arrive_release();
+        merge_here = rank == 0u;
+        if (merge_here) {
+            cluster_wait_acquire();
+            const int n1 = min(*reinterpret_cast<volatile int*>(&ctl->recv_n), d.k);
+            // rank of an entry: its place in its own list plus the number of entries of the other list above it
+            for (int e = tid; e < kk + n1; e += kThreads) {
+                const bool mine = e < kk;
+                const int i1 = mine ? e : e - kk;
+                const u64 c = mine ? m.sorted[i1] : m.recv[i1];
+                const u64* run = mine ? m.recv : m.sorted;
+                int lo = 0, hi = mine ? n1 : kk;
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (run[mid] > c) lo = mid + 1;
+                    else hi = mid;
+                }
+                if (i1 + lo < d.k) m.list[i1 + lo] = c;
+            }
+            consumer_sync();
+            kk = min(kk + n1, d.k);
+            for (int i = tid; i < kk; i += kThreads) m.sorted[i] = m.list[i];
+            consumer_sync();
+        }
+    } else if (nseg > 1) {
         // A row with several segments: segment s publishes its ordered candidates in its own part of the row's
         // scratch (entries [s * k, s * k + count), the count in entry kMergeCap - 1 - s), then draws a ticket; the
         // CTA that draws the row's last ticket merges.  The planner keeps nseg * (k + 1) within kMergeCap.
@@ -658,6 +697,8 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
     __syncthreads();   // the only barrier the producer warp takes part in
     if (warp == kWarps) {
         if (a.bulk_ok) producer_loop(a, m.stage, ctl, t_begin, nt);
+        __syncwarp();
+        if (a.pair) cluster_arrive_release();   // every thread of the pair arrives exactly once (see segment_end)
         return;
     }
     trace_mark(a, 1);
@@ -874,16 +915,27 @@ int prepare_device_kernels(int* ctas_per_sm) {
 }
 
 int launch_stream_kernel(const StreamArgs& a, int grid, void* stream) {
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (a.overlap) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (a.pair) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 2;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kBlockThreads);
     cfg.dynamicSmemBytes = kSmemTotal;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cfg.attrs = attr;
-    cfg.numAttrs = a.overlap ? 1 : 0;
+    cfg.numAttrs = n;
     if (a.softcap != 0.0f) return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<true>, a);
     return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<false>, a);
 }

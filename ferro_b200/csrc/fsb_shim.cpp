@@ -84,6 +84,7 @@ struct fsb_handle {
     float softcap = 0.0f;
     int32_t vocab_offset = 0;
     int launch_overlap = 0;
+    int pair_ok = 1;                   // clusters of two CTAs can be launched on this device
     std::vector<Stream> streams;
     std::vector<int> free_ids;
     // device scratch shared by all batches of this handle
@@ -276,6 +277,8 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.softcap = h->softcap;
         a.overlap = h->launch_overlap;
         const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
+        // rows of exactly two aligned segments: the two CTAs of a row run as a cluster and exchange candidates on chip
+        a.pair = (h->pair_ok && a.tiles_per_row == 2 * a.tiles_per_cta && grid == 2 * a.n_rows) ? 1 : 0;
         const int e = fsb::launch_stream_kernel(a, grid, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         h->counters.kernel_launches++;
