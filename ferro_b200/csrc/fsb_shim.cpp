@@ -141,26 +141,35 @@ int64_t window_begin(const ferro_sampler_params& p, int64_t len) {
 
 Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
     Plan pl;
-    pl.tiles_per_row = (n_vocab + fsb::kTile - 1) / fsb::kTile;
-    pl.total_tiles = n_rows * pl.tiles_per_row;
+    const int T = (n_vocab + fsb::kTile - 1) / fsb::kTile;
+    pl.tiles_per_row = T;
+    pl.total_tiles = n_rows * T;
     const int slots = std::max(1, h->sm_count * std::max(1, h->ctas_per_sm));
-    int q = (pl.total_tiles + slots - 1) / slots;
-    // a row's scratch holds kMergeCap entries, k candidates and a count per segment
-    const int max_seg = std::max(2, fsb::kMergeCap / (std::max(1, kmax) + 1));   // k entries and a count per segment
-    const int q_min = (pl.tiles_per_row + (max_seg - 1) - 1) / (max_seg - 1);
-    q = std::max(q, q_min);
-    q = std::max(1, std::min(q, fsb::kMaxTilesPerCta));
-    if (pl.tiles_per_row <= fsb::kMaxTilesPerCta && n_rows >= 2 * slots) {
+    // a row's scratch holds kMergeCap entries: k candidates and a count per segment
+    const int max_seg = std::max(2, fsb::kMergeCap / (std::max(1, kmax) + 1));
+    const int q_min = (T + (max_seg - 1) - 1) / (max_seg - 1);
+    const int q_fill = (pl.total_tiles + slots - 1) / slots;   // fewest tiles per CTA that still give a single wave
+    int q = std::max(1, std::min(std::max(q_fill, q_min), fsb::kMaxTilesPerCta));
+    if (T <= fsb::kMaxTilesPerCta && n_rows >= 2 * slots) {
         // plenty of rows: one CTA per row.  Every CTA pays its start and its end-of-segment work once per row
         // instead of once per piece, and no row has to be merged.
-        q = pl.tiles_per_row;
+        q = T;
     } else {
-        // a CTA whose range holds a row boundary pays the end-of-segment work twice: prefer the next q that divides
-        // the row (or is a multiple of it) when that costs at most a quarter more tiles per CTA
-        for (int c = q; c <= std::min(fsb::kMaxTilesPerCta, q + q / 4 + 1); ++c) {
-            if (pl.tiles_per_row % c == 0 || c % pl.tiles_per_row == 0) {
+        // Otherwise a row is cut into nseg = T / q aligned pieces.  Fewer tiles per CTA shorten the streaming (per 32 KiB
+        // tile about 0.25 us on a lone SM, 0.6 us when every SM streams), more pieces lengthen the merge: nothing for one
+        // piece, the on-chip exchange of a CTA pair for two, ordered lists merged by binary search up to 16, a
+        // gather-and-select beyond (measured on B200, in us).  Pick the cheapest q that divides the row and keeps
+        // the grid within one wave.
+        double best = 1e30;
+        for (int c = q; c <= std::min(T, fsb::kMaxTilesPerCta); ++c) {
+            if (T % c != 0) continue;
+            const int nseg = T / c;
+            const double busy = std::min(1.0, (double)n_rows * nseg / slots);
+            const double merge = nseg == 1 ? 0.0 : nseg == 2 ? 1.4 : nseg <= 8 ? 2.4 + 0.25 * nseg : nseg <= 16 ? 4.4 + 0.5 * nseg : 10.0 + 0.3 * nseg;
+            const double cost = (0.25 + 0.35 * busy) * c + merge;
+            if (cost < best) {
+                best = cost;
                 q = c;
-                break;
             }
         }
     }
