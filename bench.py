@@ -182,6 +182,97 @@ def run_reference_arm(args, rank):
     print(json.dumps(out), flush=True)
 
 
+def _time_launches(torch, launch, n):
+    """Microseconds per call of `launch(i)` over n back-to-back calls, CUDA events on the current stream."""
+    for i in range(3):
+        launch(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        launch(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return 1e3 * e0.elapsed_time(e1) / n
+
+
+def side_figures(torch, dist, fb, eng, device, rank, world, sids, hists, bufs, barrier):
+    """Figures that explain the headline but are not it.  All device-timed, launch overlap off."""
+    from ferro_b200 import sharded
+    out = {}
+    eng.set_launch_overlap(False)
+    # the whole public call with device-resident logits, as a server makes it every step: stage descriptors and the
+    # 512-id windows (one host-to-device copy), launch, read the tokens back, synchronise; and the same with the
+    # histories resident on the device (only descriptors go up)
+    for resident in (False, True):
+        if resident:
+            for s_, hh_ in zip(sids, hists):
+                eng.history_set(int(s_), hh_)
+        call = (lambda i: eng.sample_batch_resident(sids, bufs[i % len(bufs)].data_ptr(), n_vocab=VOCAB)) if resident else \
+               (lambda i: eng.sample_batch(sids, bufs[i % len(bufs)], hists, n_vocab=VOCAB))
+        for i in range(3):
+            call(i)
+        t0 = time.perf_counter()
+        n_call = 100
+        for i in range(n_call):
+            call(i)
+        out["device_logits_call_us_resident_histories" if resident else "device_logits_call_us"] = 1e6 * (time.perf_counter() - t0) / n_call
+    out["staging_h2d_bytes"] = ROWS * 64 + ROWS * HIST * 4
+    # warm: the same 67 MB buffer every launch (mostly L2-resident)
+    batch = eng.prepare_batch(sids, hists, VOCAB)
+    out["warm_launch_us"] = _time_launches(torch, lambda i: batch.launch(bufs[0].data_ptr()), 100)
+    batch.free()
+    # other shapes through the same kernel (seeded normal logits; the value distribution does not matter for time)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(99 + rank)
+    rng = np.random.default_rng(5)
+    for name, rows, vocab, k, hl, temp in (("cfg5_512x262144_k40", 512, 262144, 40, 1024, 0.8), ("cfg4_136x65536_greedy", 136, 65536, 1, 0, 0.0),
+                                           ("cfg2_like_8x65536_k50", 8, 65536, 50, 256, 0.8)):
+        big = [torch.randn(rows, vocab, device=device, generator=gen) * 3.0 for _ in range(2 if rows * vocab > 5e7 else 8)]
+        p = fb.make_params(rows, temperature=temp, top_k=max(k, 1), top_p=0.9, repetition_penalty=1.1 if hl else 1.0)
+        p["seed"] = 99 + np.arange(rows)
+        hh = [rng.integers(0, vocab, size=hl).astype(np.int32) for _ in range(rows)]
+        e2 = fb.Engine(device=device.index, max_rows=rows, max_vocab=vocab, max_hist_ids=rows * max(hl, 1) + 16)
+        e2.set_cuda_stream(torch.cuda.current_stream().cuda_stream)
+        s2 = e2.open_streams(p)
+        b2 = e2.prepare_batch(s2, hh, vocab)
+        us = _time_launches(torch, lambda i: b2.launch(big[i % len(big)].data_ptr()), 40)
+        out[name] = {"launch_us": us, "logits_gb_s": rows * vocab * 4 / us / 1e3, "rows_per_s": rows / us * 1e6}
+        b2.free()
+        e2.close()
+        del big
+    if world > 1:
+        # the serving batch split by vocabulary: every rank holds V / world columns of all 512 rows, selects its
+        # candidates, one NCCL all-gather, merge on every rank (ferro_b200.sharded.VocabShardedSampler)
+        rows, vocab = 512, 262144
+        lo, hi = sharded.vocab_partition(vocab, world)[rank]
+        shard = [torch.randn(rows, hi - lo, device=device, generator=gen) * 3.0 for _ in range(2)]
+        p = fb.make_params(rows, temperature=0.8, top_k=40, top_p=0.9, repetition_penalty=1.1)
+        p["seed"] = 99 + np.arange(rows)                       # the same streams on every rank
+        hh = [np.random.default_rng(1000 + r).integers(0, vocab, size=1024).astype(np.int32) for r in range(rows)]
+        e3 = fb.Engine(device=device.index, max_rows=rows, max_vocab=hi - lo, max_hist_ids=rows * 1024 + 16)
+        e3.set_cuda_stream(torch.cuda.current_stream().cuda_stream)
+        e3.set_vocab_offset(lo)
+        s3 = e3.open_streams(p)
+        b3 = e3.prepare_batch(s3, hh, hi - lo)
+        lists = torch.zeros((rows, sharded.MAX_K), dtype=torch.int64, device=device)
+        counts = torch.zeros((rows,), dtype=torch.int32, device=device)
+
+        def step(i):
+            b3.shard_launch(shard[i % 2].data_ptr(), lists.data_ptr(), counts.data_ptr())
+            al, ac = sharded.gather_candidate_lists(lists, counts)
+            b3.merge_launch(al.data_ptr(), ac.data_ptr(), world)
+        barrier()
+        us = _time_launches(torch, step, 30)
+        t = torch.tensor([us], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out["cfg5_vocab_sharded"] = {"step_us": float(t.item()), "rows_per_s": rows / float(t.item()) * 1e6, "columns_per_gpu": hi - lo,
+                                     "exchange": "NCCL all-gather of 512 x 256 x 8 B + 512 x 4 B per rank"}
+        b3.free()
+        e3.close()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -189,6 +280,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the side figures (staging, warm launch, other shapes, vocabulary sharding)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -294,6 +386,12 @@ def main():
     h2d = ROWS * VOCAB * 4 + ROWS * 64 + ROWS * HIST * 4
     d2h = ROWS * 4 + 4
 
+    # ---- side figures, outside the headline: staging cost, a warm (L2-resident) launch, two other shapes, and with
+    # several GPUs the vocabulary-sharded variant of the serving batch.  Skipped with --no-extras.
+    extras = None
+    if not args.no_extras:
+        extras = side_figures(torch, dist, fb, eng, device, rank, world, sids, hists, bufs, barrier)
+
     # ---- parity of the last timed batch (outside the timed region; rank 0)
     parity = None
     if rank == 0:
@@ -329,6 +427,8 @@ def main():
             "clocks": clock_rec,
             "parity_mismatches_last_batch": parity,
         }
+        if extras is not None:
+            out["extras"] = extras
         if world == 1 and not args.no_cpu_baseline:
             val, single, threads, kind, sample = cpu_reference_rows_per_s(seconds_budget=10.0)
             out["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample, "single_thread_value": single}
