@@ -390,7 +390,10 @@ def main():
     # several GPUs the vocabulary-sharded variant of the serving batch.  Skipped with --no-extras.
     extras = None
     if not args.no_extras:
-        extras = side_figures(torch, dist, fb, eng, device, rank, world, sids, hists, bufs, barrier)
+        try:
+            extras = side_figures(torch, dist, fb, eng, device, rank, world, sids, hists, bufs, barrier)
+        except Exception as ex:   # side figures must never cost the headline line
+            extras = {"error": f"{type(ex).__name__}: {ex}"}
 
     # ---- parity of the last timed batch (outside the timed region; rank 0)
     parity = None
