@@ -201,75 +201,89 @@ def side_figures(torch, dist, fb, eng, device, rank, world, sids, hists, bufs, b
     from ferro_b200 import sharded
     out = {}
     eng.set_launch_overlap(False)
-    # the whole public call with device-resident logits, as a server makes it every step: stage descriptors and the
-    # 512-id windows (one host-to-device copy), launch, read the tokens back, synchronise; and the same with the
-    # histories resident on the device (only descriptors go up)
-    for resident in (False, True):
-        if resident:
-            for s_, hh_ in zip(sids, hists):
-                eng.history_set(int(s_), hh_)
-        call = (lambda i: eng.sample_batch_resident(sids, bufs[i % len(bufs)].data_ptr(), n_vocab=VOCAB)) if resident else \
-               (lambda i: eng.sample_batch(sids, bufs[i % len(bufs)], hists, n_vocab=VOCAB))
-        for i in range(3):
-            call(i)
-        t0 = time.perf_counter()
-        n_call = 100
-        for i in range(n_call):
-            call(i)
-        out["device_logits_call_us_resident_histories" if resident else "device_logits_call_us"] = 1e6 * (time.perf_counter() - t0) / n_call
-    out["staging_h2d_bytes"] = ROWS * 64 + ROWS * HIST * 4
-    # warm: the same 67 MB buffer every launch (mostly L2-resident)
-    batch = eng.prepare_batch(sids, hists, VOCAB)
-    out["warm_launch_us"] = _time_launches(torch, lambda i: batch.launch(bufs[0].data_ptr()), 100)
-    batch.free()
-    # other shapes through the same kernel (seeded normal logits; the value distribution does not matter for time)
     gen = torch.Generator(device=device)
     gen.manual_seed(99 + rank)
-    rng = np.random.default_rng(5)
-    for name, rows, vocab, k, hl, temp in (("cfg5_512x262144_k40", 512, 262144, 40, 1024, 0.8), ("cfg4_136x65536_greedy", 136, 65536, 1, 0, 0.0),
-                                           ("cfg2_like_8x65536_k50", 8, 65536, 50, 256, 0.8)):
-        big = [torch.randn(rows, vocab, device=device, generator=gen) * 3.0 for _ in range(2 if rows * vocab > 5e7 else 8)]
-        p = fb.make_params(rows, temperature=temp, top_k=max(k, 1), top_p=0.9, repetition_penalty=1.1 if hl else 1.0)
-        p["seed"] = 99 + np.arange(rows)
-        hh = [rng.integers(0, vocab, size=hl).astype(np.int32) for _ in range(rows)]
-        e2 = fb.Engine(device=device.index, max_rows=rows, max_vocab=vocab, max_hist_ids=rows * max(hl, 1) + 16)
-        e2.set_cuda_stream(torch.cuda.current_stream().cuda_stream)
-        s2 = e2.open_streams(p)
-        b2 = e2.prepare_batch(s2, hh, vocab)
-        us = _time_launches(torch, lambda i: b2.launch(big[i % len(big)].data_ptr()), 40)
-        out[name] = {"launch_us": us, "logits_gb_s": rows * vocab * 4 / us / 1e3, "rows_per_s": rows / us * 1e6}
-        b2.free()
-        e2.close()
-        del big
+    try:   # nothing in here is collective: a rank that fails still reaches the collective part below
+        # the whole public call with device-resident logits, as a server makes it every step: stage descriptors and the
+        # 512-id windows (one host-to-device copy), launch, read the tokens back, synchronise; and the same with the
+        # histories resident on the device (only descriptors go up)
+        for resident in (False, True):
+            if resident:
+                for s_, hh_ in zip(sids, hists):
+                    eng.history_set(int(s_), hh_)
+            call = (lambda i: eng.sample_batch_resident(sids, bufs[i % len(bufs)].data_ptr(), n_vocab=VOCAB)) if resident else \
+                   (lambda i: eng.sample_batch(sids, bufs[i % len(bufs)], hists, n_vocab=VOCAB))
+            for i in range(3):
+                call(i)
+            t0 = time.perf_counter()
+            n_call = 100
+            for i in range(n_call):
+                call(i)
+            out["device_logits_call_us_resident_histories" if resident else "device_logits_call_us"] = 1e6 * (time.perf_counter() - t0) / n_call
+        out["staging_h2d_bytes"] = ROWS * 64 + ROWS * HIST * 4
+        # warm: the same 67 MB buffer every launch (mostly L2-resident)
+        batch = eng.prepare_batch(sids, hists, VOCAB)
+        out["warm_launch_us"] = _time_launches(torch, lambda i: batch.launch(bufs[0].data_ptr()), 100)
+        batch.free()
+        # other shapes through the same kernel (seeded normal logits; the value distribution does not matter for time)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(99 + rank)
+        rng = np.random.default_rng(5)
+        for name, rows, vocab, k, hl, temp in (("cfg5_512x262144_k40", 512, 262144, 40, 1024, 0.8), ("cfg4_136x65536_greedy", 136, 65536, 1, 0, 0.0),
+                                               ("cfg2_like_8x65536_k50", 8, 65536, 50, 256, 0.8)):
+            big = [torch.randn(rows, vocab, device=device, generator=gen) * 3.0 for _ in range(2 if rows * vocab > 5e7 else 8)]
+            p = fb.make_params(rows, temperature=temp, top_k=max(k, 1), top_p=0.9, repetition_penalty=1.1 if hl else 1.0)
+            p["seed"] = 99 + np.arange(rows)
+            hh = [rng.integers(0, vocab, size=hl).astype(np.int32) for _ in range(rows)]
+            e2 = fb.Engine(device=device.index, max_rows=rows, max_vocab=vocab, max_hist_ids=rows * max(hl, 1) + 16)
+            e2.set_cuda_stream(torch.cuda.current_stream().cuda_stream)
+            s2 = e2.open_streams(p)
+            b2 = e2.prepare_batch(s2, hh, vocab)
+            us = _time_launches(torch, lambda i: b2.launch(big[i % len(big)].data_ptr()), 40)
+            out[name] = {"launch_us": us, "logits_gb_s": rows * vocab * 4 / us / 1e3, "rows_per_s": rows / us * 1e6}
+            b2.free()
+            e2.close()
+            del big
+    except Exception as ex:
+        out["error"] = f"{type(ex).__name__}: {ex}"
     if world > 1:
+        # (every rank reaches this point: the figures above involve no collective and are guarded per rank)
         # the serving batch split by vocabulary: every rank holds V / world columns of all 512 rows, selects its
         # candidates, one NCCL all-gather, merge on every rank (ferro_b200.sharded.VocabShardedSampler)
         rows, vocab = 512, 262144
         lo, hi = sharded.vocab_partition(vocab, world)[rank]
-        shard = [torch.randn(rows, hi - lo, device=device, generator=gen) * 3.0 for _ in range(2)]
-        p = fb.make_params(rows, temperature=0.8, top_k=40, top_p=0.9, repetition_penalty=1.1)
-        p["seed"] = 99 + np.arange(rows)                       # the same streams on every rank
-        hh = [np.random.default_rng(1000 + r).integers(0, vocab, size=1024).astype(np.int32) for r in range(rows)]
-        e3 = fb.Engine(device=device.index, max_rows=rows, max_vocab=hi - lo, max_hist_ids=rows * 1024 + 16)
-        e3.set_cuda_stream(torch.cuda.current_stream().cuda_stream)
-        e3.set_vocab_offset(lo)
-        s3 = e3.open_streams(p)
-        b3 = e3.prepare_batch(s3, hh, hi - lo)
-        lists = torch.zeros((rows, sharded.MAX_K), dtype=torch.int64, device=device)
-        counts = torch.zeros((rows,), dtype=torch.int32, device=device)
-
-        def step(i):
-            b3.shard_launch(shard[i % 2].data_ptr(), lists.data_ptr(), counts.data_ptr())
-            al, ac = sharded.gather_candidate_lists(lists, counts)
-            b3.merge_launch(al.data_ptr(), ac.data_ptr(), world)
-        barrier()
-        us = _time_launches(torch, step, 30)
-        t = torch.tensor([us], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        out["cfg5_vocab_sharded"] = {"step_us": float(t.item()), "rows_per_s": rows / float(t.item()) * 1e6, "columns_per_gpu": hi - lo,
-                                     "exchange": "NCCL all-gather of 512 x 256 x 8 B + 512 x 4 B per rank"}
-        b3.free()
-        e3.close()
+        ready, e3, b3 = 1, None, None
+        try:
+            shard = [torch.randn(rows, hi - lo, device=device, generator=gen) * 3.0 for _ in range(2)]
+            p = fb.make_params(rows, temperature=0.8, top_k=40, top_p=0.9, repetition_penalty=1.1)
+            p["seed"] = 99 + np.arange(rows)                       # the same streams on every rank
+            hh = [np.random.default_rng(1000 + r).integers(0, vocab, size=1024).astype(np.int32) for r in range(rows)]
+            e3 = fb.Engine(device=device.index, max_rows=rows, max_vocab=hi - lo, max_hist_ids=rows * 1024 + 16)
+            e3.set_cuda_stream(torch.cuda.current_stream().cuda_stream)
+            e3.set_vocab_offset(lo)
+            s3 = e3.open_streams(p)
+            b3 = e3.prepare_batch(s3, hh, hi - lo)
+            lists = torch.zeros((rows, sharded.MAX_K), dtype=torch.int64, device=device)
+            counts = torch.zeros((rows,), dtype=torch.int32, device=device)
+        except Exception:
+            ready = 0
+        flag = torch.tensor([ready], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)            # every rank takes part in the collectives below, or none
+        if int(flag.item()) == 1:
+            def step(i):
+                b3.shard_launch(shard[i % 2].data_ptr(), lists.data_ptr(), counts.data_ptr())
+                al, ac = sharded.gather_candidate_lists(lists, counts)
+                b3.merge_launch(al.data_ptr(), ac.data_ptr(), world)
+            barrier()
+            us = _time_launches(torch, step, 30)
+            t = torch.tensor([us], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            out["cfg5_vocab_sharded"] = {"step_us": float(t.item()), "rows_per_s": rows / float(t.item()) * 1e6, "columns_per_gpu": hi - lo,
+                                         "exchange": "NCCL all-gather of 512 x 256 x 8 B + 512 x 4 B per rank"}
+        if b3 is not None:
+            b3.free()
+        if e3 is not None:
+            e3.close()
     return out
 
 
@@ -313,7 +327,7 @@ def main():
     n_buf = 8   # 8 x 67 MB = 537 MB, more than four times the 126 MB L2: every step streams from HBM
     bufs = [device_logits(torch, gen, device) for _ in range(n_buf)]
     params, hists = make_params(rank), make_histories(rank)
-    eng = fb.Engine(device=local_rank, max_rows=ROWS, max_vocab=VOCAB, max_hist_ids=ROWS * HIST + 16)
+    eng = fb.Engine(device=local_rank, max_rows=ROWS, max_vocab=VOCAB, max_hist_ids=2 * ROWS * HIST + 16)
     eng.set_cuda_stream(torch.cuda.current_stream().cuda_stream)
     sids = eng.open_streams(params)
     batch = eng.prepare_batch(sids, hists, VOCAB)
