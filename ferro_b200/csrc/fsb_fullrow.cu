@@ -7,6 +7,10 @@
 //   2. if k < n: the k-th candidate by a counting radix descent over the candidate keys      (:27-31)
 //   3. weights e_i = exp((double)(x_i - max) / T) of the candidates, kept as 2^-62 fixed point      (:40)
 //   4. min-p bound, top-p crossing and the draw by radix descents over accumulated weight     (:43-49)
+// Before the descents of step 4 the kernel tries a shortcut: the elements that weigh at least 2^-10 of the row's
+// total are, in candidate order, a prefix of the sorted row; at most kHeavyCap of them are gathered, sorted and
+// summed exactly, and the top-p crossing, the kept set and the draw are looked up in that prefix.  A descent over
+// the whole row is only run when a target lies beyond the prefix (flat rows).  Both ways give the same answer.
 // Sums of weights are accumulated as integers, so they do not depend on the order in which threads add: the
 // result is deterministic and differs from the reference's sequential fp64 sums by rounding only (~1e-13).
 #include <cuda_runtime.h>
@@ -53,6 +57,17 @@ struct FullShared {
     u64 res_pfx;
     U128 res_above;
     int res_found;
+    int heavy_cnt;        // elements gathered into the heavy prefix
+    int hit[2];           // results of look-ups in the prefix
+};
+
+constexpr int kHeavyCap = 1024;   // one element per thread
+// Heavy prefix of a row in shared memory: gathered composites, the same in order, and their cumulative weights.
+struct Heavy {
+    u64* raw;      // [kHeavyCap] as gathered; reused for the sorted runs
+    u64* sorted;   // [kHeavyCap] descending
+    u64* cum_lo;   // [kHeavyCap] inclusive cumulative weight, low and high words
+    u64* cum_hi;
 };
 
 struct FullArgs {
@@ -76,12 +91,12 @@ struct RowView {
     const float* row;
     const unsigned* bitmap;   // null: no penalty
     float pen, cap;
-    __device__ __forceinline__ float at(int i) const {
-        float x = row[i];
+    __device__ __forceinline__ float fix(float x, int i) const {   // a loaded logit as the sampler sees it
         if (cap != 0.0f) x = __fmul_rn(cap, tanhf(__fdiv_rn(x, cap)));
         if (bitmap && ((bitmap[i >> 5] >> (i & 31)) & 1u)) x = x > 0.0f ? __fdiv_rn(x, pen) : __fmul_rn(x, pen);
         return x;
     }
+    __device__ __forceinline__ float at(int i) const { return fix(row[i], i); }
 };
 
 __device__ __forceinline__ u64 block_max_u64(u64 v, FullShared* sh) {
@@ -204,6 +219,24 @@ __device__ bool weight_descent(const RowView& rv, int n, int id_base, const u64*
     return found;
 }
 
+
+// Index of the first entry of the heavy prefix whose cumulative weight reaches `target`, or -1 if even the whole
+// prefix weighs less.  All threads of the CTA must call; `slot` is 0 or 1.
+__device__ int heavy_first_reaching(const Heavy& hv, int m, U128 target, FullShared* sh, int slot) {
+    const int t = threadIdx.x;
+    if (t == 0) sh->hit[slot] = -1;
+    __syncthreads();
+    if (t < m) {
+        const bool here = u128_ge(U128{hv.cum_hi[t], hv.cum_lo[t]}, target);
+        const bool before = t > 0 && u128_ge(U128{hv.cum_hi[t - 1], hv.cum_lo[t - 1]}, target);
+        if (here && !before) sh->hit[slot] = t;
+    }
+    __syncthreads();
+    const int r = sh->hit[slot];
+    __syncthreads();
+    return r;
+}
+
 __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     FullShared* sh = reinterpret_cast<FullShared*>(smem_raw);
@@ -211,6 +244,11 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
     const int tid = threadIdx.x;
     const RowDesc d = a.rows[blockIdx.x];
     const int n = a.n_vocab;
+    Heavy hv;
+    hv.raw = reinterpret_cast<u64*>(smem_raw + sizeof(FullShared) + ((sizeof(unsigned) * (size_t)((n + 31) / 32) + 15) & ~(size_t)15));
+    hv.sorted = hv.raw + kHeavyCap;
+    hv.cum_lo = hv.sorted + kHeavyCap;
+    hv.cum_hi = hv.cum_lo + kHeavyCap;
     const int id_base = a.vocab_offset;
     const float* row = a.logits + d.logits_off;
 
@@ -263,6 +301,7 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
     // ---- 3. weights of the candidates, their sum
     u64* wts = a.weights + (size_t)blockIdx.x * (size_t)n;
     U128 part{0ull, 0ull};
+    unsigned cand_part = 0u;
     const double inv_t = (double)d.temperature;
     for (int i = tid; i < n; i += kFullThreads) {
         const float x = rf.at(i);
@@ -270,6 +309,7 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
         if (x == x && make_comp(x, i + id_base) >= c_k) {
             const double e = exp(__ddiv_rn((double)__fsub_rn(x, mx), inv_t));
             wgt = __double2ull_rn(__dmul_rn(e, 4611686018427387904.0));   // 2^62
+            ++cand_part;
         }
         wts[i] = wgt;
         const u64 lo = part.lo + wgt;
@@ -281,17 +321,83 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
     if (tid < 256) {
         sh->h_lo[tid] = 0ull;
         sh->h_hi[tid] = 0ull;
+        sh->h_cnt[tid] = 0u;
     }
+    if (tid == 0) sh->heavy_cnt = 0;
     __syncthreads();
     {
         const u64 old = atomicAdd(&sh->h_lo[0], part.lo);
         if (old + part.lo < old) atomicAdd(&sh->h_hi[0], 1ull);
         if (part.hi) atomicAdd(&sh->h_hi[0], part.hi);
+        if (cand_part) atomicAdd(&sh->h_cnt[0], cand_part);
     }
     __syncthreads();
     const U128 S{sh->h_hi[0], sh->h_lo[0]};
+    const int n_cand = (int)sh->h_cnt[0];
     __syncthreads();
     const double sum = __dmul_rn(u128_to_double(S), 2.168404344971008868014905601739883422851562500e-19);   // * 2^-62
+
+    // ---- 3b. the heavy prefix: every candidate that weighs at least 2^-10 of the total (there are at most 1024 of
+    // them, and in candidate order they come before every lighter one), in order, with exact cumulative weights
+    int m = 0;   // length of the prefix; 0 = no shortcut (too many heavy elements cannot happen, none can: flat rows)
+    if ((S.hi >> 10) == 0ull) {
+        u64 thr_w = (S.hi << 54) | (S.lo >> 10);
+        if (thr_w == 0ull) thr_w = 1ull;
+        for (int i = tid; i < n; i += kFullThreads) {
+            const u64 wgt = wts[i];
+            if (wgt >= thr_w) {
+                const int pos = atomicAdd(&sh->heavy_cnt, 1);
+                if (pos < kHeavyCap) hv.raw[pos] = make_comp(rf.at(i), i + id_base);
+            }
+        }
+        __syncthreads();
+        m = sh->heavy_cnt <= kHeavyCap ? sh->heavy_cnt : 0;
+        __syncthreads();
+    }
+    if (m > 0) {
+        // order them: every warp sorts a run of 32 in registers, then each entry counts, by binary search, the
+        // entries of the other runs above it
+        const int lane = tid & 31, warp = tid >> 5, runs = (m + 31) >> 5;
+        u64 c = 0ull;
+        if (warp < runs) {
+            u64 v[1];
+            v[0] = tid < m ? hv.raw[tid] : 0ull;
+            warp_sort_desc<1>(v);
+            c = v[0];
+            hv.raw[tid] = c;
+        }
+        __syncthreads();
+        if (c != 0ull) {
+            int rank = lane;
+            for (int r2 = 0; r2 < runs; ++r2) {
+                if (r2 == warp) continue;
+                const u64* run = hv.raw + 32 * r2;
+                int lo = 0;
+#pragma unroll
+                for (int step = 16; step > 0; step >>= 1)
+                    if (run[lo + step - 1] > c) lo += step;
+                if (run[lo] > c) ++lo;
+                rank += lo;
+            }
+            hv.sorted[rank] = c;
+        }
+        __syncthreads();
+        // weights from the values (the same formula as above), then one thread adds them up exactly
+        if (tid < m) {
+            const double e = exp(__ddiv_rn((double)__fsub_rn(comp_value(hv.sorted[tid]), mx), inv_t));
+            hv.cum_lo[tid] = __double2ull_rn(__dmul_rn(e, 4611686018427387904.0));
+        }
+        __syncthreads();
+        if (tid == 0) {
+            U128 run{0ull, 0ull};
+            for (int i = 0; i < m; ++i) {
+                run = u128_add(run, U128{0ull, hv.cum_lo[i]});
+                hv.cum_lo[i] = run.lo;
+                hv.cum_hi[i] = run.hi;
+            }
+        }
+        __syncthreads();
+    }
 
     // ---- 4a. min-p: the last candidate whose probability is not below pr[0] * min_p   (pr[0] = 1 / sum)
     u64 c_keep = c_k;
@@ -314,12 +420,25 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
     if (d.top_p < 1.0f) {
         const U128 target = double_to_u128_ceil(__dmul_rn(__dmul_rn((double)d.top_p, sum), 4611686018427387904.0));
         u64 c_p;
-        if (weight_descent(rf, n, id_base, wts, c_k, target, cmax, cmin, sh, &c_p, &dummy)) c_keep = max(c_keep, c_p);
+        const int ip = m > 0 ? heavy_first_reaching(hv, m, target, sh, 0) : -1;
+        if (ip >= 0) c_keep = max(c_keep, hv.sorted[ip]);
+        else if (weight_descent(rf, n, id_base, wts, c_k, target, cmax, cmin, sh, &c_p, &dummy)) c_keep = max(c_keep, c_p);
     }
     // ---- 4c. total weight and size of the kept set
+    // (known without a pass when the kept set is the whole candidate set, or ends inside the heavy prefix)
+    int keep_idx = -1;   // index of c_keep in the prefix, if it lies there
+    if (m > 0 && c_keep >= hv.sorted[m - 1]) {
+        if (tid == 0) sh->hit[1] = -1;
+        __syncthreads();
+        if (tid < m && hv.sorted[tid] == c_keep) sh->hit[1] = tid;
+        __syncthreads();
+        keep_idx = sh->hit[1];
+        __syncthreads();
+    }
+    const bool keep_all = c_keep == c_k;
     U128 kept_w{0ull, 0ull};
     unsigned kept_cnt = 0u;
-    for (int i = tid; i < n; i += kFullThreads) {
+    for (int i = tid; i < ((keep_all || keep_idx >= 0) ? 0 : n); i += kFullThreads) {
         const float x = rf.at(i);
         if (x == x && make_comp(x, i + id_base) >= c_keep) {
             const u64 lo = kept_w.lo + wts[i];
@@ -341,15 +460,17 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
         atomicAdd(&sh->h_cnt[0], kept_cnt);
     }
     __syncthreads();
-    const U128 KW{sh->h_hi[0], sh->h_lo[0]};
-    const int n_keep = (int)sh->h_cnt[0];
+    const U128 KW = keep_idx >= 0 ? U128{hv.cum_hi[keep_idx], hv.cum_lo[keep_idx]} : keep_all ? S : U128{sh->h_hi[0], sh->h_lo[0]};
+    const int n_keep = keep_idx >= 0 ? keep_idx + 1 : keep_all ? n_cand : (int)sh->h_cnt[0];
     __syncthreads();
     // ---- 4d. the draw: first kept candidate whose cumulative weight reaches u * (kept weight)
     double u = __dmul_rn(__ull2double_rn(d.rng_word), 5.42101086242752217003726400434970855712890625e-20);   // 2^-64
     if (u >= 1.0) u = __longlong_as_double(0x3FEFFFFFFFFFFFFFll);
     const U128 target = double_to_u128_ceil(__dmul_rn(u, u128_to_double(KW)));
     u64 c_tok;
-    if (!weight_descent(rf, n, id_base, wts, c_keep, target, cmax, cmin, sh, &c_tok, &dummy) || c_tok < c_keep) c_tok = c_keep;
+    const int it = m > 0 ? heavy_first_reaching(hv, m, target, sh, 0) : -1;
+    if (it >= 0) c_tok = max(hv.sorted[it], c_keep);
+    else if (!weight_descent(rf, n, id_base, wts, c_keep, target, cmax, cmin, sh, &c_tok, &dummy) || c_tok < c_keep) c_tok = c_keep;
     if (tid == 0) {
         a.tokens[out] = comp_id(c_tok);
         if (a.kept_n) {
@@ -362,7 +483,10 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
 
 }  // namespace
 
-size_t full_row_smem_bytes(int n_vocab) { return sizeof(FullShared) + sizeof(unsigned) * (size_t)((n_vocab + 31) / 32); }
+size_t full_row_smem_bytes(int n_vocab) {
+    const size_t bitmap = (sizeof(unsigned) * (size_t)((n_vocab + 31) / 32) + 15) & ~(size_t)15;
+    return sizeof(FullShared) + bitmap + 4 * sizeof(u64) * (size_t)kHeavyCap;
+}
 
 int prepare_full_row_kernel(int max_vocab) {
     return (int)cudaFuncSetAttribute(full_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)full_row_smem_bytes(max_vocab));
