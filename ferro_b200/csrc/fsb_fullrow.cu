@@ -48,10 +48,12 @@ __device__ __forceinline__ U128 double_to_u128_ceil(double d) {
     return r;
 }
 
+constexpr int kHistCopies = 16;  // the level histogram is kept in several copies (one per lane group): fewer threads
+                                 // hit the same shared-memory word at once; the copies are added up before the walk
 struct FullShared {
-    u64 h_lo[256];        // weight histogram of one radix level, low words
-    u64 h_hi[256];        // high words
-    unsigned h_cnt[256];  // element counts per digit
+    u64 h_lo[kHistCopies * 256];        // weight histogram of one radix level, low words (copy c at [c * 256])
+    u64 h_hi[kHistCopies * 256];        // high words
+    unsigned h_cnt[kHistCopies * 256];  // element counts per digit
     u64 red[2 * kFullWarps];
     float redf[kFullWarps];
     u64 res_pfx;
@@ -119,12 +121,13 @@ struct HistAcc {
     unsigned c;
     __device__ __forceinline__ void flush(FullShared* sh) {
         if (d < 0 || c == 0u) return;
-        atomicAdd(&sh->h_cnt[d], c);
+        const int b = (int)(threadIdx.x & (kHistCopies - 1)) * 256 + d;
+        atomicAdd(&sh->h_cnt[b], c);
         if (w.lo) {
-            const u64 old = atomicAdd(&sh->h_lo[d], w.lo);
-            if (old + w.lo < old) atomicAdd(&sh->h_hi[d], 1ull);
+            const u64 old = atomicAdd(&sh->h_lo[b], w.lo);
+            if (old + w.lo < old) atomicAdd(&sh->h_hi[b], 1ull);
         }
-        if (w.hi) atomicAdd(&sh->h_hi[d], w.hi);
+        if (w.hi) atomicAdd(&sh->h_hi[b], w.hi);
         c = 0u;
         w = U128{0ull, 0ull};
     }
@@ -173,10 +176,10 @@ __device__ bool weight_descent(const RowView& rv, int n, int id_base, const u64*
     while (hb >= 0 && found) {
         const int w = hb + 1 < 8 ? hb + 1 : 8, lo = hb + 1 - w;
         const unsigned dmask = (1u << w) - 1u;
-        if (tid < 256) {
-            sh->h_lo[tid] = 0ull;
-            sh->h_hi[tid] = 0ull;
-            sh->h_cnt[tid] = 0u;
+        for (int i = tid; i < kHistCopies * 256; i += kFullThreads) {
+            sh->h_lo[i] = 0ull;
+            sh->h_hi[i] = 0ull;
+            sh->h_cnt[i] = 0u;
         }
         __syncthreads();
         HistAcc acc{-1, U128{0ull, 0ull}, 0u};
@@ -187,6 +190,19 @@ __device__ bool weight_descent(const RowView& rv, int n, int id_base, const u64*
             if (c >= floor_c && (c & mask) == pfx) acc.add((int)((unsigned)(c >> lo) & dmask), weights ? weights[i] : 1ull, sh);
         }
         acc.flush(sh);
+        __syncthreads();
+        if (tid < 256) {   // add the copies up into copy 0
+            U128 t{sh->h_hi[tid], sh->h_lo[tid]};
+            unsigned cn = sh->h_cnt[tid];
+#pragma unroll
+            for (int c = 1; c < kHistCopies; ++c) {
+                t = u128_add(t, U128{sh->h_hi[c * 256 + tid], sh->h_lo[c * 256 + tid]});
+                cn += sh->h_cnt[c * 256 + tid];
+            }
+            sh->h_lo[tid] = t.lo;
+            sh->h_hi[tid] = t.hi;
+            sh->h_cnt[tid] = cn;
+        }
         __syncthreads();
         if (tid == 0) {   // walk the digits from the top until the accumulated weight reaches the target
             U128 run = above;
