@@ -71,6 +71,8 @@ struct fsb_batch {
     int32_t* h_hist() const { return reinterpret_cast<int32_t*>(h_in + sizeof(fsb::RowDesc) * (size_t)cap_rows); }
     fsb::RowDesc* d_rows() const { return reinterpret_cast<fsb::RowDesc*>(d_in); }
     int32_t* d_hist() const { return reinterpret_cast<int32_t*>(d_in + sizeof(fsb::RowDesc) * (size_t)cap_rows); }
+    // the kernels' status word sits right behind the tokens, so that one copy brings both back
+    uint32_t* d_status() const { return reinterpret_cast<uint32_t*>(d_tokens + cap_rows); }
     size_t in_bytes_used() const { return sizeof(fsb::RowDesc) * (size_t)cap_rows + sizeof(int32_t) * (size_t)hist_ids; }
 };
 
@@ -194,9 +196,10 @@ int alloc_batch(fsb_handle* h, int cap_rows, int64_t cap_hist, fsb_batch** out) 
     b->cap_hist = std::max<int64_t>(cap_hist, 1);
     const size_t in_bytes = sizeof(fsb::RowDesc) * (size_t)cap_rows + sizeof(int32_t) * (size_t)b->cap_hist;
     cudaError_t e = cudaMallocHost(reinterpret_cast<void**>(&b->h_in), in_bytes);
-    if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&b->h_tokens), sizeof(int32_t) * (size_t)cap_rows);
+    if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&b->h_tokens), sizeof(int32_t) * ((size_t)cap_rows + 1));
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->d_in), in_bytes);
-    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->d_tokens), sizeof(int32_t) * (size_t)cap_rows);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->d_tokens), sizeof(int32_t) * ((size_t)cap_rows + 1));
+    if (e == cudaSuccess) e = cudaMemset(b->d_tokens, 0, sizeof(int32_t) * ((size_t)cap_rows + 1));
     if (e != cudaSuccess) {
         free_batch_buffers(b);
         delete b;
@@ -267,7 +270,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.fill = h->d_fill;
         a.ticket = h->d_fill + h->max_rows;
         a.tokens = b->d_tokens;
-        a.status = h->d_status;
+        a.status = b->d_status();
         a.kept_ids = keep_kept ? h->d_kept_ids : nullptr;
         a.kept_pr = keep_kept ? h->d_kept_pr : nullptr;
         a.kept_n = keep_kept ? h->d_kept_n : nullptr;
@@ -304,7 +307,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         }
         const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, b->hist_dev ? b->hist_dev : b->d_hist(), h->d_weights, b->d_tokens,
                                                   keep_kept ? h->d_kept_ids : nullptr, keep_kept ? h->d_kept_pr : nullptr,
-                                                  keep_kept ? h->d_kept_n : nullptr, h->d_status, b->n_vocab, h->vocab_offset,
+                                                  keep_kept ? h->d_kept_n : nullptr, b->d_status(), b->n_vocab, h->vocab_offset,
                                                   (b->flags & FSB_WRITE_BACK) ? 1 : 0, h->softcap, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "full-row kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         h->counters.kernel_launches++;
@@ -315,13 +318,14 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
 }
 
 int fetch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out) {
-    FSB_CUDA(h, cudaMemcpyAsync(b->h_tokens, b->d_tokens, sizeof(int32_t) * (size_t)b->n_rows, cudaMemcpyDeviceToHost, h->stream));
-    FSB_CUDA(h, cudaMemcpyAsync(h->h_status, h->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, h->stream));
+    // tokens and the status word behind them in one copy (the gap between n_rows and cap_rows is small)
+    FSB_CUDA(h, cudaMemcpyAsync(b->h_tokens, b->d_tokens, sizeof(int32_t) * ((size_t)b->cap_rows + 1), cudaMemcpyDeviceToHost, h->stream));
     FSB_CUDA(h, cudaStreamSynchronize(h->stream));
-    if (*h->h_status != 0u) {
-        const unsigned st = *h->h_status;
+    const unsigned st = (unsigned)b->h_tokens[b->cap_rows];
+    if (st != 0u) {
         // put the self-resetting counters and the status word back into their idle state
         cudaMemsetAsync(h->d_fill, 0, sizeof(uint32_t) * (2 * (size_t)h->max_rows + 1), h->stream);
+        cudaMemsetAsync(b->d_status(), 0, sizeof(uint32_t), h->stream);
         cudaStreamSynchronize(h->stream);
         return fail(h, FSB_ERR_DEVICE, "kernel status 0x%x (1 copy timeout, 2 candidate overflow, 4 merge overflow, 8 empty row, 16 tie)", st);
     }
@@ -1004,7 +1008,7 @@ int fsb_batch_merge_launch(fsb_handle* h, fsb_batch* b, const uint64_t* lists_de
     cudaSetDevice(h->device);
     const bool keep_kept = (b->flags & FSB_KEEP_KEPT_SET) != 0;
     const int e = fsb::launch_merge_lists(lists_dev, counts_dev, n_lists, b->n_cand, b->d_rows(), b->d_tokens, keep_kept ? h->d_kept_ids : nullptr,
-                                          keep_kept ? h->d_kept_pr : nullptr, keep_kept ? h->d_kept_n : nullptr, h->d_status, h->stream);
+                                          keep_kept ? h->d_kept_pr : nullptr, keep_kept ? h->d_kept_n : nullptr, b->d_status(), h->stream);
     if (e != 0) return fail(h, FSB_ERR_CUDA, "merge kernel launch: %s", cudaGetErrorString((cudaError_t)e));
     h->counters.kernel_launches++;
     b->launched = true;
