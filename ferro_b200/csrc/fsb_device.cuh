@@ -173,7 +173,7 @@ struct SharedCtl {
     int need_compact;                 // a lane's queue is nearly full: the CTA must re-select
     int abort;                        // a copy did not land in time
     u64 ev_bound;                     // composite bound of the latest re-selection (0: nothing was dropped)
-    int recv_n;                       // paired CTAs: candidates the other CTA of the pair has put into the receive buffer
+    int recv_n[8];                    // clustered CTAs: candidates CTA r of the row's cluster has put into part r - 1 of the receive buffer (entry r)
     SegCtx seg;
 };
 

@@ -23,7 +23,9 @@ constexpr size_t kSmemQueue = (size_t)kLaneQueue * kThreads * sizeof(unsigned); 
 constexpr size_t kSmemCells = (size_t)kFlatCells * kCellBytes;                     // gathered cells; a list of composites otherwise
 constexpr size_t kSmemKept = (size_t)kMaxK * kCellBytes;                           // cells that survived a re-selection; selection scratch
 constexpr size_t kSmemBitmap = (size_t)kBitmapWords * sizeof(unsigned);
-constexpr size_t kSmemRecv = (size_t)kMaxK * sizeof(u64);   // paired CTAs: the other CTA's ordered candidates arrive here
+constexpr int kRecvCap = 512;                                // clustered CTAs: the other CTAs' ordered candidates arrive here,
+constexpr size_t kSmemRecv = (size_t)kRecvCap * sizeof(u64);   // (cluster size - 1) parts of k entries
+static_assert(kRecvCap >= kMaxK, "a pair can always exchange");
 constexpr size_t kSmemTotal = kSmemStage + kSmemQueue + kSmemCells + kSmemKept + kSmemBitmap + kSmemRecv + sizeof(SharedCtl);
 static_assert(kSmemTotal <= 227 * 1024, "one CTA per SM");
 static_assert(kSmemCells >= (size_t)kMergeCap * sizeof(u64), "the element list lives in the gathered cells' memory");
@@ -62,7 +64,7 @@ struct Smem {
     u64* list;          // = cells
     u64* sorted;        // = kcells
     unsigned* bitmap;
-    u64* recv;          // [kMaxK] receive buffer of a paired CTA
+    u64* recv;          // [kRecvCap] receive buffer of the first CTA of a cluster
     SharedCtl* ctl;
 };
 __device__ __forceinline__ Smem smem_view() {
@@ -566,37 +568,66 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
     bool merge_here = true;
     int kk = topk_sorted(m.list, n_el, d.k, m.sorted, ctl);
     if (a.pair) {
-        // The row's two CTAs are a cluster: CTA 1 puts its ordered candidates into CTA 0's receive buffer, both
-        // arrive at the cluster's barrier (the only phase of it in this kernel: the producer warps arrived when they
-        // finished), and CTA 0 merges.  No global memory, no ticket.
+        // The row's CTAs are a cluster: CTA r > 0 puts its ordered candidates into part r - 1 of CTA 0's receive
+        // buffer, all arrive at the cluster's barrier (the only phase of it in this kernel: the producer warps arrived
+        // when they finished), and CTA 0 merges.  No global memory, no ticket.
         const unsigned rank = cluster_cta_rank();
         if (rank != 0u) {
-            const unsigned remote = cluster_map_shared(smem_u32(m.recv), 0u);
+            const unsigned remote = cluster_map_shared(smem_u32(m.recv + (rank - 1u) * (unsigned)d.k), 0u);
             for (int i = tid; i < kk; i += kThreads) cluster_store_u64(remote + 8u * (unsigned)i, m.sorted[i]);
-            if (tid == 0) cluster_store_u32(cluster_map_shared(smem_u32(&ctl->recv_n), 0u), (unsigned)kk);
+            if (tid == 0) cluster_store_u32(cluster_map_shared(smem_u32(&ctl->recv_n[rank]), 0u), (unsigned)kk);
         }
         __syncwarp();
         cluster_arrive_release();
         merge_here = rank == 0u;
         if (merge_here) {
             cluster_wait_acquire();
-            const int n1 = min(*reinterpret_cast<volatile int*>(&ctl->recv_n), d.k);
-            // rank of an entry: its place in its own list plus the number of entries of the other list above it
-            for (int e = tid; e < kk + n1; e += kThreads) {
-                const bool mine = e < kk;
-                const int i1 = mine ? e : e - kk;
-                const u64 c = mine ? m.sorted[i1] : m.recv[i1];
-                const u64* run = mine ? m.recv : m.sorted;
-                int lo = 0, hi = mine ? n1 : kk;
-                while (lo < hi) {
-                    const int mid = (lo + hi) >> 1;
-                    if (run[mid] > c) lo = mid + 1;
-                    else hi = mid;
+            if (a.pair == 2) {
+                // two lists: the rank of an entry is its place in its own list plus the number of entries of the other above it
+                const int n1 = min(*reinterpret_cast<volatile int*>(&ctl->recv_n[1]), d.k);
+                for (int e = tid; e < kk + n1; e += kThreads) {
+                    const bool mine = e < kk;
+                    const int i1 = mine ? e : e - kk;
+                    const u64 c = mine ? m.sorted[i1] : m.recv[i1];
+                    const u64* run = mine ? m.recv : m.sorted;
+                    int lo = 0, hi = mine ? n1 : kk;
+                    while (lo < hi) {
+                        const int mid = (lo + hi) >> 1;
+                        if (run[mid] > c) lo = mid + 1;
+                        else hi = mid;
+                    }
+                    if (i1 + lo < d.k) m.list[i1 + lo] = c;
                 }
-                if (i1 + lo < d.k) m.list[i1 + lo] = c;
+                consumer_sync();
+                kk = min(kk + n1, d.k);
+            } else {
+                // several lists: the same, summed over all the other lists
+                const int nl = a.pair;
+                if (tid == 0) ctl->recv_n[0] = kk;
+                consumer_sync();
+                int total = 0;
+                for (int s2 = 0; s2 < nl; ++s2) total += min(*reinterpret_cast<volatile int*>(&ctl->recv_n[s2]), d.k);
+                for (int e = tid; e < nl * d.k; e += kThreads) {
+                    const int s1 = e / d.k, i1 = e - s1 * d.k;
+                    if (i1 >= min(ctl->recv_n[s1], d.k)) continue;
+                    const u64 c = s1 == 0 ? m.sorted[i1] : m.recv[(s1 - 1) * d.k + i1];
+                    int rk = i1;
+                    for (int s2 = 0; s2 < nl; ++s2) {
+                        if (s2 == s1) continue;
+                        const u64* run = s2 == 0 ? m.sorted : m.recv + (s2 - 1) * d.k;   // descending: count its entries above c
+                        int lo = 0, hi = min(ctl->recv_n[s2], d.k);
+                        while (lo < hi) {
+                            const int mid = (lo + hi) >> 1;
+                            if (run[mid] > c) lo = mid + 1;
+                            else hi = mid;
+                        }
+                        rk += lo;
+                    }
+                    if (rk < d.k) m.list[rk] = c;
+                }
+                consumer_sync();
+                kk = min(total, d.k);
             }
-            consumer_sync();
-            kk = min(kk + n1, d.k);
             for (int i = tid; i < kk; i += kThreads) m.sorted[i] = m.list[i];
             consumer_sync();
         }
@@ -698,7 +729,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
     if (warp == kWarps) {
         if (a.bulk_ok) producer_loop(a, m.stage, ctl, t_begin, nt);
         __syncwarp();
-        if (a.pair) cluster_arrive_release();   // every thread of the pair arrives exactly once (see segment_end)
+        if (a.pair) cluster_arrive_release();   // every thread of the cluster arrives exactly once (see segment_end)
         return;
     }
     trace_mark(a, 1);
@@ -924,7 +955,7 @@ int launch_stream_kernel(const StreamArgs& a, int grid, void* stream) {
     }
     if (a.pair) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 2;
+        attr[n].val.clusterDim.x = (unsigned)a.pair;
         attr[n].val.clusterDim.y = 1;
         attr[n].val.clusterDim.z = 1;
         ++n;

@@ -159,7 +159,7 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
     } else {
         // Otherwise a row is cut into nseg = T / q aligned pieces.  Fewer tiles per CTA shorten the streaming (per 32 KiB
         // tile about 0.25 us on a lone SM, 0.6 us when every SM streams), more pieces lengthen the merge: nothing for one
-        // piece, the on-chip exchange of a CTA pair for two, ordered lists merged by binary search up to 16, a
+        // piece, the on-chip exchange inside a cluster of 2, 4 or 8 CTAs, ordered lists merged through scratch up to 16, a
         // gather-and-select beyond (measured on B200, in us).  Pick the cheapest q that divides the row and keeps
         // the grid within one wave.
         double best = 1e30;
@@ -167,7 +167,9 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
             if (T % c != 0) continue;
             const int nseg = T / c;
             const double busy = std::min(1.0, (double)n_rows * nseg / slots);
-            const double merge = nseg == 1 ? 0.0 : nseg == 2 ? 1.4 : nseg <= 8 ? 2.4 + 0.25 * nseg : nseg <= 16 ? 4.4 + 0.5 * nseg : 10.0 + 0.3 * nseg;
+            const bool on_chip = (nseg == 2 || nseg == 4 || nseg == 8) && (nseg - 1) * std::max(1, kmax) <= 512;   // a cluster per row
+            const double merge = nseg == 1 ? 0.0 : on_chip ? (nseg == 2 ? 1.4 : nseg == 4 ? 2.0 : 3.3)
+                                 : nseg <= 8 ? 2.4 + 0.25 * nseg : nseg <= 16 ? 4.4 + 0.5 * nseg : 10.0 + 0.3 * nseg;
             const double cost = (0.25 + 0.35 * busy) * c + merge;
             if (cost < best) {
                 best = cost;
@@ -289,8 +291,10 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.softcap = h->softcap;
         a.overlap = h->launch_overlap;
         const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
-        // rows of exactly two aligned segments: the two CTAs of a row run as a cluster and exchange candidates on chip
-        a.pair = (h->pair_ok && a.tiles_per_row == 2 * a.tiles_per_cta && grid == 2 * a.n_rows) ? 1 : 0;
+        // rows of exactly 2, 4 or 8 aligned segments: the CTAs of a row run as a cluster and exchange candidates on chip
+        a.pair = 0;
+        for (int c = 2; c <= 8; c *= 2)   // receive buffer: (c - 1) lists of kmax entries in 512
+            if (h->pair_ok && a.tiles_per_row == c * a.tiles_per_cta && grid == c * a.n_rows && (c - 1) * b->kmax <= 512) a.pair = c;
         const int e = fsb::launch_stream_kernel(a, grid, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         h->counters.kernel_launches++;
