@@ -158,7 +158,7 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
         q = T;
     } else {
         // Otherwise a row is cut into nseg = T / q aligned pieces.  Fewer tiles per CTA shorten the streaming (per 32 KiB
-        // tile about 0.25 us on a lone SM, 0.6 us when every SM streams), more pieces lengthen the merge: nothing for one
+        // tile about 0.4 us on a lone SM, 0.6 us when every SM streams), more pieces lengthen the merge: nothing for one
         // piece, the on-chip exchange inside a cluster of 2, 4 or 8 CTAs, ordered lists merged through scratch up to 16, a
         // gather-and-select beyond (measured on B200, in us).  Pick the cheapest q that divides the row and keeps
         // the grid within one wave.
@@ -170,7 +170,7 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
             const bool on_chip = (nseg == 2 || nseg == 4 || nseg == 8) && (nseg - 1) * std::max(1, kmax) <= 512;   // a cluster per row
             const double merge = nseg == 1 ? 0.0 : on_chip ? (nseg == 2 ? 1.4 : nseg == 4 ? 2.0 : 3.3)
                                  : nseg <= 8 ? 2.4 + 0.25 * nseg : nseg <= 16 ? 4.4 + 0.5 * nseg : 10.0 + 0.3 * nseg;
-            const double cost = (0.25 + 0.35 * busy) * c + merge;
+            const double cost = (0.4 + 0.2 * busy) * c + merge;
             if (cost < best) {
                 best = cost;
                 q = c;
