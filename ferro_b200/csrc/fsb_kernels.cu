@@ -43,14 +43,16 @@ constexpr long long kCopyWaitCycles = 2000000000ll;   // about 1 s: a bulk copy 
 // The [rows][n_vocab] matrix is cut into CTA tiles of kTile logits; the flat list of tiles is dealt to the CTAs in
 // equal contiguous ranges, and the part of a row that one CTA owns is a "segment".  One extra warp, the producer,
 // brings the CTA tiles into a ring of kStages shared-memory slots, one 1-D bulk copy per tile, so every logit is
-// read from HBM exactly once; the eight consumer warps each own one eighth (a warp tile of kWTile logits) of every
-// tile, wait for it to land, look at it and hand the slot back - they meet at the ring, never at a barrier.
+// read from HBM exactly once; the sixteen consumer warps each own one sixteenth (a warp tile of kWTile logits) of
+// every tile, wait for it to land, look at it and hand the slot back - they meet at the ring, never at a barrier.
 // Lane l owns float4 number l + 32 * q (q = 0..3) of a warp tile: a "cell" of four consecutive logits.  While
 // streaming a lane does not look at single logits: it takes the maximum of each cell, and where that reaches the
-// admission bound it notes the cell's location (one predicated 4-byte store into a queue only this lane writes).
-// At the end of a segment the noted cells are read again (from L2, as a rule), their logits that reach the final
-// bound are ranked, and the segment's k best go to the row's scratch area; the CTA that draws the row's last
-// ticket merges and finishes the row.  Nobody spins on another CTA; waits for this CTA's own copies are bounded.
+// admission bound it notes the cell (one predicated 4-byte store of its truncated maximum and its location into a
+// queue only this lane writes).  At the end of a segment the noted cells the bound has not overtaken are read again
+// (from L2, as a rule), their logits that reach the final bound are ordered, and the segment's k best are the row's
+// candidates - or, when a row has several segments, go to the first CTA of the row's cluster through shared memory,
+// or to the row's scratch area, where the CTA that draws the row's last ticket merges them.  Nobody spins on
+// another CTA; waits for this CTA's own copies are bounded.
 
 // The shared memory of a CTA.  The gathered cells' memory doubles as a list of composites (elements, merging),
 // the survivors' memory as the ordered candidates of the epilogue.
