@@ -43,7 +43,7 @@ PARAMS_DTYPE = np.dtype(
 API_SYMBOLS = [
     "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap", "fsb_batch_shard_launch", "fsb_batch_merge_launch", "fsb_argmax_rows_static", "fsb_stream_history_set", "fsb_stream_history_append", "fsb_stream_history_len",
     "fsb_sample_batch_resident",
-    "fsb_set_trace_buffer",
+    "fsb_set_trace_buffer", "fsb_set_scan_sums", "fsb_set_vocab_shard", "fsb_verify_windows_resident",
     "fsb_params_default", "fsb_params_validate", "fsb_stream_open", "fsb_stream_close", "fsb_stream_params",
     "fsb_stream_state_get", "fsb_stream_state_set", "fsb_sample_batch", "fsb_verify_windows", "fsb_last_kept",
     "fsb_batch_prepare", "fsb_batch_redraw", "fsb_batch_launch", "fsb_batch_tokens", "fsb_batch_kernel_count",
@@ -92,6 +92,9 @@ def load_library(build_if_missing: bool = True):
     L.fsb_set_vocab_offset.argtypes = [vp, C.c_int32]
     L.fsb_set_launch_overlap.argtypes = [vp, C.c_int]
     L.fsb_set_trace_buffer.argtypes = [vp, vp]
+    L.fsb_set_scan_sums.argtypes = [vp, C.c_int]
+    L.fsb_set_vocab_shard.argtypes = [vp, C.c_int32, C.c_int32]
+    L.fsb_verify_windows_resident.argtypes = [vp, i32, vp, vp, vp, vp, i64, i32, vp, vp, vp, vp, u32]
     L.fsb_params_default.argtypes = [vp]
     L.fsb_params_default.restype = None
     L.fsb_params_validate.argtypes = [vp]
@@ -243,6 +246,14 @@ class Engine:
     def set_vocab_offset(self, offset: int):
         self._check(self.lib.fsb_set_vocab_offset(self._h, int(offset)))
 
+    def set_vocab_shard(self, offset: int, global_vocab: int):
+        """This engine holds columns [offset, offset + n_vocab) of rows that are `global_vocab` columns wide."""
+        self._check(self.lib.fsb_set_vocab_shard(self._h, int(offset), int(global_vocab)))
+
+    def set_scan_sums(self, on: bool):
+        """Epilogue sums by warp prefix scans instead of one thread adding in candidate order (see the C header)."""
+        self._check(self.lib.fsb_set_scan_sums(self._h, 1 if on else 0))
+
     # -- streams
     def open_stream(self, params) -> int:
         p = np.ascontiguousarray(np.asarray(params, dtype=PARAMS_DTYPE).reshape(-1)[:1])
@@ -303,6 +314,27 @@ class Engine:
                                                 C.c_void_p(ptr), ld, n_vocab, flat.ctypes.data, off.ctypes.data,
                                                 ma.ctypes.data if ma is not None else None, tokens.ctypes.data, acc.ctypes.data,
                                                 conf.ctypes.data, flags))
+        return [tokens[row_off[i]:row_off[i + 1]] for i in range(n_streams)], acc, conf
+
+    def verify_windows_resident(self, stream_ids, rows, logits, n_vocab: int | None = None, max_accept=None, flags: int = 0):
+        """``verify_windows`` with the streams' resident histories; with APPEND_SAMPLED the accepted tokens are appended."""
+        sids = np.ascontiguousarray(stream_ids, dtype=np.int32)
+        n_streams = len(sids)
+        row_off = np.zeros(n_streams + 1, dtype=np.int32)
+        for i, r in enumerate(rows):
+            row_off[i + 1] = row_off[i] + len(r)
+        rows_flat = np.concatenate([np.asarray(r, dtype=np.int32) for r in rows]).astype(np.int32)
+        n_rows = int(row_off[-1])
+        if n_vocab is None:
+            n_vocab = int(logits.shape[-1])
+        ptr, ld, flags, keep = _logits_pointer(logits, n_rows, n_vocab, flags)
+        tokens = np.zeros(n_rows, dtype=np.int32)
+        acc = np.zeros(n_streams, dtype=np.int32)
+        conf = np.zeros(n_streams, dtype=np.int32)
+        ma = np.ascontiguousarray(max_accept, dtype=np.int32) if max_accept is not None else None
+        self._check(self.lib.fsb_verify_windows_resident(self._h, n_streams, sids.ctypes.data, row_off.ctypes.data, rows_flat.ctypes.data,
+                                                         C.c_void_p(ptr), ld, n_vocab, ma.ctypes.data if ma is not None else None,
+                                                         tokens.ctypes.data, acc.ctypes.data, conf.ctypes.data, flags))
         return [tokens[row_off[i]:row_off[i + 1]] for i in range(n_streams)], acc, conf
 
     def last_kept(self, row: int, cap: int = MAX_CANDIDATE_K):

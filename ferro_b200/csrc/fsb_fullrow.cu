@@ -376,10 +376,7 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
         const int lane = tid & 31, warp = tid >> 5, runs = (m + 31) >> 5;
         u64 c = 0ull;
         if (warp < runs) {
-            u64 v[1];
-            v[0] = tid < m ? hv.raw[tid] : 0ull;
-            warp_sort_desc<1>(v);
-            c = v[0];
+            c = warp_sort32_desc(tid < m ? hv.raw[tid] : 0ull);
             hv.raw[tid] = c;
         }
         __syncthreads();

@@ -4,7 +4,7 @@
 //   repetition penalty (src/sampler.cpp:11-18) -> greedy argmax (:19-23) or top-k candidates (:25-35)
 //   -> fp64 softmax (:37-41) -> min-p (:43) -> top-p (:44) -> seeded draw (:45-49).
 // (reference paths are relative to the paragontasx/ferro project root)
-// How it works is described above SegCtx below.
+// How it works is described above the kernel below.
 #include <cuda_runtime.h>
 
 #include "../../include/ferro_sampler_b200.h"
@@ -15,58 +15,57 @@ namespace {
 
 constexpr int kWarps = kThreads / 32;
 constexpr int kWTile = kTile / kWarps;          // 512 logits: a warp's part of a CTA tile
-constexpr int kBlockThreads = kThreads + 32;    // consumers + the producer warp
-constexpr int kMaxJ = (kFlatCells + kMaxK + kThreads - 1) / kThreads;   // cells one thread may hold in a re-selection
+constexpr int kCopyWarp = kWarps;               // issues the bulk copies
+constexpr int kSetupWarp = kWarps + 1;          // fetches work items, builds their penalty bitmaps
+constexpr int kBlockThreads = kThreads + 64;
 
 constexpr size_t kSmemStage = (size_t)kStages * kTile * sizeof(float);
-constexpr size_t kSmemQueue = (size_t)kLaneQueue * kThreads * sizeof(unsigned);   // the lanes' queues of noted cells
-constexpr size_t kSmemCells = (size_t)kFlatCells * kCellBytes;                     // gathered cells; a list of composites otherwise
-constexpr size_t kSmemKept = (size_t)kMaxK * kCellBytes;                           // cells that survived a re-selection; selection scratch
-constexpr size_t kSmemBitmap = (size_t)kBitmapWords * sizeof(unsigned);
-constexpr int kRecvCap = 512;                                // clustered CTAs: the other CTAs' ordered candidates arrive here,
-constexpr size_t kSmemRecv = (size_t)kRecvCap * sizeof(u64);   // (cluster size - 1) parts of k entries
-static_assert(kRecvCap >= kMaxK, "a pair can always exchange");
-constexpr size_t kSmemTotal = kSmemStage + kSmemQueue + kSmemCells + kSmemKept + kSmemBitmap + kSmemRecv + sizeof(SharedCtl);
+constexpr size_t kSmemPools = (size_t)kWarps * kPoolCap * sizeof(u64);          // the warps' candidate pools; a row's lists while they are merged
+constexpr size_t kSmemBitmap = 2 * (size_t)kItemBitmapWords * sizeof(unsigned);   // penalty bitmaps of two work items
+constexpr size_t kSmemList = (size_t)kListCap * sizeof(u64);                    // an item's candidates; the epilogue's doubles
+constexpr size_t kSmemSorted = (size_t)kMaxK * sizeof(u64);                     // ordered candidates
+constexpr size_t kSmemTotal = kSmemStage + kSmemPools + kSmemBitmap + kSmemList + kSmemSorted + sizeof(SharedCtl);
 static_assert(kSmemTotal <= 227 * 1024, "one CTA per SM");
-static_assert(kSmemCells >= (size_t)kMergeCap * sizeof(u64), "the element list lives in the gathered cells' memory");
-static_assert(kMergeCap >= 4 * kMaxK, "the logits of kMaxK surviving cells must fit into the element list");
-static_assert(kMergeCap >= 2 * kMaxK, "the epilogue's arrays live in the list's memory");
-static_assert(kSmemKept >= (size_t)kMaxK * sizeof(u64), "the ordered candidates live in the survivors' memory");
+static_assert(kSmemPools >= (size_t)kRowScratch * sizeof(u64), "a row's published lists fit into the pools' memory");
+static_assert(kSmemList >= 2 * (size_t)kMaxK * sizeof(double), "the epilogue's arrays live in the list's memory");
 static_assert(kWTile == 512, "a lane owns four float4 of a warp tile");
-static_assert(kMaxTilesPerCta <= 32, "a location is seven bits: the tile number above two bits (bit 7 is free)");
-static_assert(kFlatCells >= kThreads, "a capped gather round takes at least one cell per thread");
-static_assert(kLaneQueue % 4 == 0 && kLaneQueue >= 8, "lanes look at four cells per tile");
+static_assert(kPoolCap >= kMaxK + 128, "a warp keeps its k best and still has room for the candidates of 128 cells");
+static_assert(kPoolCap % 32 == 0 && kPoolCap / 32 <= 12, "a warp holds its pool in twelve registers per lane when it selects");
 
-constexpr long long kCopyWaitCycles = 2000000000ll;   // about 1 s: a bulk copy that has not landed by then is reported, not awaited
+constexpr long long kWaitCycles = 2000000000ll;   // about 1 s: a wait that has not ended by then is reported, not continued
 
 // How the streaming kernel works.
-// The [rows][n_vocab] matrix is cut into CTA tiles of kTile logits; the flat list of tiles is dealt to the CTAs in
-// equal contiguous ranges, and the part of a row that one CTA owns is a "segment".  One extra warp, the producer,
-// brings the CTA tiles into a ring of kStages shared-memory slots, one 1-D bulk copy per tile, so every logit is
-// read from HBM exactly once; the sixteen consumer warps each own one sixteenth (a warp tile of kWTile logits) of
-// every tile, wait for it to land, look at it and hand the slot back - they meet at the ring, never at a barrier.
-// Lane l owns float4 number l + 32 * q (q = 0..3) of a warp tile: a "cell" of four consecutive logits.  While
-// streaming a lane does not look at single logits: it takes the maximum of each cell, and where that reaches the
-// admission bound it notes the cell (one predicated 4-byte store of its truncated maximum and its location into a
-// queue only this lane writes).  At the end of a segment the noted cells the bound has not overtaken are read again
-// (from L2, as a rule), their logits that reach the final bound are ordered, and the segment's k best are the row's
-// candidates - or, when a row has several segments, go to the first CTA of the row's cluster through shared memory,
-// or to the row's scratch area, where the CTA that draws the row's last ticket merges them.  Nobody spins on
-// another CTA; waits for this CTA's own copies are bounded.
+// The [rows][n_vocab] matrix is cut into CTA tiles of kTile logits, and every row into the same few chunks of up
+// to kItemTilesMax tiles.  A work item is one chunk of one row.  The grid is one CTA per SM (or fewer, for small
+// batches); CTA b starts with item b and draws further items from a counter in global memory, so that the CTAs
+// finish together however unevenly the SMs are served.  Items are numbered chunk by chunk (the first chunk of
+// every row, then the second, ...): the small chunks at the end of the schedule even out the finish.
+//
+// A CTA has three kinds of warps, which meet only at mbarriers:
+//   * the set-up warp fetches the next item, reads the row's descriptor and builds the bitmap of the item's
+//     penalised columns from the row's window ids - one item ahead of the consumers;
+//   * the copy warp brings the item's tiles into a ring of kStages shared-memory slots, one 1-D bulk copy per
+//     tile, so every logit is read from HBM exactly once; it runs ahead of the consumers across item borders;
+//   * sixteen consumer warps each own one sixteenth (512 logits) of every tile.  A lane owns four cells (float4)
+//     per tile.  It takes each cell's maximum; a warp whose lanes all stay below the admission bound is done with
+//     the tile.  Otherwise the logits that reach the bound go, as composites, into the warp's pool in shared memory
+//     (ballot-compacted: no atomics).  The bound is the smallest, over the warps, of the r-th largest of a warp's 32
+//     lane maxima (r = ceil(k / 16)): at least k logits of the item reach it.  It is set at the item's first tile
+//     and refreshed at tiles 1, 2, 4 without a barrier; a later chunk of a row starts from the bound the row's
+//     earlier chunks have left in global memory.  A warp whose pool fills up drops what the bound has overtaken
+//     and, if that is not enough (rows of equal values), keeps exactly its k best - ties by token id.
+// At the end of an item the warps' surviving candidates are gathered, ordered, and the k best published in the
+// item's part of the row's scratch; the CTA that publishes the row's last chunk (a ticket) merges the ordered
+// lists and runs the epilogue.  No CTA ever waits for another CTA; waits for this CTA's own copies and
+// hand-overs are bounded.
 
-// The shared memory of a CTA.  The gathered cells' memory doubles as a list of composites (elements, merging),
-// the survivors' memory as the ordered candidates of the epilogue.
+// The shared memory of a CTA.
 struct Smem {
     float* stage;       // [kStages][kTile] ring of CTA tiles
-    unsigned* queue;    // [kLaneQueue][kThreads] cells noted by each lane: truncated maximum | location
-    float4* cells;      // [kFlatCells] gathered cells ...
-    int* ids;           // [kFlatCells] ... and their first token ids
-    float4* kcells;     // [kMaxK] survivors of re-selections
-    int* kids;          // [kMaxK]
-    u64* list;          // = cells
-    u64* sorted;        // = kcells
-    unsigned* bitmap;
-    u64* recv;          // [kRecvCap] receive buffer of the first CTA of a cluster
+    u64* pools;         // [kWarps][kPoolCap] candidates the warps have admitted; a row's published lists while they are merged
+    unsigned* bitmap;   // [2][kItemBitmapWords]
+    u64* list;          // [kListCap] the item's candidates
+    u64* sorted;        // [kMaxK] the k best, in order
     SharedCtl* ctl;
 };
 __device__ __forceinline__ Smem smem_view() {
@@ -75,21 +74,30 @@ __device__ __forceinline__ Smem smem_view() {
     unsigned char* p = smem_raw;
     m.stage = reinterpret_cast<float*>(p);
     p += kSmemStage;
-    m.queue = reinterpret_cast<unsigned*>(p);
-    p += kSmemQueue;
-    m.cells = reinterpret_cast<float4*>(p);
-    m.ids = reinterpret_cast<int*>(p + (size_t)kFlatCells * sizeof(float4));
-    m.list = reinterpret_cast<u64*>(p);
-    p += kSmemCells;
-    m.kcells = reinterpret_cast<float4*>(p);
-    m.kids = reinterpret_cast<int*>(p + (size_t)kMaxK * sizeof(float4));
-    m.sorted = reinterpret_cast<u64*>(p);
-    p += kSmemKept;
+    m.pools = reinterpret_cast<u64*>(p);
+    p += kSmemPools;
     m.bitmap = reinterpret_cast<unsigned*>(p);
     p += kSmemBitmap;
-    m.recv = reinterpret_cast<u64*>(p);
-    m.ctl = reinterpret_cast<SharedCtl*>(p + kSmemRecv);
+    m.list = reinterpret_cast<u64*>(p);
+    p += kSmemList;
+    m.sorted = reinterpret_cast<u64*>(p);
+    p += kSmemSorted;
+    m.ctl = reinterpret_cast<SharedCtl*>(p);
     return m;
+}
+
+// Waits for a barrier phase, for about a second at most (much less once some wait of this CTA has run out).
+__device__ __forceinline__ bool mbar_wait_bounded(u64* bar, unsigned parity, SharedCtl* ctl) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long lim = *reinterpret_cast<volatile int*>(&ctl->abort) ? 2000ll : kWaitCycles;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > lim) return false;
+    return true;
+}
+__device__ __forceinline__ void report_timeout(SharedCtl* ctl, unsigned* status) {
+    *reinterpret_cast<volatile int*>(&ctl->abort) = 1;
+    atomicOr(status, kStatusCopyTimeout);
 }
 
 // Final-logit softcap over a warp tile, in place (src/model_gemma4.cpp:521).  Only the softcap build calls it.
@@ -103,12 +111,12 @@ __device__ __noinline__ void softcap_tile(float* st, int len, float cap, float* 
 }
 
 // Repetition penalty on the penalised columns of a warp tile, in place in shared memory (src/sampler.cpp:17).
-// The tile's bits of the segment bitmap are one word per 32 columns; each of the first lanes owns one word and
+// The tile's bits of the item's bitmap are one word per 32 columns; each of the first lanes owns one word and
 // patches the columns whose bits are set.  A bit is set once however often an id occurs in the window.
-__device__ __forceinline__ void patch_tile(float* st, int len, int col0, int seg_lo, float pen, const unsigned* bitmap, float* wb_row) {
+__device__ __forceinline__ void patch_tile(float* st, int len, int col0, int item_lo, float pen, const unsigned* bitmap, float* wb_row) {
     const int lane = threadIdx.x & 31;
     const int nw = (len + 31) >> 5;
-    unsigned w = (lane < nw) ? bitmap[((col0 - seg_lo) >> 5) + lane] : 0u;
+    unsigned w = (lane < nw) ? bitmap[((col0 - item_lo) >> 5) + lane] : 0u;
     if (__ballot_sync(0xffffffffu, w != 0u) == 0u) return;
     while (w) {
         const int off = 32 * lane + __ffs(w) - 1;
@@ -145,10 +153,10 @@ __device__ __forceinline__ float warp_bound(float run_max, int k) {
     return key_float(key);
 }
 
-// Admission bound of the CTA: at least k logits of the segment reach the smallest of the warps' bounds (eight
-// warps, at least ceil(k / 8) logits each, or 32 * 8 >= kMaxK), so no logit below it is among the segment's k
-// best.  Each warp posts its value; values only grow, so a reader may use another warp's older value without a
-// barrier.
+// Admission bound of the CTA: at least k logits of the item reach the smallest of the warps' bounds (sixteen
+// warps, at least ceil(k / 16) logits each, or 32 * 16 >= kMaxK), so no logit below it is among the item's k
+// best.  Each warp posts its value; within an item values only grow, so a reader may use another warp's older
+// value without a barrier.
 __device__ __forceinline__ float min_warp_bounds(SharedCtl* ctl) {
     float m = __int_as_float(0x7f800000);
 #pragma unroll
@@ -159,547 +167,320 @@ __device__ __forceinline__ float min_warp_bounds(SharedCtl* ctl) {
     }
     return m;
 }
-// Diagnostics: slot 0 takes the global timer (ns) once, the others the SM cycle counter (cheap to read).
+
+// Diagnostics: time stamps of CTA phases (see fsb_set_trace_buffer).
 __device__ __forceinline__ void trace_mark(const StreamArgs& a, int slot) {
-    if (a.trace && threadIdx.x == 0) {
-        a.trace[(size_t)blockIdx.x * 8 + slot] = slot == 0 ? global_timer_ns() : (u64)clock64();
-        if (slot == 0) a.trace[(size_t)blockIdx.x * 8 + 7] = (u64)clock64();
-    }
+    if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
+}
+__device__ __forceinline__ void trace_set(const StreamArgs& a, int slot, u64 v) {
+    if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 16 + slot] = v;
 }
 
-// Composite of a cell: (largest of its four logits, first token id).  A logit of the k best of a set of cells
-// always lies in one of the k cells with the largest composites.
-__device__ __forceinline__ u64 cell_comp(float4 x, int id0) { return make_comp(fmaxf(max3(x.x, x.y, x.z), x.w), id0); }
-
-// A queue entry: the cell's maximum with its low eight bits cleared (rounded toward zero) | the cell's location,
-// (tile of the segment << 2) | q.  For any a >= b, entry_value of a's entry >= truncated(b): testing entries
-// against a truncated bound never drops a cell whose maximum reaches the bound.
-__device__ __forceinline__ unsigned make_entry(float mx, unsigned loc) { return (__float_as_uint(mx) & 0xFFFFFF00u) | loc; }
-__device__ __forceinline__ float entry_value(unsigned e) { return __uint_as_float(e & 0xFFFFFF00u); }
-__device__ __forceinline__ float truncated(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFFF00u); }
-
-// Notes a cell in this lane's queue if its maximum reaches the bound: a compare, the entry, one predicated store and
-// one predicated increment - no branch.  `q_base` is the shared-memory address of the lane's entry 0; entries of
-// one lane are kThreads * 4 bytes apart.
-__device__ __forceinline__ void note_cell_if(float mx, float thr, unsigned loc, unsigned q_base, int& qn) {
-    const unsigned entry = make_entry(mx, loc);
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .u32 a;\n\t"
-        "setp.ge.f32 p, %2, %3;\n\t"
-        "mad.lo.u32 a, %0, %5, %1;\n\t"
-        "@p st.shared.u32 [a], %4;\n\t"
-        "@p add.s32 %0, %0, 1;\n\t}"
-        : "+r"(qn)
-        : "r"(q_base), "f"(mx), "f"(thr), "r"(entry), "n"(kThreads * 4)
-        : "memory");
-}
-
-// Drops the entries of this lane's queue whose cell maximum cannot reach `thr` any more; returns the new length.
-__device__ __forceinline__ int drop_stale(unsigned* myq, int qn, float thr) {
-    const float t = truncated(thr);
+// ---- a warp's pool of admitted candidates ----------------------------------------------------------------------
+// Keeps the entries of the warp's pool that are >= floor_c, in place and in order; returns their number.
+__device__ __forceinline__ int filter_pool(u64* pool, int n, u64 floor_c) {
+    const int lane = threadIdx.x & 31;
+    const unsigned lt = (1u << lane) - 1u;
     int w = 0;
-    for (int i = 0; i < qn; ++i) {
-        const unsigned e = myq[i * kThreads];
-        if (entry_value(e) >= t) myq[(w++) * kThreads] = e;
+    for (int i0 = 0; i0 < n; i0 += 32) {
+        const int i = i0 + lane;
+        const u64 c = i < n ? pool[i] : 0ull;
+        const bool keep = i < n && c >= floor_c;
+        const unsigned bm = __ballot_sync(0xffffffffu, keep);   // every lane has read its entry by now
+        if (keep) pool[w + __popc(bm & lt)] = c;
+        w += __popc(bm);
     }
+    __syncwarp();
     return w;
 }
 
-// Column of the cell a queue entry of this thread names.
-__device__ __forceinline__ int loc_column(unsigned loc, const SegCtx& sc) {
-    loc &= 0xFFu;
-    return sc.seg_lo + (int)(loc >> 2) * kTile + (int)(threadIdx.x >> 5) * kWTile + 4 * ((int)(threadIdx.x & 31) + 32 * (int)(loc & 3u));
-}
-
-// The cell at column `col` of the row, as loaded (no transformation).  Columns past the end of the row are NaN.
-__device__ __forceinline__ float4 load_cell(const SegCtx& sc, int col) {
-    if (sc.vec_ok && col + 4 <= sc.n_vocab) return __ldcg(reinterpret_cast<const float4*>(sc.row + col));
-    const float qnan = __int_as_float(0x7fc00000);
-    float4 t;
-    t.x = (col < sc.n_vocab) ? __ldcg(sc.row + col) : qnan;
-    t.y = (col + 1 < sc.n_vocab) ? __ldcg(sc.row + col + 1) : qnan;
-    t.z = (col + 2 < sc.n_vocab) ? __ldcg(sc.row + col + 2) : qnan;
-    t.w = (col + 3 < sc.n_vocab) ? __ldcg(sc.row + col + 3) : qnan;
-    return t;
-}
-
-// Softcap, then penalty, as the streaming pass applied them to the cell at column `col`.
-template <bool SOFTCAP>
-__device__ __forceinline__ float4 transform_cell(float4 t, const SegCtx& sc, const unsigned* bitmap, int col) {
-    if (sc.final_in_mem) return t;
-    if (SOFTCAP) {
-        t.x = __fmul_rn(sc.cap, tanhf(__fdiv_rn(t.x, sc.cap)));
-        t.y = __fmul_rn(sc.cap, tanhf(__fdiv_rn(t.y, sc.cap)));
-        t.z = __fmul_rn(sc.cap, tanhf(__fdiv_rn(t.z, sc.cap)));
-        t.w = __fmul_rn(sc.cap, tanhf(__fdiv_rn(t.w, sc.cap)));
-    }
-    if (sc.has_pen) {
-        const int b = col - sc.seg_lo;   // a multiple of four: the four bits lie in one word
-        const unsigned bits = (bitmap[b >> 5] >> (b & 31)) & 0xFu;
-        if (bits) {
-            if (bits & 1u) t.x = t.x > 0.0f ? __fdiv_rn(t.x, sc.pen) : __fmul_rn(t.x, sc.pen);
-            if (bits & 2u) t.y = t.y > 0.0f ? __fdiv_rn(t.y, sc.pen) : __fmul_rn(t.y, sc.pen);
-            if (bits & 4u) t.z = t.z > 0.0f ? __fdiv_rn(t.z, sc.pen) : __fmul_rn(t.z, sc.pen);
-            if (bits & 8u) t.w = t.w > 0.0f ? __fdiv_rn(t.w, sc.pen) : __fmul_rn(t.w, sc.pen);
-        }
-    }
-    return t;
-}
-
-// Exclusive prefix sum of one int per consumer thread over the CTA (thread order) and the total.  Contains two
-// barriers; uses ctl->red.
-struct ScanResult {
-    int before;
-    int total;
-};
-__device__ __forceinline__ ScanResult cta_scan(int v, SharedCtl* ctl) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int inc = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += t;
-    }
-    if (lane == 31) reinterpret_cast<int*>(ctl->red)[warp] = inc;
-    consumer_sync();
-    int before = inc - v, total = 0;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        const int s = reinterpret_cast<int*>(ctl->red)[w];
-        if (w < warp) before += s;
-        total += s;
-    }
-    consumer_sync();   // the scratch may be written again
-    return ScanResult{before, total};
-}
-
-// Re-selection over the nq gathered cells (flat arrays) and the nkept survivors: the k cells with the largest
-// composites become the survivors' list.  Returns their number and the composite bound they passed (0: nothing was
-// dropped).  All consumer threads must call, after a barrier that made the gathered cells visible.
-struct SelectResult {
-    int count;
-    u64 bound;
-};
-__device__ __noinline__ SelectResult select_cells(int nq, int nkept, int k) {
-    const Smem cs = smem_view();
-    SharedCtl* ctl = cs.ctl;
-    const int tid = threadIdx.x;
-    const int n = nq + nkept;
-    float4 cx[kMaxJ];
-    int cid[kMaxJ];
-    u64 cc[kMaxJ];
-#pragma unroll
-    for (int j = 0; j < kMaxJ; ++j) {
-        const int f = tid + j * kThreads;
-        cc[j] = 0ull;
-        cid[j] = 0;
-        cx[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (f < n) {
-            cx[j] = f < nq ? cs.cells[f] : cs.kcells[f - nq];
-            cid[j] = f < nq ? cs.ids[f] : cs.kids[f - nq];
-            cc[j] = cell_comp(cx[j], cid[j]);
-        }
-    }
-    consumer_sync();   // every cell is in registers: the survivors' memory may be rewritten
-    u64 L = 0ull;
-    if (n > k) {
-        u64 mn = ~0ull, mx = 0ull;
-#pragma unroll
-        for (int j = 0; j < kMaxJ; ++j) {
-            if (cc[j] != 0ull) {
-                mn = min(mn, cc[j]);
-                mx = max(mx, cc[j]);
-            }
-        }
-        cta_minmax(mn, mx, ctl);
-        L = bisect_bound(k, mn, mx, ctl, [&](u64 t) {
-            int c = 0;
-#pragma unroll
-            for (int j = 0; j < kMaxJ; ++j) c += cc[j] >= t ? 1 : 0;   // empty slots hold 0, t is never 0
-            return c;
-        });
-    }
-    if (tid == 0) ctl->out_cnt = 0;
-    consumer_sync();
-#pragma unroll
-    for (int j = 0; j < kMaxJ; ++j) {
-        if (cc[j] != 0ull && cc[j] >= L) {
-            const int p = atomicAdd(&ctl->out_cnt, 1);
-            if (p < kMaxK) {
-                cs.kcells[p] = cx[j];
-                cs.kids[p] = cid[j];
-            }
-        }
-    }
-    consumer_sync();
-    return SelectResult{min(ctl->out_cnt, kMaxK), L};
-}
-
-// The re-selection proper (rare): every lane drops the noted cells the bound has overtaken, the rest are read again
-// and the CTA keeps the k best cells.  All consumer threads call it, after the barrier of the rendez-vous.
-template <bool SOFTCAP>
-__device__ __noinline__ int compact_cells(int qn, int nkept, float thr_f) {
-    const Smem m = smem_view();
-    SharedCtl* ctl = m.ctl;
-    const SegCtx& sc = ctl->seg;
-    const int k = sc.k;
-    const int tid = threadIdx.x;
-    u64 bound = 0ull;
-    // every lane first drops what the bound has overtaken; then gather rounds: everything at once if it fits, else
-    // three cells per thread and round
-    qn = drop_stale(m.queue + tid, qn, fmaxf(thr_f, min_warp_bounds(ctl)));
-    int cap = kLaneQueue;
-    if (cta_scan(qn, ctl).total > kFlatCells) cap = kFlatCells / kThreads;
-    for (;;) {
-        const int cnt = min(qn, cap);
-        const ScanResult sr = cta_scan(cnt, ctl);
-        if (sr.total == 0) break;
-        for (int i0 = 0; i0 < cnt; i0 += 4) {   // four loads in flight
-            float4 c[4];
-            int col[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                col[u] = -1;
-                if (i0 + u < cnt) {
-                    col[u] = loc_column(m.queue[(size_t)(qn - 1 - i0 - u) * kThreads + tid], sc);
-                    c[u] = load_cell(sc, col[u]);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (col[u] >= 0) {
-                    m.cells[sr.before + i0 + u] = transform_cell<SOFTCAP>(c[u], sc, m.bitmap, col[u]);
-                    m.ids[sr.before + i0 + u] = col[u] + sc.id_base;
-                }
-            }
-        }
-        qn -= cnt;
-        consumer_sync();
-        const SelectResult r = select_cells(sr.total, nkept, k);
-        nkept = r.count;
-        bound = max(bound, r.bound);
-    }
-    if (tid == 0) {
-        ctl->need_compact = 0;
-        ctl->ev_bound = bound;
-    }
-    consumer_sync();
-    return 1 | (nkept << 1);
-}
-
-// One rendez-vous of all consumer warps of the CTA.  A warp comes here because it saw a request for a re-selection
-// (a lane's queue is nearly full), or because it has finished its part of the segment.  Every warp posts its
-// bound and the number of cells its lanes hold.  If a re-selection was asked for, the queued cells are read again
-// and the CTA keeps the k best cells (they become the survivors' list, all queues become empty), and `happened`
-// is set; otherwise every warp had finished and the posted values describe the whole segment.  Warps depend on
-// nothing but their own copies while streaming and look out for requests at every tile and in every wait, so
-// every warp gets here in bounded time.
-// Returns (happened) | (survivors << 1); the composite bound of a re-selection is left in ctl->ev_bound and the
-// warps' bounds in ctl->wbound.
-__device__ __forceinline__ int event_happened(int ev) { return ev & 1; }
-__device__ __forceinline__ int event_nkept(int ev) { return (ev >> 1) & 1023; }
-template <bool SOFTCAP>
-__device__ __forceinline__ int cta_event(int qn, int nkept, float run_max, float thr_f) {
-    const Smem m = smem_view();
-    SharedCtl* ctl = m.ctl;
-    const SegCtx& sc = ctl->seg;
-    const int k = sc.k;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float wb = warp_bound(run_max, k);
-    if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
-    if (tid == 0) ctl->out_cnt = 0;
-    consumer_sync();
-    if (*reinterpret_cast<volatile int*>(&ctl->need_compact) == 0) return nkept << 1;
-    return compact_cells<SOFTCAP>(qn, nkept, thr_f);
-}
-
-// Appends to the element list the logits of up to N cells of this thread that reach `thr` (NaNs and columns past
-// the end of the row take no part).  A warp reserves its part of the list with one atomic.  All lanes of the warp
-// must call; ncell = 0 contributes nothing.  Entries past the list's capacity are counted but not written.
-template <int N>
-__device__ __forceinline__ void append_elements(const float4 (&c)[N], const int (&id0)[N], int ncell, float thr, int id_end, u64* list,
-                                                SharedCtl* ctl) {
-    static_assert(N <= 8, "one mask bit per logit");
+// The k-th largest of the n > k distinct composites of the warp's pool: exactly k entries are >= the result.
+__device__ __forceinline__ u64 warp_kth_largest(const u64* pool, int n, int k) {
     const int lane = threadIdx.x & 31;
-    unsigned mask = 0u;
+    u64 v[kPoolCap / 32];
+    u64 mn = ~0ull, mx = 0ull;
 #pragma unroll
-    for (int u = 0; u < N; ++u) {
-        if (u < ncell) {
-            const float xs[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (xs[e] >= thr && id0[u] + e < id_end) mask |= 1u << (4 * u + e);
+    for (int j = 0; j < kPoolCap / 32; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = i < n ? pool[i] : 0ull;
+        if (i < n) {
+            mn = min(mn, v[j]);
+            mx = max(mx, v[j]);
         }
     }
-    const int mine = __popc(mask);
-    int inc = mine;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += t;
+    for (int o = 16; o; o >>= 1) {
+        mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     }
-    const int wtotal = __shfl_sync(0xffffffffu, inc, 31);
-    if (wtotal == 0) return;
-    int base = 0;
-    if (lane == 31) base = atomicAdd(&ctl->out_cnt, wtotal);
-    base = __shfl_sync(0xffffffffu, base, 31);
-    int p = base + inc - mine;
-#pragma unroll
-    for (int u = 0; u < N; ++u) {
-        const float xs[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-            if (mask & (1u << (4 * u + e))) {
-                if (p < kMergeCap) list[p] = make_comp(xs[e], id0[u] + e);
-                ++p;
-            }
-    }
-}
-
-// The producer: one lane brings the CTA tiles in, one 1-D bulk copy per tile (large copies: the copy engine's cost
-// is per request), into a ring of kStages slots.  A slot is refilled once all consumer warps have handed it back.
-__device__ __forceinline__ void producer_loop(const StreamArgs& a, float* stage, SharedCtl* ctl, int t_begin, int nt) {
-    if ((threadIdx.x & 31) != 0) return;
-    const int T = a.tiles_per_row, V = a.n_vocab;
-    int irow = t_begin / T, ij = t_begin - irow * T;
-    long long t_last = clock64();
-    int i = 0;
-    while (i < nt) {
-        const int slot = i % kStages;
-        // the first kStages tiles find their slots free; later ones wait for the consumers' hand-back
-        if (i >= kStages && !mbar_try_wait(&ctl->empty[slot], (unsigned)((i / kStages - 1) & 1))) {
-            if (clock64() - t_last > kCopyWaitCycles) {   // the consumers never came back: report and stop
-                atomicOr(a.status, kStatusCopyTimeout);
-                return;
-            }
-            continue;
-        }
-        const int col0 = ij * kTile;
-        const int len = min(kTile, V - col0);   // >= 1
-        const float* src = a.logits + (a.row_ld >= 0 ? (int64_t)irow * a.row_ld : a.rows[irow].logits_off) + col0;
-        float* dst = stage + (size_t)slot * kTile;
-        const unsigned bytes = (unsigned)(len & ~3) * 4u;
-        for (int e = len & ~3; e < len; ++e) dst[e] = src[e];   // ragged tail by plain loads
-        if (bytes) {
-            fence_proxy_async_smem();   // generic-proxy accesses to this slot (the consumers' patches) precede the async write
-            mbar_expect_tx(&ctl->full[slot], bytes);
-            bulk_g2s(dst, src, bytes, &ctl->full[slot]);
-        } else {
-            mbar_arrive(&ctl->full[slot]);
-        }
-        t_last = clock64();
-        ++i;
-        if (++ij == T) {
-            ij = 0;
-            ++irow;
-        }
-    }
-}
-
-// The end of a segment.  All consumer threads call it once they have looked at their last tile of the segment:
-// re-selections that were still asked for, the rendez-vous of the finished warps, the element list, the segment's
-// k best logits in order, and - in the CTA that draws the row's last ticket - the merge and the row's epilogue.
-template <bool SOFTCAP>
-__device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn, int nkept, float thr_f, float run_max, bool mark) {
-    const Smem m = smem_view();
-    SharedCtl* ctl = m.ctl;
-    const SegCtx& sc = ctl->seg;
-    const int tid = threadIdx.x;
-    const int T = a.tiles_per_row, V = a.n_vocab, Q = a.tiles_per_cta;
-    const RowDesc d = a.rows[row];
-    unsigned* myq = m.queue + tid;
-    const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
-    float thr_final;
-    int n_el;
-    for (;;) {
-        for (;;) {   // re-selections that were still asked for, then the rendez-vous of the finished warps
-            const int ev = cta_event<SOFTCAP>(qn, nkept, run_max, thr_f);
-            if (!event_happened(ev)) break;
-            qn = 0;
-            nkept = event_nkept(ev);
-        }
-        thr_final = fmaxf(thr_f, min_warp_bounds(ctl));
-        if (mark) trace_mark(a, 4);
-        // ---- the logits of the noted cells that reach the final bound become the element list
-        const int id_end = V + sc.id_base;
-        if (nkept > 0) {
-            float4 c[1];
-            int id0[1];
-            c[0] = m.kcells[min(tid, nkept - 1)];
-            id0[0] = m.kids[min(tid, nkept - 1)];
-            append_elements<1>(c, id0, tid < nkept ? 1 : 0, thr_final, id_end, m.list, ctl);
-        }
-        qn = drop_stale(myq, qn, thr_final);   // most noted cells have been overtaken by the bound
-        // a thread reads up to four of its cells per round (lanes rarely hold more that the bound has not overtaken)
-        const int rounds = (__reduce_max_sync(0xffffffffu, qn) + 3) >> 2;
+    if (mx == mn) return mn;
+    const int hb = 63 - __clzll((long long)(mx ^ mn));
+    u64 pfx = (hb == 63) ? 0ull : (mx & (~0ull << (hb + 1)));
 #pragma unroll 1
-        for (int rd = 0; rd < rounds; ++rd) {
-            float4 c[4];
-            int id0[4];
-            const int n = max(0, min(4, qn - 4 * rd));
+    for (int b = hb; b >= 0; --b) {
+        const u64 trial = pfx | (1ull << b);
+        int c = 0;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                id0[u] = 0;
-                c[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (u < n) {
-                    id0[u] = loc_column(myq[(4 * rd + u) * kThreads], sc);
-                    c[u] = load_cell(sc, id0[u]);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (u < n) {
-                    c[u] = transform_cell<SOFTCAP>(c[u], sc, m.bitmap, id0[u]);
-                    id0[u] += sc.id_base;
-                }
-            }
-            append_elements<4>(c, id0, n, thr_final, id_end, m.list, ctl);
-        }
-        consumer_sync();
-        n_el = ctl->out_cnt;
-        if (n_el <= kMergeCap) break;
-        // more logits reach the bound than the list can take (many equal values): keep the k best cells first
-        consumer_sync();
-        *reinterpret_cast<volatile int*>(&ctl->need_compact) = 1;
+        for (int j = 0; j < kPoolCap / 32; ++j) c += v[j] >= trial ? 1 : 0;   // empty slots hold 0, trial is never 0
+        const int total = __reduce_add_sync(0xffffffffu, c);
+        if (total >= k) pfx = trial;
+        if (total == k) break;
     }
-    if (mark) trace_mark(a, 2);
-    pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
-    // the segment's k best logits (or all, if fewer), in order
-    const int first_cta = (row * T) / Q, last_cta = (row * T + T - 1) / Q;
-    const int nseg = last_cta - first_cta + 1;
-    bool merge_here = true;
-    int kk = topk_sorted(m.list, n_el, d.k, m.sorted, ctl);
-    if (a.pair) {
-        // The row's CTAs are a cluster: CTA r > 0 puts its ordered candidates into part r - 1 of CTA 0's receive
-        // buffer, all arrive at the cluster's barrier (the only phase of it in this kernel: the producer warps arrived
-        // when they finished), and CTA 0 merges.  No global memory, no ticket.
-        const unsigned rank = cluster_cta_rank();
-        if (rank != 0u) {
-            const unsigned remote = cluster_map_shared(smem_u32(m.recv + (rank - 1u) * (unsigned)d.k), 0u);
-            for (int i = tid; i < kk; i += kThreads) cluster_store_u64(remote + 8u * (unsigned)i, m.sorted[i]);
-            if (tid == 0) cluster_store_u32(cluster_map_shared(smem_u32(&ctl->recv_n[rank]), 0u), (unsigned)kk);
+    return pfx;
+}
+
+// What a warp knows about its pool: entries, the value bound and the composite bound (0: none) they passed.
+struct PoolState {
+    int n;
+    float thr;
+    u64 wcomp;
+};
+// Makes room in a pool that is nearly full: refresh the bound, drop what it has overtaken; if the pool is still
+// too full (many equal values, or a stream that keeps rising), keep exactly the warp's k best - no logit of this
+// warp's stream below the k-th of them can be among the item's k best.
+__device__ __noinline__ PoolState compact_pool(u64* pool, int n, float thr, u64 wcomp, int k, SharedCtl* ctl) {
+    thr = fmaxf(thr, min_warp_bounds(ctl));
+    n = filter_pool(pool, n, max(comp_floor_of(thr), wcomp));
+    if (n > kPoolCap - 128) {
+        const u64 L = warp_kth_largest(pool, n, k);
+        n = filter_pool(pool, n, L);
+        wcomp = max(wcomp, L);
+        thr = fmaxf(thr, comp_floor_value(L));
+    }
+    return PoolState{n, thr, wcomp};
+}
+
+// More candidates than the list holds have survived the final bound (many equal values): the CTA finds the k-th
+// largest over all pools by bisection and the list gets exactly the k best.  All consumer threads call; returns the
+// number of entries of the list.
+__device__ __noinline__ int overflow_select(u64* pool, int pn, int k, u64* list, SharedCtl* ctl) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    u64 v[kPoolCap / 32];
+    u64 mn = ~0ull, mx = 0ull;
+#pragma unroll
+    for (int j = 0; j < kPoolCap / 32; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = i < pn ? pool[i] : 0ull;
+        if (i < pn) {
+            mn = min(mn, v[j]);
+            mx = max(mx, v[j]);
+        }
+    }
+    cta_minmax(mn, mx, ctl);
+    const u64 L = bisect_bound(k, mn, mx, ctl, [&](u64 t) {
+        int c = 0;
+#pragma unroll
+        for (int j = 0; j < kPoolCap / 32; ++j) c += v[j] >= t ? 1 : 0;
+        return c;
+    });
+    if (tid == 0) ctl->n_el = 0;
+    consumer_sync();
+    pn = filter_pool(pool, pn, L);
+    int base = 0;
+    if (lane == 0 && pn) base = atomicAdd(&ctl->n_el, pn);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    for (int i = lane; i < pn; i += 32)
+        if (base + i < kListCap) list[base + i] = pool[i];
+    consumer_sync();
+    return min(ctl->n_el, kListCap);
+}
+
+// ---- the set-up warp ------------------------------------------------------------------------------------------
+// Fetches work items (the first is the CTA's own number, the others come from the counter), reads the row's
+// descriptor, builds the bitmap of the item's penalised columns, and hands the item over: first to the copy warp
+// (as soon as the item's place is known), then to the consumers.
+__device__ __forceinline__ void setup_loop(const StreamArgs& a, const Smem& m) {
+    SharedCtl* ctl = m.ctl;
+    const int lane = threadIdx.x & 31;
+    int next_idx = (int)blockIdx.x;   // lane 0's copy counts
+    bool waited = !a.overlap;         // without launch overlap there is nothing to wait for
+    for (int seq = 0;; ++seq) {
+        const int b = seq & 1;
+        ItemCtx* ic = &ctl->item[b];
+        bool ok = true;
+        if (seq >= 2) ok = mbar_wait_bounded(&ctl->item_free[b], (unsigned)(((seq >> 1) - 1) & 1), ctl);
+        if (!ok && lane == 0) report_timeout(ctl, a.status);
+        const int idx = __shfl_sync(0xffffffffu, next_idx, 0);
+        if (!ok || idx >= a.n_items || *reinterpret_cast<volatile int*>(&ctl->abort)) {
+            if (lane == 0) {
+                ic->done = 1;
+                mbar_arrive(&ctl->item_posted[b]);
+                mbar_arrive(&ctl->item_ready[b]);
+            }
+            break;
+        }
+        const int chunk = idx / a.n_rows, row = idx - chunk * a.n_rows;
+        int tile0 = 0;
+        for (int c = 0; c < chunk; ++c) tile0 += a.chunk_len[c];
+        const int nt = a.chunk_len[chunk];
+        if (lane == 0) {
+            ic->done = 0;
+            ic->row = row;
+            ic->chunk = chunk;
+            ic->tile0 = tile0;
+            ic->ntiles = nt;
+            ic->row_ptr = a.logits + (a.row_ld >= 0 ? (int64_t)row * a.row_ld : a.rows[row].logits_off);
+            mbar_arrive(&ctl->item_posted[b]);   // the copies may start
+        }
+        // the row's descriptor: four lanes, 16 bytes each
+        if (lane < 4) reinterpret_cast<uint4*>(&ic->d)[lane] = __ldg(reinterpret_cast<const uint4*>(a.rows + row) + lane);
+        __syncwarp();
+        const RowDesc& d = ic->d;
+        if (lane == 0) {
+            // a bound the row's earlier chunks have left (never read before the previous launch is complete: it resets it)
+            unsigned key = 0u;
+            if (a.n_chunks > 1 && waited) key = __ldcg(a.row_bound + row);
+            ic->thr0 = key ? key_float(key) : -__int_as_float(0x7f800000);
+        }
+        if (d.flags & kRowPenalty) {
+            const int lo = tile0 * kTile, hi = min(a.n_vocab, (tile0 + nt) * kTile);
+            unsigned* bm = m.bitmap + (size_t)b * kItemBitmapWords;
+            const int words4 = ((hi - lo + 31) / 32 + 3) / 4;
+            for (int i = lane; i < words4; i += 32) reinterpret_cast<uint4*>(bm)[i] = make_uint4(0u, 0u, 0u, 0u);
+            __syncwarp();
+            const int32_t* h = a.hist + d.hist_begin;
+            const int n = d.hist_len;
+            for (int i0 = 0; i0 < n; i0 += 32 * 8) {   // eight loads in flight per lane
+                int c[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = i0 + 32 * u + lane;
+                    c[u] = i < n ? __ldg(h + i) - a.vocab_offset : -1;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (c[u] >= lo && c[u] < hi) atomicOr(&bm[(c[u] - lo) >> 5], 1u << ((c[u] - lo) & 31));
+            }
         }
         __syncwarp();
-        cluster_arrive_release();
-        merge_here = rank == 0u;
-        if (merge_here) {
-            cluster_wait_acquire();
-            if (a.pair == 2) {
-                // two lists: the rank of an entry is its place in its own list plus the number of entries of the other above it
-                const int n1 = min(*reinterpret_cast<volatile int*>(&ctl->recv_n[1]), d.k);
-                for (int e = tid; e < kk + n1; e += kThreads) {
-                    const bool mine = e < kk;
-                    const int i1 = mine ? e : e - kk;
-                    const u64 c = mine ? m.sorted[i1] : m.recv[i1];
-                    const u64* run = mine ? m.recv : m.sorted;
-                    int lo = 0, hi = mine ? n1 : kk;
-                    while (lo < hi) {
-                        const int mid = (lo + hi) >> 1;
-                        if (run[mid] > c) lo = mid + 1;
-                        else hi = mid;
-                    }
-                    if (i1 + lo < d.k) m.list[i1 + lo] = c;
-                }
-                consumer_sync();
-                kk = min(kk + n1, d.k);
-            } else {
-                // several lists: the same, summed over all the other lists
-                const int nl = a.pair;
-                if (tid == 0) ctl->recv_n[0] = kk;
-                consumer_sync();
-                int total = 0;
-                for (int s2 = 0; s2 < nl; ++s2) total += min(*reinterpret_cast<volatile int*>(&ctl->recv_n[s2]), d.k);
-                for (int e = tid; e < nl * d.k; e += kThreads) {
-                    const int s1 = e / d.k, i1 = e - s1 * d.k;
-                    if (i1 >= min(ctl->recv_n[s1], d.k)) continue;
-                    const u64 c = s1 == 0 ? m.sorted[i1] : m.recv[(s1 - 1) * d.k + i1];
-                    int rk = i1;
-                    for (int s2 = 0; s2 < nl; ++s2) {
-                        if (s2 == s1) continue;
-                        const u64* run = s2 == 0 ? m.sorted : m.recv + (s2 - 1) * d.k;   // descending: count its entries above c
-                        int lo = 0, hi = min(ctl->recv_n[s2], d.k);
-                        while (lo < hi) {
-                            const int mid = (lo + hi) >> 1;
-                            if (run[mid] > c) lo = mid + 1;
-                            else hi = mid;
-                        }
-                        rk += lo;
-                    }
-                    if (rk < d.k) m.list[rk] = c;
-                }
-                consumer_sync();
-                kk = min(total, d.k);
+        if (lane == 0) {
+            mbar_arrive(&ctl->item_ready[b]);   // releases the warp's writes to the waiting consumers
+            // the next item's number, fetched now so that it is there when this item has been handed over
+            if (!waited) {
+                pdl_wait_prior();   // the counter belongs to the previous launch until that is complete
+                waited = true;
             }
-            for (int i = tid; i < kk; i += kThreads) m.sorted[i] = m.list[i];
-            consumer_sync();
+            next_idx = (int)gridDim.x + (int)atomicAdd(a.work, 1u);
         }
-    } else if (nseg > 1) {
-        // A row with several segments: segment s publishes its ordered candidates in its own part of the row's
-        // scratch (entries [s * k, s * k + count), the count in entry kMergeCap - 1 - s), then draws a ticket; the
-        // CTA that draws the row's last ticket merges.  The planner keeps nseg * (k + 1) within kMergeCap.
-        const int seg = (int)blockIdx.x - first_cta;
-        u64* dst = reinterpret_cast<u64*>(a.scratch) + (size_t)row * kMergeCap;
-        if ((seg + 1) * d.k + nseg <= kMergeCap) {
-            for (int i = tid; i < kk; i += kThreads) dst[seg * d.k + i] = m.sorted[i];
-            if (tid == 0) dst[kMergeCap - 1 - seg] = (u64)kk;
-        } else if (tid == 0) {
-            atomicOr(a.status, kStatusMergeOverflow);
+    }
+    if (lane == 0) {
+        // the CTA that leaves last puts the counters back for the next launch (every CTA has drawn its last number)
+        if (!waited) pdl_wait_prior();
+        if (ticket_add_acq_rel(a.work + 1, 1u) == gridDim.x - 1u) {
+            a.work[0] = 0u;
+            a.work[1] = 0u;
+        }
+    }
+}
+
+// ---- the copy warp --------------------------------------------------------------------------------------------
+// One lane brings the items' tiles in, one 1-D bulk copy per tile (large copies: the copy engine's cost is per
+// request), into a ring of kStages slots.  A slot is refilled once all consumer warps have handed it back.
+__device__ __forceinline__ void copy_loop(const StreamArgs& a, const Smem& m) {
+    if ((threadIdx.x & 31) != 0) return;
+    SharedCtl* ctl = m.ctl;
+    const int V = a.n_vocab;
+    int it = 0;
+    for (int seq = 0;; ++seq) {
+        const int b = seq & 1;
+        if (!mbar_wait_bounded(&ctl->item_posted[b], (unsigned)((seq >> 1) & 1), ctl)) {
+            report_timeout(ctl, a.status);
+            return;
+        }
+        const ItemCtx* ic = &ctl->item[b];
+        if (ic->done) return;
+        const float* row_ptr = ic->row_ptr;
+        const int tile0 = ic->tile0, nt = ic->ntiles;
+        for (int j = 0; j < nt; ++j, ++it) {
+            const int slot = it % kStages;
+            // the first kStages tiles find their slots free; later ones wait for the consumers' hand-back
+            if (it >= kStages && !mbar_wait_bounded(&ctl->empty[slot], (unsigned)((it / kStages - 1) & 1), ctl)) {
+                report_timeout(ctl, a.status);
+                return;
+            }
+            const int col0 = (tile0 + j) * kTile;
+            const int len = min(kTile, V - col0);   // >= 1
+            const float* src = row_ptr + col0;
+            float* dst = m.stage + (size_t)slot * kTile;
+            const unsigned bytes = (unsigned)(len & ~3) * 4u;
+            for (int e = len & ~3; e < len; ++e) dst[e] = src[e];   // ragged tail by plain loads
+            if (bytes) {
+                fence_proxy_async_smem();   // generic-proxy accesses to this slot (the consumers' patches) precede the async write
+                mbar_expect_tx(&ctl->full[slot], bytes);
+                bulk_g2s(dst, src, bytes, &ctl->full[slot]);
+            } else {
+                mbar_arrive(&ctl->full[slot]);
+            }
+        }
+    }
+}
+
+// ---- the end of an item ---------------------------------------------------------------------------------------
+// All consumer threads call it once they have looked at the item's last tile: the final bound, the warps'
+// surviving candidates gathered into the list, the k best in order, published; in the CTA that publishes the
+// row's last chunk, the merge of the row's lists and the epilogue.
+__device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64* pool, int pn, float thr, u64 wcomp, float run_max, int row,
+                                         int chunk) {
+    SharedCtl* ctl = m.ctl;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int k = ctl->cur.k;
+    const float wb = warp_bound(run_max, k);
+    if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
+    consumer_sync();
+    thr = fmaxf(thr, min_warp_bounds(ctl));
+    pn = filter_pool(pool, pn, max(comp_floor_of(thr), wcomp));
+    int base = 0;
+    if (lane == 0 && pn) base = atomicAdd(&ctl->n_el, pn);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    if (base + pn <= kListCap)
+        for (int i = lane; i < pn; i += 32) m.list[base + i] = pool[i];
+    consumer_sync();
+    int n_el = ctl->n_el;
+    if (n_el > kListCap) n_el = overflow_select(pool, pn, k, m.list, ctl);
+    trace_mark(a, 5);
+    int kk = topk_sorted(m.list, n_el, k, m.sorted, ctl);
+    if (tid == 0) ctl->n_el = 0;   // for the next item (barriers follow)
+    trace_mark(a, 6);
+    pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
+    bool finish_here = true;
+    if (a.n_chunks > 1) {
+        // chunk c of a row publishes its ordered candidates at entries [c * k, c * k + count) of the row's scratch, the
+        // count in entry stride - 1 - c, and leaves the bound they prove for the row's later chunks; then it draws a
+        // ticket, and the CTA that draws the row's last ticket merges.  The planner keeps chunks * (k + 1) within the stride.
+        u64* dst = reinterpret_cast<u64*>(a.scratch) + (size_t)row * (size_t)a.scratch_stride;
+        for (int i = tid; i < kk; i += kThreads) dst[chunk * k + i] = m.sorted[i];
+        if (tid == 0) {
+            dst[a.scratch_stride - 1 - chunk] = (u64)kk;
+            if (kk == k) atomicMax(a.row_bound + row, (unsigned)(m.sorted[k - 1] >> 32));
         }
         consumer_sync();   // orders the CTA's stores before the ticket, whose release publishes them to the device
-        if (tid == 0) ctl->last = (ticket_add_acq_rel(&a.ticket[row], 1u) == (unsigned)(nseg - 1)) ? 1 : 0;
+        if (tid == 0) ctl->last = (ticket_add_acq_rel(a.ticket + row, 1u) == (unsigned)(a.n_chunks - 1)) ? 1 : 0;
         consumer_sync();
-        merge_here = ctl->last != 0;
-        if (merge_here) {   // all segments of the row have published (L2 reads, never L1)
-            if (tid == 0) a.ticket[row] = 0u;   // ready for the next launch
-            if (nseg <= kNumWarps) {
-                // few ordered lists: the rank of an entry is its place in its own list plus, for every other list,
-                // the number of entries above it (binary search); the lists keep their places in shared memory
-                // (counts and entries are read in one go; entries past a list's count are stale and ignored below)
-                const int span = nseg * d.k;
-                if (tid < nseg) ctl->wcount[tid] = min((int)__ldcg(dst + kMergeCap - 1 - tid), d.k);
-                for (int e = tid; e < span; e += kThreads) m.list[e] = __ldcg(dst + e);
-                consumer_sync();
-                int total = 0;
-                for (int s2 = 0; s2 < nseg; ++s2) total += ctl->wcount[s2];
-                for (int e = tid; e < span; e += kThreads) {
-                    const int s1 = e / d.k, i1 = e - s1 * d.k;
-                    if (i1 >= ctl->wcount[s1]) continue;
-                    const u64 c = m.list[e];
-                    int rank = i1;
-                    for (int s2 = 0; s2 < nseg; ++s2) {
-                        if (s2 == s1) continue;
-                        const u64* run = m.list + s2 * d.k;   // descending: count its entries above c
-                        int lo = 0, hi = ctl->wcount[s2];
-                        while (lo < hi) {
-                            const int mid = (lo + hi) >> 1;
-                            if (run[mid] > c) lo = mid + 1;
-                            else hi = mid;
-                        }
-                        rank += lo;
-                    }
-                    if (rank < d.k) m.sorted[rank] = c;
-                }
-                kk = min(total, d.k);
-                consumer_sync();
-            } else {   // many short lists: gather them into one list and order that
-                int total = 0;
-                for (int s2 = 0; s2 < nseg; ++s2) {
-                    const int n2 = min((int)__ldcg(dst + kMergeCap - 1 - s2), d.k);
-                    for (int i = tid; i < n2; i += kThreads) m.list[total + i] = __ldcg(dst + s2 * d.k + i);
-                    total += n2;
-                }
-                consumer_sync();
-                kk = topk_sorted(m.list, total, d.k, m.sorted, ctl);
+        finish_here = ctl->last != 0;
+        trace_mark(a, 7);
+        if (finish_here) {   // all chunks of the row have published (L2 reads, never L1)
+            if (tid == 0) {
+                a.ticket[row] = 0u;   // ready for the next launch
+                a.row_bound[row] = 0u;
             }
+            const int nl = a.n_chunks;
+            if (tid < nl) ctl->wcount[tid] = min((int)__ldcg(dst + a.scratch_stride - 1 - tid), k);
+            const int span = nl * k;
+            u64* lists = m.pools;   // the pools are idle until the next item starts
+            for (int e = tid; e < span; e += kThreads) lists[e] = __ldcg(dst + e);
+            consumer_sync();
+            kk = merge_sorted_lists(lists, nl, k, m.sorted, ctl);
+            trace_mark(a, 8);
         }
     }
-    if (mark) trace_mark(a, 5);
-    if (merge_here) {
-        const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index};
-        row_epilogue(m.sorted, kk, rt, reinterpret_cast<double*>(m.list), ctl, tout);
+    if (finish_here) {
+        const RowDesc& d = ctl->cur;
+        const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
+        const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index, a.scan_sums};
+        row_epilogue(m.sorted, kk, rt, reinterpret_cast<double*>(m.list), tout);
+        trace_mark(a, 9);
     }
-    consumer_sync();
-    if (mark) trace_mark(a, 6);
+    consumer_sync();   // the list, the ordered candidates and the pools may be written again
 }
 
 template <bool SOFTCAP>
@@ -707,211 +488,164 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
     const Smem m = smem_view();
     SharedCtl* ctl = m.ctl;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int T = a.tiles_per_row, V = a.n_vocab;
-    const int t_begin = blockIdx.x * a.tiles_per_cta;
-    const int t_end = min(t_begin + a.tiles_per_cta, a.total_tiles);
-    const int nt = t_end - t_begin;
+    const int V = a.n_vocab;
     // With launch overlap on, the next launch in the stream may start as soon as this one leaves room; like this one
-    // it waits for its predecessor before it writes anything (segment_end), so only the reading of logits overlaps.
+    // it waits for its predecessor before it writes anything or draws from the work counter, so only the reading of
+    // a CTA's first item overlaps.
     pdl_launch_dependents();
-    if (nt <= 0) return;
-    trace_mark(a, 0);
-    if (a.write_back) pdl_wait_prior();   // this launch stores into the logits while it streams
-
     if (tid == 0) {   // one thread initialises every barrier, then makes the initialisation visible to the copy engine
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(&ctl->full[s], 1u);                  // the producer's arrive (+ the copy's bytes)
+            mbar_init(&ctl->full[s], 1u);                  // the copy warp's arrive (+ the copy's bytes)
             mbar_init(&ctl->empty[s], (unsigned)kWarps);   // one arrive per consumer warp
         }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctl->item_posted[b], 1u);
+            mbar_init(&ctl->item_ready[b], 1u);
+            mbar_init(&ctl->item_free[b], (unsigned)kWarps);
+        }
         ctl->abort = 0;
-        ctl->need_compact = 0;
+        ctl->n_el = 0;
         fence_mbar_init();
+        if (a.trace) {
+            for (int s = 0; s < 16; ++s) a.trace[(size_t)blockIdx.x * 16 + s] = 0ull;
+            a.trace[(size_t)blockIdx.x * 16 + 0] = global_timer_ns();
+        }
     }
-    __syncthreads();   // the only barrier the producer warp takes part in
-    if (warp == kWarps) {
-        if (a.bulk_ok) producer_loop(a, m.stage, ctl, t_begin, nt);
-        __syncwarp();
-        if (a.pair) cluster_arrive_release();   // every thread of the cluster arrives exactly once (see segment_end)
+    __syncthreads();   // the only barrier all warps take part in
+    if (warp == kSetupWarp) {
+        setup_loop(a, m);
         return;
     }
-    trace_mark(a, 1);
+    if (warp == kCopyWarp) {
+        if (a.bulk_ok) copy_loop(a, m);
+        return;
+    }
+    if (a.write_back) pdl_wait_prior();   // this launch stores into the logits while it streams
 
     // ------------------------------------------------------------------------------------------ consumers
-    // The loop over a segment's tiles contains no call: everything rare (re-selections, the end of the segment)
-    // happens outside it, so that the loop's state stays in registers.
     const float ninf = -__int_as_float(0x7f800000);
-    unsigned* myq = m.queue + tid;   // entry i of this lane's queue is myq[i * kThreads]
-    const unsigned q_base = smem_u32(myq);
+    const unsigned lt = (1u << lane) - 1u;
+    u64* const pool = m.pools + (size_t)warp * kPoolCap;
     float* const st_warp = m.stage + warp * kWTile;
-    int it = 0;                            // tiles of this CTA looked at so far (the position in the ring)
-    for (int tile = t_begin; tile < t_end;) {
-        // ---- a new segment starts (all consumer warps are here together: kernel start or after a segment end)
-        const int row = tile / T, j0 = tile - row * T;
-        const int seg_nt = min(t_end - tile, T - j0);
-        const int seg_lo = j0 * kTile;
-        const int seg_hi = min(V, (j0 + seg_nt) * kTile);
-        const RowDesc d = a.rows[row];
-        const float* row_ptr = a.logits + d.logits_off;
+    int it = 0;        // tiles of this CTA looked at so far (the position in the ring)
+    int n_items = 0;
+    for (int seq = 0;; ++seq) {
+        const int b = seq & 1;
+        const ItemCtx* ic = &ctl->item[b];
+        if (!mbar_wait_bounded(&ctl->item_ready[b], (unsigned)((seq >> 1) & 1), ctl) && lane == 0) report_timeout(ctl, a.status);
+        if (tid == 0 && !ctl->abort && !ic->done) ctl->cur = ic->d;   // the end-of-item work outlives the hand-over slot
+        consumer_sync();   // every warp takes the same way out
+        if (*reinterpret_cast<volatile int*>(&ctl->abort) || ic->done) break;
+        const int row = ic->row, chunk = ic->chunk, tile0 = ic->tile0, nt = ic->ntiles;
+        const float* row_ptr = ic->row_ptr;
         float* wb_row = a.write_back ? const_cast<float*>(row_ptr) : nullptr;
-        const float pen = d.penalty;
-        const int row_k = d.k;
-        const bool has_pen = (d.flags & kRowPenalty) != 0;
-        if (tid == 0) {   // what the rendez-vous code needs to know about the segment
-            SegCtx& sc = ctl->seg;
-            sc.row = row_ptr;
-            sc.pen = pen;
-            sc.cap = a.softcap;
-            sc.has_pen = has_pen ? 1 : 0;
-            sc.id_base = a.vocab_offset;
-            sc.seg_lo = seg_lo;
-            sc.n_vocab = V;
-            sc.vec_ok = a.bulk_ok;
-            sc.k = row_k;
-            sc.final_in_mem = a.write_back;
-        }
-        if (has_pen) {   // bitmap of the penalised columns of this segment
-            const int words = (seg_hi - seg_lo + 31) >> 5;
-            for (int i = tid; i < words; i += kThreads) m.bitmap[i] = 0u;
-            consumer_sync();
-            const int32_t* h = a.hist + d.hist_begin;
-            for (int i = tid; i < d.hist_len; i += kThreads) {
-                const int c = h[i] - a.vocab_offset;
-                if (c >= seg_lo && c < seg_hi) atomicOr(&m.bitmap[(c - seg_lo) >> 5], 1u << ((c - seg_lo) & 31));
-            }
-        }
-        consumer_sync();
+        const float pen = ic->d.penalty;
+        const int k = ic->d.k;
+        const bool has_pen = (ic->d.flags & kRowPenalty) != 0;
+        const unsigned* bitmap = m.bitmap + (size_t)b * kItemBitmapWords;
+        const int item_lo = tile0 * kTile;
+        float thr = ic->thr0, run_max = ninf;
+        u64 wcomp = 0ull;   // composite bound of this warp after it had to keep its k best (0: none)
+        int pn = 0;         // entries in this warp's pool (the same value in every lane)
+        int col0 = item_lo + warp * kWTile;   // first column of this warp's part of the tile
+        if (seq == 0) trace_mark(a, 1);
 
-        float thr_f = ninf, run_max = ninf;
-        u64 thr_comp = 0ull;
-        int qn = 0;       // cells in this lane's queue
-        int nkept = 0;    // cells in the survivors' list (the same value in every thread)
-        int s = 0;        // tiles of the segment this warp has looked at
-        int col0 = seg_lo + warp * kWTile;   // first column of this warp's part of tile s
-
-        for (;;) {
-            int reason = 0;   // why the loop over the tiles was left: 0 = segment done, 1 = a queue of this warp is nearly full,
-                              // 2 = another warp asked for a re-selection while this one was waiting for a copy
-            unsigned slot = (unsigned)it % kStages, par = ((unsigned)it / kStages) & 1u;   // ring slot of tile `it` and its phase
-            for (; s < seg_nt; ++s, ++it, col0 += kTile, slot = (slot + 1u) % kStages, par ^= (slot == 0u ? 1u : 0u)) {
-                if (__any_sync(0xffffffffu, qn > kLaneQueue - 4)) {
-                    reason = 1;
-                    break;
-                }
-                float* st = st_warp + slot * kTile;              // this warp's part of the CTA tile
-                const int len = min(kWTile, V - col0);            // may be <= 0 in a row's last tile
-                if (a.bulk_ok) {
-                    // ---- wait for the CTA tile's copy.  A warp that has to wait also answers re-selection requests of
-                    // other warps: a requester sits at the barrier of cta_event, and the ring only moves when every warp does.
-                    bool landed = mbar_try_wait(&ctl->full[slot], par);
-                    if (!landed) {
-                        const long long lim = ctl->abort ? 2000ll : kCopyWaitCycles;
-                        const long long t0 = clock64();
-                        for (;;) {
-                            if (mbar_try_wait(&ctl->full[slot], par)) {
-                                landed = true;
-                                break;
-                            }
-                            if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&ctl->need_compact) != 0)) break;
-                            if (clock64() - t0 > lim) {   // the copy never landed: report, carry on with what is there
-                                ctl->abort = 1;
-                                atomicOr(a.status, kStatusCopyTimeout);
-                                landed = true;
-                                break;
-                            }
-                        }
-                        if (!landed) {
-                            reason = 2;
-                            break;
-                        }
-                    }
-                } else if (len > 0) {   // rows not on 16-byte boundaries: the warp loads its tile itself
-                    const float* src = row_ptr + col0;
-                    for (int e = lane; e < len; e += 32) st[e] = src[e];
-                    __syncwarp();
-                }
-                if (SOFTCAP) {
-                    if (len > 0) softcap_tile(st, len, a.softcap, wb_row ? wb_row + col0 : nullptr);
-                }
-                if (has_pen && len > 0) patch_tile(st, len, col0, seg_lo, pen, m.bitmap, wb_row);
-                if (len < kWTile) {   // what lies past the end of a ragged row is made NaN: never a maximum, never reaches a bound
-                    for (int e = max(len, 0) + lane; e < kWTile; e += 32) st[e] = __int_as_float(0x7fc00000);
-                    __syncwarp();
-                }
-                // ---- look: the lane's four cells go to registers (four independent 16-byte loads)
-                const float4* st4 = reinterpret_cast<const float4*>(st);
-                const float4 x0 = st4[lane], x1 = st4[lane + 32], x2 = st4[lane + 64], x3 = st4[lane + 96];
-                const float m0 = fmaxf(max3(x0.x, x0.y, x0.z), x0.w);
-                const float m1 = fmaxf(max3(x1.x, x1.y, x1.z), x1.w);
-                const float m2 = fmaxf(max3(x2.x, x2.y, x2.z), x2.w);
-                const float m3 = fmaxf(max3(x3.x, x3.y, x3.z), x3.w);
-                run_max = fmaxf(max3(run_max, m0, m1), fmaxf(m2, m3));
+        for (int s = 0; s < nt; ++s, ++it, col0 += kTile) {
+            const unsigned slot = (unsigned)it % kStages, par = ((unsigned)it / kStages) & 1u;
+            float* st = st_warp + slot * kTile;              // this warp's part of the CTA tile
+            const int len = min(kWTile, V - col0);            // may be <= 0 in a row's last tile
+            if (a.bulk_ok) {
+                if (!mbar_wait_bounded(&ctl->full[slot], par, ctl) && lane == 0) report_timeout(ctl, a.status);   // carry on with what is there
+            } else if (len > 0) {   // rows not on 16-byte boundaries: the warp loads its part of the tile itself
+                const float* src = row_ptr + col0;
+                for (int e = lane; e < len; e += 32) st[e] = src[e];
                 __syncwarp();
-                if (lane == 0 && a.bulk_ok) mbar_arrive(&ctl->empty[slot]);   // the slot goes back to the producer
-
-                // ---- the admission bound: set at the segment's first tile (all warps must have posted: one barrier per
-                // segment), then refreshed without a barrier at tiles 1, 2, 4, 8, ... of the segment
-                if ((s & (s - 1)) == 0) {   // s = 0, 1, 2, 4, 8, ...
-                    const float wb = warp_bound(run_max, row_k);
-                    if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
-                    if (s == 0) consumer_sync();
-                    else __syncwarp();
-                    thr_f = fmaxf(thr_f, min_warp_bounds(ctl));
-                }
-
-                // ---- note the cells whose maximum reaches the bound (padding past the end of a row never does)
-                const unsigned loc = (unsigned)s << 2;
-                if (thr_comp == 0ull) {
-                    note_cell_if(m0, thr_f, loc, q_base, qn);
-                    note_cell_if(m1, thr_f, loc | 1u, q_base, qn);
-                    note_cell_if(m2, thr_f, loc | 2u, q_base, qn);
-                    note_cell_if(m3, thr_f, loc | 3u, q_base, qn);
-                } else {   // after a re-selection: ties at the bound are settled by token id
-                    const int id_lane = col0 + 4 * lane + a.vocab_offset;
-                    if (m0 >= thr_f && make_comp(m0, id_lane) >= thr_comp) myq[(qn++) * kThreads] = make_entry(m0, loc);
-                    if (m1 >= thr_f && make_comp(m1, id_lane + 128) >= thr_comp) myq[(qn++) * kThreads] = make_entry(m1, loc | 1u);
-                    if (m2 >= thr_f && make_comp(m2, id_lane + 256) >= thr_comp) myq[(qn++) * kThreads] = make_entry(m2, loc | 2u);
-                    if (m3 >= thr_f && make_comp(m3, id_lane + 384) >= thr_comp) myq[(qn++) * kThreads] = make_entry(m3, loc | 3u);
-                }
             }
-            if (reason == 0) break;
-            // ---- a re-selection: the CTA keeps the k best of the cells noted so far, every queue becomes empty
-            if (reason == 1) {   // first drop what the bound has overtaken: that alone makes room, as a rule
-                qn = drop_stale(myq, qn, thr_f);
-                if (!__any_sync(0xffffffffu, qn > kLaneQueue - 4)) continue;
-                *reinterpret_cast<volatile int*>(&ctl->need_compact) = 1;
+            if (seq == 0 && s == 0) trace_mark(a, 2);
+            if (SOFTCAP) {
+                if (len > 0) softcap_tile(st, len, a.softcap, wb_row ? wb_row + col0 : nullptr);
             }
-            const int ev = cta_event<SOFTCAP>(qn, nkept, run_max, thr_f);
-            if (event_happened(ev)) {
-                qn = 0;
-                nkept = event_nkept(ev);
-                const u64 eb = ctl->ev_bound;
-                if (eb) {
-                    thr_comp = max(thr_comp, eb);
-                    thr_f = fmaxf(thr_f, comp_floor_value(eb));
+            if (has_pen && len > 0) patch_tile(st, len, col0, item_lo, pen, bitmap, wb_row);
+            if (len < kWTile) {   // what lies past the end of a ragged row is made NaN: never a maximum, never reaches a bound
+                for (int e = max(len, 0) + lane; e < kWTile; e += 32) st[e] = __int_as_float(0x7fc00000);
+                __syncwarp();
+            }
+            // ---- look: the lane's four cells go to registers (four independent 16-byte loads)
+            const float4* st4 = reinterpret_cast<const float4*>(st);
+            const float4 x0 = st4[lane], x1 = st4[lane + 32], x2 = st4[lane + 64], x3 = st4[lane + 96];
+            const float m0 = fmaxf(max3(x0.x, x0.y, x0.z), x0.w);
+            const float m1 = fmaxf(max3(x1.x, x1.y, x1.z), x1.w);
+            const float m2 = fmaxf(max3(x2.x, x2.y, x2.z), x2.w);
+            const float m3 = fmaxf(max3(x3.x, x3.y, x3.z), x3.w);
+            const float mt = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+            run_max = fmaxf(run_max, mt);
+            __syncwarp();
+            if (lane == 0 && a.bulk_ok) mbar_arrive(&ctl->empty[slot]);   // the slot goes back to the copy warp
+
+            // ---- the admission bound: set at the item's first tile (all warps must have posted: one barrier per
+            // item), then refreshed without a barrier at tiles 1, 2, 4 of the item
+            if ((s & (s - 1)) == 0) {   // s = 0, 1, 2, 4, 8, ...
+                const float wb = warp_bound(run_max, k);
+                if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
+                if (s == 0) consumer_sync();
+                else __syncwarp();
+                thr = fmaxf(thr, min_warp_bounds(ctl));
+            }
+
+            // ---- admit the logits that reach the bound (padding past the end of a row never does)
+            if (__any_sync(0xffffffffu, mt >= thr)) {
+                const int id_lane = col0 + 4 * lane + a.vocab_offset;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 x = q == 0 ? x0 : q == 1 ? x1 : q == 2 ? x2 : x3;
+                    const float mq = q == 0 ? m0 : q == 1 ? m1 : q == 2 ? m2 : m3;
+                    if (!__any_sync(0xffffffffu, mq >= thr)) continue;
+                    if (pn > kPoolCap - 128) {
+                        const PoolState ps = compact_pool(pool, pn, thr, wcomp, k, ctl);
+                        pn = ps.n;
+                        thr = ps.thr;
+                        wcomp = ps.wcomp;
+                    }
+                    const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const u64 c = make_comp(xs[e], id_lane + 128 * q + e);
+                        const bool ok = xs[e] >= thr && c >= wcomp;
+                        const unsigned be = __ballot_sync(0xffffffffu, ok);
+                        if (ok) pool[pn + __popc(be & lt)] = c;
+                        pn += __popc(be);
+                    }
                 }
             }
         }
-        segment_end<SOFTCAP>(a, row, qn, nkept, thr_f, run_max, tile + seg_nt >= t_end);
-        tile += seg_nt;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->item_free[b]);   // descriptor slot and bitmap go back to the set-up warp
+        ++n_items;
+        trace_mark(a, 4);
+        item_end(a, m, pool, pn, thr, wcomp, run_max, row, chunk);
     }
+    trace_set(a, 3, (u64)n_items);
+    trace_mark(a, 10);
 }
 
 // Merge of per-shard candidate lists (vocabulary-sharded mode): one CTA per row gathers n_lists sorted lists of
-// up to kMaxK composites each (already in this device's memory) and runs the row epilogue.
-__global__ void __launch_bounds__(kThreads, 1) merge_lists_kernel(const u64* lists, const int32_t* list_n, int n_lists, int n_rows,
-                                                                 const RowDesc* rows, int32_t* tokens, int32_t* kept_ids,
-                                                                 double* kept_pr, int32_t* kept_n, unsigned* status) {
+// up to kMaxK composites each (already in this device's memory, list g of row r at lists + (g * n_rows + r) * list_stride)
+// and runs the row epilogue.
+__global__ void __launch_bounds__(kThreads, 1) merge_lists_kernel(const u64* lists, const int32_t* list_n, int n_lists, int list_stride, int n_rows,
+                                                                 const RowDesc* rows, int32_t* tokens, int32_t* kept_ids, double* kept_pr,
+                                                                 int32_t* kept_n, unsigned* status, int scan_sums) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     u64* buf = reinterpret_cast<u64*>(smem_raw);
     u64* out = buf + kMergeCap;
-    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(out + kMaxK);
+    double* work = reinterpret_cast<double*>(out + kMaxK);
+    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(work + 2 * kMaxK);
     const int row = blockIdx.x, tid = threadIdx.x;
     if (row >= n_rows) return;
     const RowDesc d = rows[row];
     int total = 0;   // the same in every thread
     for (int g = 0; g < n_lists; ++g) {
-        const int n = min(list_n[(size_t)g * n_rows + row], kMaxK);
-        const u64* src = lists + ((size_t)g * n_rows + row) * kMaxK;
+        const int n = min(min(list_n[(size_t)g * n_rows + row], kMaxK), list_stride);
+        const u64* src = lists + ((size_t)g * n_rows + row) * (size_t)list_stride;
         if (total + n <= kMergeCap) {
             for (int i = tid; i < n; i += kThreads) buf[total + i] = src[i];
             total += n;
@@ -921,16 +655,30 @@ __global__ void __launch_bounds__(kThreads, 1) merge_lists_kernel(const u64* lis
     }
     consumer_sync();
     const TailOut tout{tokens, kept_ids, kept_pr, kept_n, nullptr, nullptr, status};
-    const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index};
-    const int kk = topk_sorted(buf, total, d.k, out, ctl);
-    row_epilogue(out, kk, rt, reinterpret_cast<double*>(buf), ctl, tout);
+    const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k_global, d.flags, d.out_index, scan_sums};
+    const int kk = topk_sorted(buf, total, d.k_global, out, ctl);
+    row_epilogue(out, kk, rt, work, tout);
+}
+
+// Write-back for callers whose logits live in host memory: after a launch with write-back on the device copy, the
+// values at the rows' window ids (the only entries the penalty touches) are gathered, one float per window id in
+// window order, so that the host can store them into the caller's rows without redoing any arithmetic.
+__global__ void gather_patched_kernel(const float* logits, const RowDesc* rows, int n_rows, const int32_t* hist, int n_vocab, int vocab_offset,
+                                      float* out) {
+    const int row = blockIdx.x;
+    if (row >= n_rows) return;
+    const RowDesc d = rows[row];
+    for (int i = threadIdx.x; i < d.hist_len; i += blockDim.x) {
+        const int c = hist[d.hist_begin + i] - vocab_offset;
+        out[d.gather_off + i] = (c >= 0 && c < n_vocab) ? logits[d.logits_off + c] : 0.0f;
+    }
 }
 
 }  // namespace
 
 size_t stream_kernel_smem_bytes() { return kSmemTotal; }
 
-constexpr size_t kSmemMerge = (size_t)(kMergeCap + kMaxK) * sizeof(u64) + sizeof(SharedCtl);   // candidate list, ordered candidates, control
+constexpr size_t kSmemMerge = (size_t)(kMergeCap + kMaxK) * sizeof(u64) + 2 * (size_t)kMaxK * sizeof(double) + sizeof(SharedCtl);
 
 // Per-device set-up (the current device): opt in to the large dynamic shared memory; report resident CTAs per SM.
 int prepare_device_kernels(int* ctas_per_sm) {
@@ -948,18 +696,11 @@ int prepare_device_kernels(int* ctas_per_sm) {
 }
 
 int launch_stream_kernel(const StreamArgs& a, int grid, void* stream) {
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     int n = 0;
     if (a.overlap) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
-        ++n;
-    }
-    if (a.pair) {
-        attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = (unsigned)a.pair;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = 1;
         ++n;
     }
     cudaLaunchConfig_t cfg{};
@@ -973,27 +714,101 @@ int launch_stream_kernel(const StreamArgs& a, int grid, void* stream) {
     return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<false>, a);
 }
 
-// Resident histories: appends every row's new token to its stream's history on the device.  A descriptor's pad
-// words hold the index of the id pool where the token goes (negative: nowhere).
+// Resident histories: appends every row's new token to its stream's history on the device.  A row's window always
+// ends where its history ends, so the token goes to entry hist_begin + hist_len of the id pool.
 namespace {
 __global__ void append_tokens_kernel(const RowDesc* rows, int n_rows, const int32_t* tokens, int32_t* pool) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n_rows) return;
-    const int64_t at = ((int64_t)rows[r].pad[1] << 32) | (uint32_t)rows[r].pad[0];
-    if (at >= 0) pool[at] = tokens[rows[r].out_index];
+    if (rows[r].flags & kRowAppend) pool[rows[r].hist_begin + rows[r].hist_len] = tokens[rows[r].out_index];
 }
 }  // namespace
+
+// Resident verification windows.  Before the launch: draft r of a stream is the last id of row r's window, and goes
+// to that place of the id pool.  After it: per stream the accept loop of src/server.cpp:630-636 over the sampled
+// tokens (accept while the token equals the next draft, at most `lim` rows), and the last accepted token is stored
+// where the history will end - the confirmed drafts before it are in place already.  Table entry of a stream:
+// first row, rows m, limit, unused, end of the history in the pool (two words), then the m - 1 drafts.
+namespace {
+__global__ void write_drafts_kernel(const RowDesc* rows, int n_rows, int32_t* pool) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    if (rows[r].flags & kRowDraft) pool[rows[r].hist_begin + rows[r].hist_len - 1] = rows[r].gather_off;
+}
+__global__ void accept_windows_kernel(const int32_t* table, int n_streams, const int32_t* tokens, int32_t* pool) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_streams) return;
+    const int32_t* t = table + (size_t)i * kWindowTableInts;
+    const int r0 = t[0], m = t[1], lim = t[2];
+    const int64_t end = ((int64_t)t[5] << 32) | (uint32_t)t[4];
+    int acc = 0;
+    for (int r = 0; r < lim; ++r) {
+        acc = r + 1;
+        if (r + 1 < m && tokens[r0 + r] == t[6 + r]) continue;
+        break;
+    }
+    if (acc > 0) pool[end + acc - 1] = tokens[r0 + acc - 1];
+}
+}  // namespace
+
+int launch_write_drafts(const RowDesc* rows, int n_rows, int32_t* pool, void* stream) {
+    write_drafts_kernel<<<(n_rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(rows, n_rows, pool);
+    return (int)cudaGetLastError();
+}
+int launch_accept_windows(const int32_t* table, int n_streams, const int32_t* tokens, int32_t* pool, void* stream) {
+    accept_windows_kernel<<<(n_streams + 63) / 64, 64, 0, static_cast<cudaStream_t>(stream)>>>(table, n_streams, tokens, pool);
+    return (int)cudaGetLastError();
+}
 
 int launch_append_tokens(const RowDesc* rows, int n_rows, const int32_t* tokens, int32_t* pool, void* stream) {
     append_tokens_kernel<<<(n_rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(rows, n_rows, tokens, pool);
     return (int)cudaGetLastError();
 }
 
-int launch_merge_lists(const void* lists, const int32_t* list_n, int n_lists, int n_rows, const RowDesc* rows, int32_t* tokens,
-                       int32_t* kept_ids, double* kept_pr, int32_t* kept_n, uint32_t* status, void* stream) {
+int launch_merge_lists(const void* lists, const int32_t* list_n, int n_lists, int list_stride, int n_rows, const RowDesc* rows, int32_t* tokens,
+                       int32_t* kept_ids, double* kept_pr, int32_t* kept_n, uint32_t* status, int scan_sums, void* stream) {
     merge_lists_kernel<<<n_rows, kThreads, kSmemMerge, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const u64*>(lists), list_n, n_lists, n_rows, rows, tokens, kept_ids, kept_pr, kept_n, status);
+        static_cast<const u64*>(lists), list_n, n_lists, list_stride, n_rows, rows, tokens, kept_ids, kept_pr, kept_n, status, scan_sums);
     return (int)cudaGetLastError();
+}
+
+int launch_gather_patched(const float* logits, const RowDesc* rows, int n_rows, const int32_t* hist, int n_vocab, int vocab_offset,
+                          float* out, void* stream) {
+    gather_patched_kernel<<<n_rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, rows, n_rows, hist, n_vocab, vocab_offset, out);
+    return (int)cudaGetLastError();
+}
+
+// The chunk schedule of a launch: how every row is cut into work items.  `slots` = CTAs that run at once, `stride` =
+// entries of a row's scratch.  Returns the number of chunks (0: the rows cannot be scheduled within the scratch).
+int plan_chunks(int n_rows, int n_vocab, int kmax, int slots, int64_t stride, uint8_t* chunk_len) {
+    const int T = (n_vocab + kTile - 1) / kTile;
+    const int64_t by_scratch = stride / ((kmax > 1 ? kmax : 1) + 1);
+    const int max_chunks = (int)(by_scratch < kMaxChunks ? by_scratch : kMaxChunks);
+    if (max_chunks < 1) return 0;
+    const double per_cta = (double)n_rows * T / (slots > 1 ? slots : 1);   // tiles a CTA streams on average
+    // About three items per CTA keep the dynamic hand-out balanced; an item never spans more than kItemTilesMax tiles.
+    int q = (int)(per_cta / 3.0 + 0.5);
+    q = q < 1 ? 1 : (q > kItemTilesMax ? kItemTilesMax : q);
+    while ((T + q - 1) / q > max_chunks && q < kItemTilesMax) ++q;
+    if ((T + q - 1) / q > max_chunks) return 0;
+    // The last tiles of a row are cut into pieces that halve down to single tiles: the items the CTAs draw last are
+    // short, so the CTAs finish together (pointless when a CTA works on one item only).
+    int taper = (per_cta > q && q > 1) ? (q < T / 4 ? q : T / 4) : 0;
+    for (;;) {
+        int n = 0;
+        const int main_tiles = T - taper;
+        const int n_main = (main_tiles + q - 1) / q;
+        for (int i = 0; i < n_main; ++i) chunk_len[n++] = (uint8_t)(main_tiles / n_main + (i < main_tiles % n_main ? 1 : 0));
+        for (int t = taper; t > 0 && n < kMaxChunks;) {
+            const int h = t > 1 ? (t + 1) / 2 : 1;
+            chunk_len[n++] = (uint8_t)h;
+            t -= h;
+            if (t > 0 && n == kMaxChunks) n = kMaxChunks + 1;
+        }
+        if (n <= max_chunks) return n;
+        if (taper == 0) return 0;
+        taper = 0;   // no room for the short pieces
+    }
 }
 
 }  // namespace fsb
@@ -1005,14 +820,15 @@ namespace fsb {
 namespace {
 
 constexpr int kStaticMaxRows = FSB_STATIC_MAX_ROWS;
-constexpr size_t kStaticRowsOff = 0;                                                       // RowDesc[kStaticMaxRows]
-constexpr size_t kStaticFillOff = kStaticRowsOff + sizeof(RowDesc) * kStaticMaxRows;       // fill[], ticket[]: zero between calls
-constexpr size_t kStaticStatusOff = kStaticFillOff + 2 * sizeof(uint32_t) * kStaticMaxRows;   // status word: zero between calls
-constexpr size_t kStaticScratchOff = 8192;                                                 // [kStaticMaxRows][kMergeCap] candidates
-constexpr size_t kStaticBytes = kStaticScratchOff + sizeof(u64) * (size_t)kMergeCap * kStaticMaxRows;
+constexpr int kStaticStride = 2 * kMaxChunks;   // a greedy row publishes one candidate and one count per chunk
+constexpr size_t kStaticRowsOff = 0;                                                                   // RowDesc[kStaticMaxRows]
+constexpr size_t kStaticCountersOff = kStaticRowsOff + sizeof(RowDesc) * kStaticMaxRows;               // ticket[], row_bound[], work[]
+constexpr size_t kStaticStatusOff = kStaticCountersOff + sizeof(uint32_t) * (2 * kStaticMaxRows + kCounterWords);   // status word
+constexpr size_t kStaticScratchOff = 8192;                                                             // [kStaticMaxRows][kStaticStride] candidates
+constexpr size_t kStaticBytes = kStaticScratchOff + sizeof(u64) * (size_t)kStaticStride * kStaticMaxRows;
 static_assert(kStaticStatusOff + sizeof(uint32_t) <= kStaticScratchOff, "descriptors, counters and status fit below the candidates");
 
-// Zero when the library is loaded (static storage); the kernel leaves the counters at zero when it finishes.
+// Zero when the library is loaded (static storage); every call starts by putting counters and status back to zero.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
 constexpr int kStaticMaxDevices = 64;
@@ -1023,8 +839,11 @@ struct StaticDevice {
 StaticDevice g_static_dev[kStaticMaxDevices];
 
 // Row descriptors of plain greedy rows (no penalty window): row r starts at r * ld, its token goes to tokens[r].
-__global__ void static_greedy_rows_kernel(RowDesc* rows, int n_rows, int64_t ld) {
+// The first thread also clears the counters and the status word a previous call may have left set (a call that was
+// not waited for and whose kernel reported an error): stream order puts this before the streaming kernel.
+__global__ void static_greedy_rows_kernel(RowDesc* rows, int n_rows, int64_t ld, uint32_t* counters, int n_counter_words) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < n_counter_words) counters[r] = 0u;
     if (r >= n_rows) return;
     RowDesc d{};
     d.logits_off = (int64_t)r * ld;
@@ -1034,6 +853,7 @@ __global__ void static_greedy_rows_kernel(RowDesc* rows, int n_rows, int64_t ld)
     d.penalty = 1.0f;
     d.flags = kRowGreedy;
     d.out_index = r;
+    d.k_global = 1;
     rows[r] = d;
 }
 
@@ -1067,37 +887,39 @@ extern "C" int fsb_argmax_rows_static(int device, const float* logits_dev, int64
         unsigned char* base = static_cast<unsigned char*>(sd.base);
         cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
         RowDesc* rows = reinterpret_cast<RowDesc*>(base + kStaticRowsOff);
-        static_greedy_rows_kernel<<<(n_rows + 63) / 64, 64, 0, st>>>(rows, n_rows, ld);
+        uint32_t* counters = reinterpret_cast<uint32_t*>(base + kStaticCountersOff);
+        const int n_counter_words = 2 * kStaticMaxRows + kCounterWords + 1;   // tickets, bounds, work counters, status
+        static_greedy_rows_kernel<<<(n_counter_words + 63) / 64, 64, 0, st>>>(rows, n_rows, ld, counters, n_counter_words);
+        if (cudaGetLastError() != cudaSuccess) rc = FSB_ERR_CUDA;
         StreamArgs a{};
         a.logits = logits_dev;
         a.rows = rows;
         a.hist = nullptr;
         a.scratch = reinterpret_cast<uint64_t*>(base + kStaticScratchOff);
-        a.fill = reinterpret_cast<uint32_t*>(base + kStaticFillOff);
-        a.ticket = a.fill + kStaticMaxRows;
+        a.scratch_stride = kStaticStride;
+        a.ticket = counters;
+        a.row_bound = counters + kStaticMaxRows;
+        a.work = counters + 2 * kStaticMaxRows;
         a.tokens = tokens_dev;
         a.status = reinterpret_cast<uint32_t*>(base + kStaticStatusOff);
         a.row_ld = ld;
         a.n_rows = n_rows;
         a.n_vocab = n_vocab;
         a.tiles_per_row = (n_vocab + kTile - 1) / kTile;
-        a.total_tiles = n_rows * a.tiles_per_row;
-        int q = (a.total_tiles + sd.slots - 1) / sd.slots;   // equal contiguous ranges of tiles, one per resident CTA
-        q = q < 1 ? 1 : (q > kMaxTilesPerCta ? kMaxTilesPerCta : q);
-        a.tiles_per_cta = q;
+        a.n_chunks = plan_chunks(n_rows, n_vocab, 1, sd.slots, kStaticStride, a.chunk_len);
+        a.n_items = n_rows * a.n_chunks;
         a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (ld & 3) == 0) ? 1 : 0;
-        if (2 * ((a.tiles_per_row + q - 1) / q + 1) > kMergeCap) {   // one candidate and one count per segment
-            rc = FSB_ERR_CAPACITY;   // more segments per row than a row's scratch has entries (one candidate per segment)
-        } else if (launch_stream_kernel(a, (a.total_tiles + q - 1) / q, st) != 0) {
+        if (rc != FSB_OK) {
+        } else if (a.n_chunks <= 0) {
+            rc = FSB_ERR_CAPACITY;   // more chunks per row than a row's scratch has entries
+        } else if (launch_stream_kernel(a, a.n_items < sd.slots ? a.n_items : sd.slots, st) != 0) {
             rc = FSB_ERR_CUDA;
         } else if (flags & FSB_STATIC_WAIT) {
             uint32_t status = 0;
             if (cudaMemcpyAsync(&status, a.status, sizeof status, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
                 cudaStreamSynchronize(st) != cudaSuccess) {
                 rc = FSB_ERR_CUDA;
-            } else if (status != 0u) {   // put counters and status back to zero for the next call
-                cudaMemsetAsync(base + kStaticFillOff, 0, kStaticScratchOff - kStaticFillOff, st);
-                cudaStreamSynchronize(st);
+            } else if (status != 0u) {
                 rc = FSB_ERR_DEVICE;
             }
         }

@@ -10,11 +10,11 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <random>
 #include <string>
-#include <unordered_set>
 #include <vector>
 
 #include "../../include/ferro_sampler_b200.h"
@@ -41,7 +41,8 @@ struct Stream {
 };
 
 struct Plan {
-    int tiles_per_row = 0, tiles_per_cta = 0, total_tiles = 0, grid = 0;
+    int tiles_per_row = 0, n_chunks = 0, grid = 0;
+    uint8_t chunk_len[fsb::kMaxChunks] = {};
 };
 
 }  // namespace
@@ -55,15 +56,20 @@ struct fsb_batch {
     int n_cand = 0, n_full = 0;   // rows of the candidate kernel / of the full-row kernel
     int kmax = 1;
     Plan plan;
-    int64_t hist_ids = 0;
-    // pinned host staging: [RowDesc x cap_rows][int32 x cap_hist], tokens
+    int64_t hist_ids = 0;         // window ids staged with the batch
+    int64_t gather_ids = 0;       // window values a write-back for a host caller brings back
+    int64_t table_ints = 0;       // int32 words of the per-stream table of a resident verification call, staged behind the window ids
+    // pinned host staging: [RowDesc x cap_rows][int32 x cap_hist], tokens, gathered window values
     unsigned char* h_in = nullptr;
     int32_t* h_tokens = nullptr;
+    float* h_patched = nullptr;
     // device
     unsigned char* d_in = nullptr;
     int32_t* d_tokens = nullptr;
+    float* d_patched = nullptr;
     std::vector<int> sid;
     std::vector<unsigned char> stochastic;
+    std::vector<fsb::RowDesc> descs;   // descriptors in row order while a batch is staged (capacity kept between calls)
     bool launched = false;
     const int32_t* hist_dev = nullptr;   // where the rows' penalty windows live: the batch's staged copy, or the engine's id pool
 
@@ -73,7 +79,7 @@ struct fsb_batch {
     int32_t* d_hist() const { return reinterpret_cast<int32_t*>(d_in + sizeof(fsb::RowDesc) * (size_t)cap_rows); }
     // the kernels' status word sits right behind the tokens, so that one copy brings both back
     uint32_t* d_status() const { return reinterpret_cast<uint32_t*>(d_tokens + cap_rows); }
-    size_t in_bytes_used() const { return sizeof(fsb::RowDesc) * (size_t)cap_rows + sizeof(int32_t) * (size_t)hist_ids; }
+    size_t in_bytes_used() const { return sizeof(fsb::RowDesc) * (size_t)cap_rows + sizeof(int32_t) * (size_t)(hist_ids + table_ints); }
 };
 
 struct fsb_handle {
@@ -85,22 +91,21 @@ struct fsb_handle {
     bool own_stream = false;
     float softcap = 0.0f;
     int32_t vocab_offset = 0;
+    int32_t global_vocab = 0;          // vocabulary sharding: columns of the whole row (0: this engine holds whole rows)
     int launch_overlap = 0;
-    int pair_ok = 1;                   // clusters of two CTAs can be launched on this device
+    int scan_sums = 0;
     std::vector<Stream> streams;
     std::vector<int> free_ids;
     // device scratch shared by all batches of this handle
-    uint64_t* d_scratch = nullptr;
-    uint32_t* d_fill = nullptr;     // [max_rows] fill, then [max_rows] ticket, then the status word
-    uint32_t* d_status = nullptr;
-    uint32_t* h_status = nullptr;   // pinned
+    uint64_t* d_scratch = nullptr;     // [max_rows][kRowScratch] published candidate lists
+    uint32_t* d_counters = nullptr;    // [max_rows] tickets, [max_rows] row bounds, [kCounterWords] work counters: all zero between launches
     int32_t* d_kept_ids = nullptr;
     double* d_kept_pr = nullptr;
     int32_t* d_kept_n = nullptr;
     bool kept_valid = false;
-    float* d_logits_stage = nullptr;   // device copy of host logits, grown on demand
+    float* d_logits_stage = nullptr;   // device copy of host logits: max_rows x max_vocab, allocated with the engine
     size_t logits_stage_elems = 0;
-    uint64_t* d_weights = nullptr;     // fixed-point weights of the full-row kernel, grown on demand
+    uint64_t* d_weights = nullptr;     // fixed-point weights of the full-row kernel: sized with the engine
     size_t weights_elems = 0;
     uint64_t* d_trace = nullptr;       // caller-owned diagnostics buffer, or null
     fsb_batch* own = nullptr;          // the batch behind fsb_sample_batch / fsb_verify_windows
@@ -109,6 +114,8 @@ struct fsb_handle {
     std::vector<std::vector<int64_t>> pool_free;   // freed regions by size class
     fsb_counters_t counters{};
     std::string err;
+
+    size_t counter_words() const { return 2 * (size_t)max_rows + fsb::kCounterWords; }
 };
 
 namespace {
@@ -141,44 +148,36 @@ int64_t window_begin(const ferro_sampler_params& p, int64_t len) {
     return std::min(b, len);
 }
 
+// The launch plan of the candidate rows of a batch: the chunk schedule and the grid.  FSB_PLAN in the environment
+// ("5,5,5,4,4,4,3,1,1": tiles per chunk, summing to the row's tiles) overrides the schedule - a tuning aid of the
+// benchmark, never needed for correct results.
 Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
     Plan pl;
     const int T = (n_vocab + fsb::kTile - 1) / fsb::kTile;
     pl.tiles_per_row = T;
-    pl.total_tiles = n_rows * T;
     const int slots = std::max(1, h->sm_count * std::max(1, h->ctas_per_sm));
-    // a row's scratch holds kMergeCap entries: k candidates and a count per segment
-    const int max_seg = std::max(2, fsb::kMergeCap / (std::max(1, kmax) + 1));
-    const int q_min = (T + (max_seg - 1) - 1) / (max_seg - 1);
-    const int q_fill = (pl.total_tiles + slots - 1) / slots;   // fewest tiles per CTA that still give a single wave
-    int q = std::max(1, std::min(std::max(q_fill, q_min), fsb::kMaxTilesPerCta));
-    if (T <= fsb::kMaxTilesPerCta && n_rows >= 2 * slots) {
-        // plenty of rows: one CTA per row.  Every CTA pays its start and its end-of-segment work once per row
-        // instead of once per piece, and no row has to be merged.
-        q = T;
-    } else {
-        // Otherwise a row is cut into nseg = T / q aligned pieces.  Fewer tiles per CTA shorten the streaming (per 32 KiB
-        // tile about 0.4 us on a lone SM, 0.6 us when every SM streams), more pieces lengthen the merge: nothing for one
-        // piece, the on-chip exchange inside a cluster of 2, 4 or 8 CTAs, ordered lists merged through scratch up to 16, a
-        // gather-and-select beyond (measured on B200, in us).  Pick the cheapest q that divides the row and keeps
-        // the grid within one wave.
-        double best = 1e30;
-        for (int c = q; c <= std::min(T, fsb::kMaxTilesPerCta); ++c) {
-            if (T % c != 0) continue;
-            const int nseg = T / c;
-            const double busy = std::min(1.0, (double)n_rows * nseg / slots);
-            const bool on_chip = (nseg == 2 || nseg == 4 || nseg == 8) && (nseg - 1) * std::max(1, kmax) <= 512;   // a cluster per row
-            const double merge = nseg == 1 ? 0.0 : on_chip ? (nseg == 2 ? 1.4 : nseg == 4 ? 2.0 : 3.3)
-                                 : nseg <= 8 ? 2.4 + 0.25 * nseg : nseg <= 16 ? 4.4 + 0.5 * nseg : 10.0 + 0.3 * nseg;
-            const double cost = (0.4 + 0.2 * busy) * c + merge;
-            if (cost < best) {
-                best = cost;
-                q = c;
+    pl.n_chunks = fsb::plan_chunks(n_rows, n_vocab, kmax, slots, fsb::kRowScratch, pl.chunk_len);
+    if (const char* env = std::getenv("FSB_PLAN")) {
+        uint8_t tmp[fsb::kMaxChunks];
+        int n = 0, sum = 0;
+        bool ok = true;
+        for (const char* s = env; *s && ok;) {
+            char* end = nullptr;
+            const long v = std::strtol(s, &end, 10);
+            if (end == s || v < 1 || v > fsb::kItemTilesMax || n >= fsb::kMaxChunks) ok = false;
+            else {
+                tmp[n++] = (uint8_t)v;
+                sum += (int)v;
+                s = (*end == ',') ? end + 1 : end;
+                if (*end && *end != ',') ok = false;
             }
         }
+        if (ok && sum == T && (int64_t)n * (std::max(1, kmax) + 1) <= fsb::kRowScratch) {
+            pl.n_chunks = n;
+            std::memcpy(pl.chunk_len, tmp, (size_t)n);
+        }
     }
-    pl.tiles_per_cta = q;
-    pl.grid = (pl.total_tiles + q - 1) / q;
+    pl.grid = (int)std::min<int64_t>((int64_t)n_rows * pl.n_chunks, slots);
     return pl;
 }
 
@@ -186,22 +185,31 @@ void free_batch_buffers(fsb_batch* b) {
     if (!b) return;
     if (b->h_in) cudaFreeHost(b->h_in);
     if (b->h_tokens) cudaFreeHost(b->h_tokens);
+    if (b->h_patched) cudaFreeHost(b->h_patched);
     if (b->d_in) cudaFree(b->d_in);
     if (b->d_tokens) cudaFree(b->d_tokens);
-    b->h_in = nullptr; b->h_tokens = nullptr; b->d_in = nullptr; b->d_tokens = nullptr;
+    if (b->d_patched) cudaFree(b->d_patched);
+    b->h_in = nullptr; b->h_tokens = nullptr; b->h_patched = nullptr; b->d_in = nullptr; b->d_tokens = nullptr; b->d_patched = nullptr;
 }
 
-int alloc_batch(fsb_handle* h, int cap_rows, int64_t cap_hist, fsb_batch** out) {
+// `patched` > 0: also buffers for that many gathered window values (write-back for host callers).
+int alloc_batch(fsb_handle* h, int cap_rows, int64_t cap_hist, int64_t patched, fsb_batch** out) {
     fsb_batch* b = new (std::nothrow) fsb_batch();
     if (!b) return fail(h, FSB_ERR_INVALID, "out of host memory");
     b->cap_rows = cap_rows;
     b->cap_hist = std::max<int64_t>(cap_hist, 1);
-    const size_t in_bytes = sizeof(fsb::RowDesc) * (size_t)cap_rows + sizeof(int32_t) * (size_t)b->cap_hist;
+    cap_hist = b->cap_hist + (int64_t)fsb::kWindowTableInts * cap_rows;   // room for the table of a resident verification call
+    b->descs.reserve((size_t)cap_rows);
+    b->sid.reserve((size_t)cap_rows);
+    b->stochastic.reserve((size_t)cap_rows);
+    const size_t in_bytes = sizeof(fsb::RowDesc) * (size_t)cap_rows + sizeof(int32_t) * (size_t)cap_hist;
     cudaError_t e = cudaMallocHost(reinterpret_cast<void**>(&b->h_in), in_bytes);
     if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&b->h_tokens), sizeof(int32_t) * ((size_t)cap_rows + 1));
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->d_in), in_bytes);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->d_tokens), sizeof(int32_t) * ((size_t)cap_rows + 1));
     if (e == cudaSuccess) e = cudaMemset(b->d_tokens, 0, sizeof(int32_t) * ((size_t)cap_rows + 1));
+    if (e == cudaSuccess && patched > 0) e = cudaMallocHost(reinterpret_cast<void**>(&b->h_patched), sizeof(float) * (size_t)patched);
+    if (e == cudaSuccess && patched > 0) e = cudaMalloc(reinterpret_cast<void**>(&b->d_patched), sizeof(float) * (size_t)patched);
     if (e != cudaSuccess) {
         free_batch_buffers(b);
         delete b;
@@ -216,41 +224,46 @@ Stream* get_stream(fsb_handle* h, int sid) {
     return &h->streams[(size_t)sid];
 }
 
-void fill_desc(fsb::RowDesc& d, const ferro_sampler_params& p, int n_vocab, int64_t logits_off, int64_t hist_begin, int64_t hist_len,
-               uint64_t word, int out_index) {
+// `n_vocab` = the columns this engine holds; with vocabulary sharding the row's candidate count follows the whole
+// row's width (src/sampler.cpp:27 with n = the global vocabulary), the shard's its own.
+void fill_desc(const fsb_handle* h, fsb::RowDesc& d, const ferro_sampler_params& p, int n_vocab, int64_t logits_off, int64_t hist_begin,
+               int64_t hist_len, uint64_t word, int out_index) {
     std::memset(&d, 0, sizeof d);
     d.rng_word = word;
     d.logits_off = logits_off;
     d.hist_begin = hist_begin;
     d.hist_len = (int32_t)hist_len;
     const bool greedy = is_greedy(p);
+    const int n_global = h->global_vocab > 0 ? h->global_vocab : n_vocab;
     d.k = greedy ? 1 : ((p.top_k > 0 && p.top_k < n_vocab) ? p.top_k : n_vocab);   // src/sampler.cpp:27
+    d.k_global = greedy ? 1 : ((p.top_k > 0 && p.top_k < n_global) ? p.top_k : n_global);
     d.temperature = p.temperature;
     d.top_p = p.top_p;
     d.min_p = p.min_p;
     d.penalty = p.repetition_penalty;
     d.flags = (greedy ? fsb::kRowGreedy : 0) | (hist_len > 0 ? fsb::kRowPenalty : 0);
     d.out_index = out_index;
+    d.gather_off = 0;
 }
 
 // Orders the staged descriptors: candidate-path rows first, full-row-path rows after; fixes the launch plan.
-int finalize_batch(fsb_handle* h, fsb_batch* b, std::vector<fsb::RowDesc>& descs) {
-    std::vector<fsb::RowDesc> full;
+int finalize_batch(fsb_handle* h, fsb_batch* b) {
     int n_cand = 0, kmax = 1;
     fsb::RowDesc* dst = b->h_rows();
-    for (const auto& d : descs) {
-        if (d.k <= fsb::kMaxK) {
+    auto on_chip = [](const fsb::RowDesc& d) { return d.k <= fsb::kMaxK && d.k_global <= fsb::kMaxK; };
+    for (const auto& d : b->descs)
+        if (on_chip(d)) {
             dst[n_cand++] = d;
             kmax = std::max(kmax, d.k);
-        } else {
-            full.push_back(d);
         }
-    }
-    for (size_t i = 0; i < full.size(); ++i) dst[n_cand + (int)i] = full[i];
+    int n_full = 0;
+    for (const auto& d : b->descs)
+        if (!on_chip(d)) dst[n_cand + n_full++] = d;
     b->n_cand = n_cand;
-    b->n_full = (int)full.size();
+    b->n_full = n_full;
     b->kmax = kmax;
     b->plan = make_plan(h, std::max(n_cand, 1), b->n_vocab, kmax);
+    if (n_cand > 0 && b->plan.n_chunks <= 0) return fail(h, FSB_ERR_CAPACITY, "rows of %d logits cannot be scheduled with k = %d", b->n_vocab, kmax);
     return FSB_OK;
 }
 
@@ -263,14 +276,17 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
                  int32_t* shard_n = nullptr) {
     if (shard_out && b->n_full > 0)
         return fail(h, FSB_ERR_RANGE, "rows whose candidate count exceeds %d (top_k = 0 or large) cannot be sharded by vocabulary", fsb::kMaxK);
+    const int32_t* hist = b->hist_dev ? b->hist_dev : b->d_hist();
     if (b->n_cand > 0) {
         fsb::StreamArgs a{};
         a.logits = logits_dev;
         a.rows = b->d_rows();
-        a.hist = b->hist_dev ? b->hist_dev : b->d_hist();
+        a.hist = hist;
         a.scratch = h->d_scratch;
-        a.fill = h->d_fill;
-        a.ticket = h->d_fill + h->max_rows;
+        a.scratch_stride = fsb::kRowScratch;
+        a.ticket = h->d_counters;
+        a.row_bound = h->d_counters + h->max_rows;
+        a.work = h->d_counters + 2 * (size_t)h->max_rows;
         a.tokens = b->d_tokens;
         a.status = b->d_status();
         a.kept_ids = keep_kept ? h->d_kept_ids : nullptr;
@@ -283,33 +299,22 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.n_rows = b->n_cand;
         a.n_vocab = b->n_vocab;
         a.tiles_per_row = b->plan.tiles_per_row;
-        a.tiles_per_cta = b->plan.tiles_per_cta;
-        a.total_tiles = b->n_cand * b->plan.tiles_per_row;
+        a.n_chunks = b->plan.n_chunks;
+        a.n_items = b->n_cand * b->plan.n_chunks;
+        std::memcpy(a.chunk_len, b->plan.chunk_len, sizeof a.chunk_len);
         a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (b->ld & 3) == 0) ? 1 : 0;
         a.write_back = (b->flags & FSB_WRITE_BACK) ? 1 : 0;
         a.vocab_offset = h->vocab_offset;
         a.softcap = h->softcap;
         a.overlap = h->launch_overlap;
-        const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
-        // rows of exactly 2, 4 or 8 aligned segments: the CTAs of a row run as a cluster and exchange candidates on chip
-        a.pair = 0;
-        for (int c = 2; c <= 8; c *= 2)   // receive buffer: (c - 1) lists of kmax entries in 512
-            if (h->pair_ok && a.tiles_per_row == c * a.tiles_per_cta && grid == c * a.n_rows && (c - 1) * b->kmax <= 512) a.pair = c;
-        const int e = fsb::launch_stream_kernel(a, grid, h->stream);
+        a.scan_sums = h->scan_sums;
+        const int e = fsb::launch_stream_kernel(a, b->plan.grid, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         h->counters.kernel_launches++;
     }
     if (b->n_full > 0) {   // rows whose candidate set does not fit on chip: the multi-pass full-row kernel
-        const size_t need = (size_t)b->n_full * (size_t)b->n_vocab;
-        if (need > h->weights_elems) {
-            FSB_CUDA(h, cudaStreamSynchronize(h->stream));
-            if (h->d_weights) cudaFree(h->d_weights);
-            h->d_weights = nullptr;
-            h->weights_elems = 0;
-            FSB_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->d_weights), need * sizeof(uint64_t)));
-            h->weights_elems = need;
-        }
-        const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, b->hist_dev ? b->hist_dev : b->d_hist(), h->d_weights, b->d_tokens,
+        if ((size_t)b->n_full * (size_t)b->n_vocab > h->weights_elems) return fail(h, FSB_ERR_CAPACITY, "full-vocabulary rows exceed the engine's scratch");
+        const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, hist, h->d_weights, b->d_tokens,
                                                   keep_kept ? h->d_kept_ids : nullptr, keep_kept ? h->d_kept_pr : nullptr,
                                                   keep_kept ? h->d_kept_n : nullptr, b->d_status(), b->n_vocab, h->vocab_offset,
                                                   (b->flags & FSB_WRITE_BACK) ? 1 : 0, h->softcap, h->stream);
@@ -321,17 +326,18 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
     return FSB_OK;
 }
 
-int fetch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out) {
-    // tokens and the status word behind them in one copy (the gap between n_rows and cap_rows is small)
+// Tokens and the status word behind them in one copy; `extra` floats of gathered window values in a second one.
+int fetch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out, int64_t patched = 0) {
     FSB_CUDA(h, cudaMemcpyAsync(b->h_tokens, b->d_tokens, sizeof(int32_t) * ((size_t)b->cap_rows + 1), cudaMemcpyDeviceToHost, h->stream));
+    if (patched > 0) FSB_CUDA(h, cudaMemcpyAsync(b->h_patched, b->d_patched, sizeof(float) * (size_t)patched, cudaMemcpyDeviceToHost, h->stream));
     FSB_CUDA(h, cudaStreamSynchronize(h->stream));
     const unsigned st = (unsigned)b->h_tokens[b->cap_rows];
     if (st != 0u) {
         // put the self-resetting counters and the status word back into their idle state
-        cudaMemsetAsync(h->d_fill, 0, sizeof(uint32_t) * (2 * (size_t)h->max_rows + 1), h->stream);
+        cudaMemsetAsync(h->d_counters, 0, sizeof(uint32_t) * h->counter_words(), h->stream);
         cudaMemsetAsync(b->d_status(), 0, sizeof(uint32_t), h->stream);
         cudaStreamSynchronize(h->stream);
-        return fail(h, FSB_ERR_DEVICE, "kernel status 0x%x (1 copy timeout, 2 candidate overflow, 4 merge overflow, 8 empty row, 16 tie)", st);
+        return fail(h, FSB_ERR_DEVICE, "kernel status 0x%x (1 wait timeout, 4 merge overflow, 8 row without a finite logit)", st);
     }
     if (tokens_out) std::memcpy(tokens_out, b->h_tokens, sizeof(int32_t) * (size_t)b->n_rows);
     return FSB_OK;
@@ -397,6 +403,19 @@ int sync_history(fsb_handle* h, Stream* s) {
     return FSB_OK;
 }
 
+// A call that fails after its rows were staged has consumed engine outputs without returning tokens: the engines of
+// its stochastic rows are put back, so that the streams stay in step with the reference's.
+void rollback_draws(fsb_handle* h, const fsb_batch* b) {
+    for (int i = 0; i < b->n_rows && i < (int)b->sid.size(); ++i) {
+        if (!b->stochastic[(size_t)i]) continue;
+        Stream* s = get_stream(h, b->sid[(size_t)i]);
+        if (!s || s->draws == 0) continue;
+        s->draws--;
+        s->rng.seed(s->seed_used);
+        s->rng.discard(s->draws);
+    }
+}
+
 // Stages rows "stream_ids[i] samples row i with history i" into batch b.  Consumes engine outputs.
 int stage_rows(fsb_handle* h, fsb_batch* b, int n_rows, const int* stream_ids, int64_t ld, int n_vocab, const int32_t* hist_flat,
                const int64_t* hist_off, unsigned flags) {
@@ -423,7 +442,7 @@ int stage_rows(fsb_handle* h, fsb_batch* b, int n_rows, const int* stream_ids, i
     b->hist_dev = nullptr;
     b->sid.assign(stream_ids, stream_ids + n_rows);
     b->stochastic.assign((size_t)n_rows, 0);
-    std::vector<fsb::RowDesc> descs((size_t)n_rows);
+    b->descs.resize((size_t)n_rows);
     int32_t* hs = b->h_hist();
     int64_t pos = 0;
     for (int i = 0; i < n_rows; ++i) {
@@ -437,15 +456,19 @@ int stage_rows(fsb_handle* h, fsb_batch* b, int n_rows, const int* stream_ids, i
             s->draws++;
             b->stochastic[(size_t)i] = 1;
         }
-        fill_desc(descs[(size_t)i], s->p, n_vocab, (int64_t)i * ld, pos, wl, word, i);
+        fill_desc(h, b->descs[(size_t)i], s->p, n_vocab, (int64_t)i * ld, pos, wl, word, i);
+        b->descs[(size_t)i].gather_off = (int32_t)pos;
         pos += wl;
     }
     b->hist_ids = pos;
-    return finalize_batch(h, b, descs);
+    b->gather_ids = pos;
+    b->table_ints = 0;
+    rc = finalize_batch(h, b);
+    if (rc) rollback_draws(h, b);
+    return rc;
 }
 
-void count_rows(fsb_handle* h, const fsb_batch* b, int n_sampled_mask_all) {
-    (void)n_sampled_mask_all;
+void count_rows(fsb_handle* h, const fsb_batch* b) {
     for (int i = 0; i < b->n_rows; ++i) {
         h->counters.rows_sampled++;
         if (b->stochastic[(size_t)i]) h->counters.rows_stochastic++;
@@ -456,30 +479,63 @@ void count_rows(fsb_handle* h, const fsb_batch* b, int n_sampled_mask_all) {
 
 int stage_host_logits(fsb_handle* h, const float* logits, int n_rows, int64_t ld, int n_vocab, const float** dev) {
     const size_t elems = (size_t)(n_rows - 1) * (size_t)ld + (size_t)n_vocab;
-    if (elems > h->logits_stage_elems) {
-        if (h->d_logits_stage) cudaFree(h->d_logits_stage);
-        h->d_logits_stage = nullptr;
-        h->logits_stage_elems = 0;
-        FSB_CUDA(h, cudaMalloc(reinterpret_cast<void**>(&h->d_logits_stage), elems * sizeof(float)));
-        h->logits_stage_elems = elems;
-    }
+    if (elems > h->logits_stage_elems)
+        return fail(h, FSB_ERR_CAPACITY, "host logits of %zu values (row stride %lld) exceed the engine's staging area of %zu", elems, (long long)ld,
+                    h->logits_stage_elems);
     FSB_CUDA(h, cudaMemcpyAsync(h->d_logits_stage, logits, elems * sizeof(float), cudaMemcpyHostToDevice, h->stream));
     *dev = h->d_logits_stage;
     return FSB_OK;
 }
 
-// The reference modifies the caller's host row in place (src/sampler.cpp:17).  With host logits the kernels work
-// on a device copy, so the side effect is replayed on the caller's buffer: the same fp32 operation on the same
-// distinct ids.  This touches only the penalised entries and takes no part in choosing the token.
-void replay_penalty_on_host(float* row, int n_vocab, const ferro_sampler_params& p, const int32_t* hist, int64_t len, int32_t id_offset) {
-    const int64_t b = window_begin(p, len);
-    if (b >= len) return;
-    std::unordered_set<int> seen;
-    for (int64_t i = b; i < len; ++i) {
-        const int id = hist[i] - id_offset;
-        if (id < 0 || id >= n_vocab || !seen.insert(id).second) continue;
-        row[id] = row[id] > 0 ? row[id] / p.repetition_penalty : row[id] * p.repetition_penalty;
+// The reference modifies the caller's host row in place (src/sampler.cpp:17).  With host logits the kernels work on
+// a device copy; the penalised values they leave there are gathered on the device (one per window id) and stored
+// into the caller's rows here: the host moves values, it computes nothing.
+int launch_gather(fsb_handle* h, fsb_batch* b, const float* logits_dev) {
+    if (b->gather_ids <= 0) return FSB_OK;
+    const int e = fsb::launch_gather_patched(logits_dev, b->d_rows(), b->n_rows, b->hist_dev ? b->hist_dev : b->d_hist(), b->n_vocab, h->vocab_offset,
+                                             b->d_patched, h->stream);
+    if (e != 0) return fail(h, FSB_ERR_CUDA, "gather kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+    h->counters.kernel_launches++;
+    return FSB_OK;
+}
+void scatter_patched(const fsb_handle* h, const fsb_batch* b, float* logits_host, const int32_t* ids, int64_t n, int row, int gather_off) {
+    float* rowp = logits_host + (int64_t)row * b->ld;
+    for (int64_t i = 0; i < n; ++i) {
+        const int64_t c = (int64_t)ids[i] - h->vocab_offset;
+        if (c >= 0 && c < b->n_vocab) rowp[c] = b->h_patched[gather_off + i];
     }
+}
+
+// The common tail of the synchronous calls: upload, (stage host logits), launch, (append), fetch, (write back to host).
+// `window_streams` > 0: a resident verification call - the drafts go into the id pool before the launch, and the last
+// accepted token of every stream after it (see verify_windows_impl).
+int run_staged(fsb_handle* h, fsb_batch* b, const float* logits, unsigned flags, bool append, int32_t* tokens_out, int window_streams = 0,
+               bool window_append = false) {
+    const bool on_host = (flags & FSB_LOGITS_ON_HOST) != 0;
+    const bool host_wb = on_host && (flags & FSB_WRITE_BACK) && b->gather_ids > 0;
+    int rc = upload_batch(h, b);
+    const float* dev = logits;
+    if (rc == FSB_OK && on_host) rc = stage_host_logits(h, logits, b->n_rows, b->ld, b->n_vocab, &dev);
+    if (rc == FSB_OK && window_streams > 0) {
+        const int e = fsb::launch_write_drafts(b->d_rows(), b->n_rows, h->d_pool, h->stream);
+        if (e != 0) rc = fail(h, FSB_ERR_CUDA, "draft kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+        else h->counters.kernel_launches++;
+    }
+    if (rc == FSB_OK) rc = launch_batch(h, b, dev, (flags & FSB_KEEP_KEPT_SET) != 0);
+    if (rc == FSB_OK && window_streams > 0 && window_append) {
+        const int e = fsb::launch_accept_windows(b->d_hist() + b->hist_ids, window_streams, b->d_tokens, h->d_pool, h->stream);
+        if (e != 0) rc = fail(h, FSB_ERR_CUDA, "accept kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+        else h->counters.kernel_launches++;
+    }
+    if (rc == FSB_OK && host_wb) rc = launch_gather(h, b, dev);
+    if (rc == FSB_OK && append) {
+        const int e = fsb::launch_append_tokens(b->d_rows(), b->n_rows, b->d_tokens, h->d_pool, h->stream);
+        if (e != 0) rc = fail(h, FSB_ERR_CUDA, "append kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+        else h->counters.kernel_launches++;
+    }
+    if (rc == FSB_OK) rc = fetch_tokens(h, b, tokens_out, host_wb ? b->gather_ids : 0);
+    if (rc) rollback_draws(h, b);
+    return rc;
 }
 
 }  // namespace
@@ -543,18 +599,21 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
     if (fsb::prepare_full_row_kernel(max_vocab) != 0) return bail(FSB_ERR_CUDA);
     if (cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(FSB_ERR_CUDA);
     h->own_stream = true;
-    const size_t ctr_words = 2 * (size_t)max_rows + 1;
-    if (cudaMalloc(reinterpret_cast<void**>(&h->d_scratch), sizeof(uint64_t) * (size_t)max_rows * fsb::kMergeCap) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&h->d_fill), sizeof(uint32_t) * ctr_words) != cudaSuccess ||
-        cudaMemset(h->d_fill, 0, sizeof(uint32_t) * ctr_words) != cudaSuccess ||
-        cudaMallocHost(reinterpret_cast<void**>(&h->h_status), sizeof(uint32_t)) != cudaSuccess ||
+    // Everything a call may need is allocated here, so that no call allocates: the rows' scratch, the counters, the
+    // kept-set record, the id pool, the staging area of host logits and the full-row kernel's weights.
+    h->logits_stage_elems = (size_t)max_rows * (size_t)max_vocab;
+    h->weights_elems = (size_t)max_rows * (size_t)max_vocab;
+    if (cudaMalloc(reinterpret_cast<void**>(&h->d_scratch), sizeof(uint64_t) * (size_t)max_rows * fsb::kRowScratch) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_counters), sizeof(uint32_t) * h->counter_words()) != cudaSuccess ||
+        cudaMemset(h->d_counters, 0, sizeof(uint32_t) * h->counter_words()) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_ids), sizeof(int32_t) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_pr), sizeof(double) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_n), sizeof(int32_t) * (size_t)max_rows) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&h->d_pool), sizeof(int32_t) * (size_t)std::max<int64_t>(max_hist_ids, 1)) != cudaSuccess)
+        cudaMalloc(reinterpret_cast<void**>(&h->d_pool), sizeof(int32_t) * (size_t)std::max<int64_t>(max_hist_ids, 1)) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_logits_stage), sizeof(float) * h->logits_stage_elems) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_weights), sizeof(uint64_t) * h->weights_elems) != cudaSuccess)
         return bail(FSB_ERR_CUDA);
-    h->d_status = h->d_fill + 2 * (size_t)max_rows;
-    if (alloc_batch(h, max_rows, max_hist_ids, &h->own) != FSB_OK) return bail(FSB_ERR_CUDA);
+    if (alloc_batch(h, max_rows, max_hist_ids, std::max<int64_t>(max_hist_ids, 1), &h->own) != FSB_OK) return bail(FSB_ERR_CUDA);
     *out = h;
     return FSB_OK;
 }
@@ -568,8 +627,7 @@ int fsb_destroy(fsb_handle* h) {
         delete h->own;
     }
     if (h->d_scratch) cudaFree(h->d_scratch);
-    if (h->d_fill) cudaFree(h->d_fill);
-    if (h->h_status) cudaFreeHost(h->h_status);
+    if (h->d_counters) cudaFree(h->d_counters);
     if (h->d_kept_ids) cudaFree(h->d_kept_ids);
     if (h->d_kept_pr) cudaFree(h->d_kept_pr);
     if (h->d_kept_n) cudaFree(h->d_kept_n);
@@ -612,10 +670,24 @@ int fsb_set_launch_overlap(fsb_handle* h, int on) {
     return FSB_OK;
 }
 
+int fsb_set_scan_sums(fsb_handle* h, int on) {
+    if (!h) return FSB_ERR_INVALID;
+    h->scan_sums = on ? 1 : 0;
+    return FSB_OK;
+}
+
 int fsb_set_vocab_offset(fsb_handle* h, int32_t offset) {
     if (!h) return FSB_ERR_INVALID;
     if (offset < 0) return fail(h, FSB_ERR_RANGE, "vocab offset must be >= 0");
     h->vocab_offset = offset;
+    return FSB_OK;
+}
+
+int fsb_set_vocab_shard(fsb_handle* h, int32_t offset, int32_t global_vocab) {
+    if (!h) return FSB_ERR_INVALID;
+    if (offset < 0 || global_vocab < 0 || (global_vocab > 0 && offset >= global_vocab)) return fail(h, FSB_ERR_RANGE, "bad shard: offset %d of %d columns", offset, global_vocab);
+    h->vocab_offset = offset;
+    h->global_vocab = global_vocab;
     return FSB_OK;
 }
 
@@ -689,27 +761,15 @@ int fsb_sample_batch(fsb_handle* h, int n_rows, const int* stream_ids, const flo
     fsb_batch* b = h->own;
     int rc = stage_rows(h, b, n_rows, stream_ids, ld, n_vocab, hist_flat, hist_off, flags);
     if (rc) return rc;
-    const bool on_host = (flags & FSB_LOGITS_ON_HOST) != 0;
-    if (on_host) b->flags &= ~FSB_WRITE_BACK;   // the device copy is private; the side effect is replayed below
-    rc = upload_batch(h, b);
+    rc = run_staged(h, b, logits, flags, false, tokens_out);
     if (rc) return rc;
-    const float* dev = logits;
-    if (on_host) {
-        rc = stage_host_logits(h, logits, n_rows, ld, n_vocab, &dev);
-        if (rc) return rc;
-    }
-    rc = launch_batch(h, b, dev, (flags & FSB_KEEP_KEPT_SET) != 0);
-    if (rc) return rc;
-    rc = fetch_tokens(h, b, tokens_out);
-    if (rc) return rc;
-    if (on_host && (flags & FSB_WRITE_BACK)) {
+    if ((flags & FSB_LOGITS_ON_HOST) && (flags & FSB_WRITE_BACK)) {
         for (int i = 0; i < n_rows; ++i) {
-            const Stream* s = get_stream(h, stream_ids[i]);
-            replay_penalty_on_host(const_cast<float*>(logits) + (int64_t)i * ld, n_vocab, s->p, hist_flat + hist_off[i],
-                                   hist_off[i + 1] - hist_off[i], h->vocab_offset);
+            const fsb::RowDesc& d = b->descs[(size_t)i];
+            scatter_patched(h, b, const_cast<float*>(logits), b->h_hist() + d.hist_begin, d.hist_len, i, d.gather_off);
         }
     }
-    count_rows(h, b, 0);
+    count_rows(h, b);
     return FSB_OK;
 }
 
@@ -756,12 +816,17 @@ int fsb_sample_batch_resident(fsb_handle* h, int n_rows, const int* stream_ids, 
         for (int j = 0; j < i; ++j)
             if (stream_ids[j] == stream_ids[i]) return fail(h, FSB_ERR_INVALID, "stream %d appears twice in one resident batch", stream_ids[i]);
     }
+    int64_t gather = 0;
     for (int i = 0; i < n_rows; ++i) {
         Stream* s = get_stream(h, stream_ids[i]);
         rc = sync_history(h, s);
         if (rc == FSB_OK && append) rc = ensure_region(h, s, (int64_t)s->hist.size() + 1);
         if (rc) return rc;
+        const int64_t len = (int64_t)s->hist.size();
+        gather += len - window_begin(s->p, len);
     }
+    const bool host_wb = (flags & FSB_LOGITS_ON_HOST) && (flags & FSB_WRITE_BACK);
+    if (host_wb && gather > b->cap_hist) return fail(h, FSB_ERR_CAPACITY, "%lld penalty-window ids exceed the capacity of %lld", (long long)gather, (long long)b->cap_hist);
     b->n_rows = n_rows;
     b->n_vocab = n_vocab;
     b->ld = ld;
@@ -770,7 +835,8 @@ int fsb_sample_batch_resident(fsb_handle* h, int n_rows, const int* stream_ids, 
     b->hist_ids = 0;
     b->sid.assign(stream_ids, stream_ids + n_rows);
     b->stochastic.assign((size_t)n_rows, 0);
-    std::vector<fsb::RowDesc> descs((size_t)n_rows);
+    b->descs.resize((size_t)n_rows);
+    int64_t goff = 0;
     for (int i = 0; i < n_rows; ++i) {
         Stream* s = get_stream(h, stream_ids[i]);
         const int64_t len = (int64_t)s->hist.size();
@@ -781,52 +847,46 @@ int fsb_sample_batch_resident(fsb_handle* h, int n_rows, const int* stream_ids, 
             s->draws++;
             b->stochastic[(size_t)i] = 1;
         }
-        fill_desc(descs[(size_t)i], s->p, n_vocab, (int64_t)i * ld, wl > 0 ? s->pool_off + wb : 0, wl, word, i);
-        const int64_t at = append ? s->pool_off + len : -1;
-        descs[(size_t)i].pad[0] = (int32_t)(uint32_t)(at & 0xFFFFFFFFll);
-        descs[(size_t)i].pad[1] = (int32_t)(at >> 32);
+        // the window ends where the history ends: hist_begin + hist_len is where an appended token goes
+        fsb::RowDesc& d = b->descs[(size_t)i];
+        fill_desc(h, d, s->p, n_vocab, (int64_t)i * ld, (s->pool_off >= 0 ? s->pool_off : 0) + wb, wl, word, i);
+        if (append) d.flags |= fsb::kRowAppend;
+        d.gather_off = (int32_t)goff;
+        goff += wl;
     }
-    rc = finalize_batch(h, b, descs);
-    if (rc) return rc;
-    const bool on_host = (flags & FSB_LOGITS_ON_HOST) != 0;
-    if (on_host) b->flags &= ~FSB_WRITE_BACK;
-    rc = upload_batch(h, b);
-    if (rc) return rc;
-    const float* dev = logits;
-    if (on_host) {
-        rc = stage_host_logits(h, logits, n_rows, ld, n_vocab, &dev);
-        if (rc) return rc;
+    b->gather_ids = host_wb ? goff : 0;
+    rc = finalize_batch(h, b);
+    if (rc) {
+        rollback_draws(h, b);
+        return rc;
     }
-    rc = launch_batch(h, b, dev, (flags & FSB_KEEP_KEPT_SET) != 0);
-    if (rc) return rc;
-    if (append) {
-        const int e = fsb::launch_append_tokens(b->d_rows(), n_rows, b->d_tokens, h->d_pool, h->stream);
-        if (e != 0) return fail(h, FSB_ERR_CUDA, "append kernel launch: %s", cudaGetErrorString((cudaError_t)e));
-        h->counters.kernel_launches++;
-    }
-    rc = fetch_tokens(h, b, tokens_out);
+    rc = run_staged(h, b, logits, flags & ~FSB_APPEND_SAMPLED, append, tokens_out);
     if (rc) return rc;
     for (int i = 0; i < n_rows; ++i) {
         Stream* s = get_stream(h, stream_ids[i]);
-        if (on_host && (flags & FSB_WRITE_BACK))
-            replay_penalty_on_host(const_cast<float*>(logits) + (int64_t)i * ld, n_vocab, s->p, s->hist.data(), (int64_t)s->hist.size(), h->vocab_offset);
+        if (host_wb) {
+            const fsb::RowDesc& d = b->descs[(size_t)i];
+            scatter_patched(h, b, const_cast<float*>(logits), s->hist.data() + (s->hist.size() - (size_t)d.hist_len), d.hist_len, i, d.gather_off);
+        }
         if (append) {   // the device copy already holds the token
             s->hist.push_back(tokens_out[i]);
             s->dev_len = (int64_t)s->hist.size();
         }
     }
-    count_rows(h, b, 0);
+    count_rows(h, b);
     return FSB_OK;
 }
 
-int fsb_verify_windows(fsb_handle* h, int n_streams, const int* stream_ids, const int* row_off, const int32_t* rows_flat,
-                       const float* logits, int64_t ld, int n_vocab, const int32_t* hist_flat, const int64_t* hist_off,
-                       const int* max_accept, int32_t* tokens_out, int* acc_out, int* confirmed_out, unsigned flags) {
-    if (!h) return FSB_ERR_INVALID;
-    if (!stream_ids || !row_off || !rows_flat || !logits || !hist_off || !tokens_out || !acc_out)
-        return fail(h, FSB_ERR_INVALID, "null argument");
+// The two window calls share everything but where a stream's history comes from: `hist_flat` / `hist_off` (host
+// memory, staged with the call) or, when hist_off is null, the streams' resident histories.
+static int verify_windows_impl(fsb_handle* h, int n_streams, const int* stream_ids, const int* row_off, const int32_t* rows_flat,
+                               const float* logits, int64_t ld, int n_vocab, const int32_t* hist_flat, const int64_t* hist_off,
+                               const int* max_accept, int32_t* tokens_out, int* acc_out, int* confirmed_out, unsigned flags) {
+    const bool resident = hist_off == nullptr;
+    if (!stream_ids || !row_off || !rows_flat || !logits || !tokens_out || !acc_out) return fail(h, FSB_ERR_INVALID, "null argument");
     if (n_streams <= 0) return fail(h, FSB_ERR_INVALID, "n_streams must be positive");
     if (flags & FSB_WRITE_BACK) return fail(h, FSB_ERR_INVALID, "write-back is not defined for verification windows");
+    if (!resident && (flags & FSB_APPEND_SAMPLED)) return fail(h, FSB_ERR_INVALID, "FSB_APPEND_SAMPLED needs resident histories");
     cudaSetDevice(h->device);
     fsb_batch* b = h->own;
     const int n_rows = row_off[n_streams] - row_off[0];
@@ -841,32 +901,48 @@ int fsb_verify_windows(fsb_handle* h, int n_streams, const int* stream_ids, cons
         for (int j = 0; j < i; ++j)
             if (stream_ids[j] == stream_ids[i]) return fail(h, FSB_ERR_INVALID, "stream id %d appears twice", stream_ids[i]);
         const int m = row_off[i + 1] - row_off[i];
-        const int64_t len = hist_off[i + 1] - hist_off[i];
+        const int64_t len = resident ? (int64_t)s->hist.size() : hist_off[i + 1] - hist_off[i];
         if (m <= 0 || len < 0) return fail(h, FSB_ERR_INVALID, "stream %d: empty window or bad history offsets", i);
-        if (len > 0 && !hist_flat) return fail(h, FSB_ERR_INVALID, "hist_flat is null");
-        need += (len - window_begin(s->p, len)) + (m - 1);
+        if (resident && (flags & FSB_APPEND_SAMPLED) && m - 1 > fsb::kWindowTableInts - 6)
+            return fail(h, FSB_ERR_CAPACITY, "stream %d: a resident window with FSB_APPEND_SAMPLED holds at most %d drafts", i, fsb::kWindowTableInts - 6);
+        if (!resident && len > 0 && !hist_flat) return fail(h, FSB_ERR_INVALID, "hist_flat is null");
+        need += resident ? 0 : (len - window_begin(s->p, len)) + (m - 1);
     }
     if (need > b->cap_hist) return fail(h, FSB_ERR_CAPACITY, "%lld penalty-window ids exceed the capacity of %lld", (long long)need,
                                         (long long)b->cap_hist);
+    if (resident) {
+        // The drafts of a window go behind the stream's history in its region of the id pool (they are what the history
+        // will hold if they are accepted), so that row r's window is a range of the pool like any other: make room.
+        for (int i = 0; i < n_streams; ++i) {
+            Stream* s = get_stream(h, stream_ids[i]);
+            rc = sync_history(h, s);
+            if (rc == FSB_OK) rc = ensure_region(h, s, (int64_t)s->hist.size() + (row_off[i + 1] - row_off[i]));
+            if (rc) return rc;
+        }
+    }
     b->n_rows = n_rows;
     b->n_vocab = n_vocab;
     b->ld = ld;
-    b->flags = flags;
+    b->flags = flags & ~FSB_APPEND_SAMPLED;
+    b->hist_dev = resident ? h->d_pool : nullptr;
+    b->gather_ids = 0;
     b->sid.assign((size_t)n_rows, 0);
     b->stochastic.assign((size_t)n_rows, 0);
-    std::vector<fsb::RowDesc> descs((size_t)n_rows);
+    b->descs.resize((size_t)n_rows);
     int32_t* hs = b->h_hist();
     int64_t pos = 0;
     for (int i = 0; i < n_streams; ++i) {
         Stream* s = get_stream(h, stream_ids[i]);
         const int r0 = row_off[i], m = row_off[i + 1] - r0;
-        const int64_t len = hist_off[i + 1] - hist_off[i];
+        const int64_t len = resident ? (int64_t)s->hist.size() : hist_off[i + 1] - hist_off[i];
         const bool pen_on = !(s->p.repetition_penalty == 1.0f || s->p.repeat_last_n == 0);
         // row r samples with history_i followed by draft_1..draft_r; the windows of successive rows only move
-        // forward, so one staged copy [b_0 .. len + m - 1) serves the whole stream
+        // forward, so one copy [b_0 .. len + m - 1) serves the whole stream: staged here, or the stream's pool region
         const int64_t b0 = pen_on ? window_begin(s->p, len) : len;
-        const int64_t base = pos;
-        if (pen_on) {
+        int64_t base = pos;
+        if (resident) {
+            base = s->pool_off + b0;
+        } else if (pen_on) {
             if (len > b0) std::memcpy(hs + pos, hist_flat + hist_off[i] + b0, sizeof(int32_t) * (size_t)(len - b0));
             pos += len - b0;
             for (int r = 1; r < m; ++r) hs[pos++] = rows_flat[r0 + r];
@@ -883,23 +959,40 @@ int fsb_verify_windows(fsb_handle* h, int n_streams, const int* stream_ids, cons
             }
             const uint64_t word = greedy ? 0ull : look();
             b->sid[(size_t)(r0 + r)] = stream_ids[i];
-            b->stochastic[(size_t)(r0 + r)] = greedy ? 0 : 1;
-            fill_desc(descs[(size_t)(r0 + r)], s->p, n_vocab, (int64_t)(r0 + r) * ld, hb, hl, word, r0 + r);
+            fsb::RowDesc& d = b->descs[(size_t)(r0 + r)];
+            fill_desc(h, d, s->p, n_vocab, (int64_t)(r0 + r) * ld, hb, hl, word, r0 + r);
+            if (resident && r >= 1 && hl >= 1) {   // draft_r is the last id of row r's window: a kernel puts it there before the launch
+                d.flags |= fsb::kRowDraft;
+                d.gather_off = rows_flat[r0 + r];
+            }
         }
     }
     b->hist_ids = pos;
-    rc = finalize_batch(h, b, descs);
-    if (rc) return rc;
-    rc = upload_batch(h, b);
-    if (rc) return rc;
-    const float* dev = logits;
-    if (flags & FSB_LOGITS_ON_HOST) {
-        rc = stage_host_logits(h, logits, n_rows, ld, n_vocab, &dev);
-        if (rc) return rc;
+    b->table_ints = 0;
+    const bool win_append = resident && (flags & FSB_APPEND_SAMPLED);
+    if (win_append) {
+        // per stream: first row, rows, accept limit, and where the stream's history ends in the id pool; the device walks
+        // the same accept loop as the host below and stores the last accepted token there (the confirmed drafts before
+        // it are in place already)
+        int32_t* tab = hs + pos;
+        for (int i = 0; i < n_streams; ++i) {
+            Stream* s = get_stream(h, stream_ids[i]);
+            const int r0 = row_off[i], m = row_off[i + 1] - r0;
+            const int64_t end = s->pool_off + (int64_t)s->hist.size();
+            int32_t* t = tab + (size_t)i * fsb::kWindowTableInts;
+            t[0] = r0;
+            t[1] = m;
+            t[2] = (max_accept && max_accept[i] > 0 && max_accept[i] < m) ? max_accept[i] : m;
+            t[3] = 0;
+            t[4] = (int32_t)(uint32_t)(end & 0xFFFFFFFFll);
+            t[5] = (int32_t)(end >> 32);
+            for (int r = 1; r < m; ++r) t[5 + r] = rows_flat[r0 + r];   // the drafts, for the comparison (at most kWindowTableInts - 6)
+        }
+        b->table_ints = (int64_t)n_streams * fsb::kWindowTableInts;
     }
-    rc = launch_batch(h, b, dev, (flags & FSB_KEEP_KEPT_SET) != 0);
+    rc = finalize_batch(h, b);
     if (rc) return rc;
-    rc = fetch_tokens(h, b, nullptr);
+    rc = run_staged(h, b, logits, flags & ~FSB_APPEND_SAMPLED, false, nullptr, resident ? n_streams : 0, win_append);   // no engine was advanced: nothing to roll back
     if (rc) return rc;
     // accept loop of src/server.cpp:626-636 on the sampled tokens
     for (int i = 0; i < n_streams; ++i) {
@@ -930,8 +1023,30 @@ int fsb_verify_windows(fsb_handle* h, int n_streams, const int* stream_ids, cons
         h->counters.rows_sampled += (uint64_t)acc;
         h->counters.drafted += (uint64_t)(m - 1);
         h->counters.accepted += (uint64_t)conf;
+        if (resident && (flags & FSB_APPEND_SAMPLED)) {
+            // what gen_token appends (src/server.cpp:342): the sampled tokens of the accepted rows
+            for (int r = 0; r < acc; ++r) s->hist.push_back(tokens_out[r0 + r]);
+            s->dev_len = (int64_t)s->hist.size();   // the device copy holds them: confirmed drafts, and the last token stored by the accept kernel
+        }
     }
     return FSB_OK;
+}
+
+int fsb_verify_windows(fsb_handle* h, int n_streams, const int* stream_ids, const int* row_off, const int32_t* rows_flat,
+                       const float* logits, int64_t ld, int n_vocab, const int32_t* hist_flat, const int64_t* hist_off,
+                       const int* max_accept, int32_t* tokens_out, int* acc_out, int* confirmed_out, unsigned flags) {
+    if (!h) return FSB_ERR_INVALID;
+    if (!hist_off) return fail(h, FSB_ERR_INVALID, "null argument");
+    return verify_windows_impl(h, n_streams, stream_ids, row_off, rows_flat, logits, ld, n_vocab, hist_flat, hist_off, max_accept, tokens_out, acc_out,
+                               confirmed_out, flags);
+}
+
+int fsb_verify_windows_resident(fsb_handle* h, int n_streams, const int* stream_ids, const int* row_off, const int32_t* rows_flat,
+                                const float* logits, int64_t ld, int n_vocab, const int* max_accept, int32_t* tokens_out, int* acc_out,
+                                int* confirmed_out, unsigned flags) {
+    if (!h) return FSB_ERR_INVALID;
+    return verify_windows_impl(h, n_streams, stream_ids, row_off, rows_flat, logits, ld, n_vocab, nullptr, nullptr, max_accept, tokens_out, acc_out,
+                               confirmed_out, flags);
 }
 
 int fsb_last_kept(fsb_handle* h, int row, int cap, int32_t* ids, double* probs, int* n_keep) {
@@ -956,11 +1071,14 @@ int fsb_batch_prepare(fsb_handle* h, int n_rows, const int* stream_ids, int64_t 
     if (n_rows <= 0 || !hist_off) return fail(h, FSB_ERR_INVALID, "bad arguments");
     cudaSetDevice(h->device);
     fsb_batch* b = nullptr;
-    int rc = alloc_batch(h, n_rows, hist_off[n_rows] - hist_off[0], &b);
+    int rc = alloc_batch(h, n_rows, hist_off[n_rows] - hist_off[0], 0, &b);
     if (rc) return rc;
     rc = stage_rows(h, b, n_rows, stream_ids, ld, n_vocab, hist_flat, hist_off, flags);
-    if (rc == FSB_OK) rc = upload_batch(h, b);
-    if (rc == FSB_OK && cudaStreamSynchronize(h->stream) != cudaSuccess) rc = fail(h, FSB_ERR_CUDA, "upload failed");
+    if (rc == FSB_OK) {
+        rc = upload_batch(h, b);
+        if (rc == FSB_OK && cudaStreamSynchronize(h->stream) != cudaSuccess) rc = fail(h, FSB_ERR_CUDA, "upload failed");
+        if (rc) rollback_draws(h, b);
+    }
     if (rc) {
         free_batch_buffers(b);
         delete b;
@@ -1011,8 +1129,8 @@ int fsb_batch_merge_launch(fsb_handle* h, fsb_batch* b, const uint64_t* lists_de
     if (b->n_full > 0) return fail(h, FSB_ERR_RANGE, "the batch has rows that cannot be sharded by vocabulary");
     cudaSetDevice(h->device);
     const bool keep_kept = (b->flags & FSB_KEEP_KEPT_SET) != 0;
-    const int e = fsb::launch_merge_lists(lists_dev, counts_dev, n_lists, b->n_cand, b->d_rows(), b->d_tokens, keep_kept ? h->d_kept_ids : nullptr,
-                                          keep_kept ? h->d_kept_pr : nullptr, keep_kept ? h->d_kept_n : nullptr, b->d_status(), h->stream);
+    const int e = fsb::launch_merge_lists(lists_dev, counts_dev, n_lists, fsb::kMaxK, b->n_cand, b->d_rows(), b->d_tokens, keep_kept ? h->d_kept_ids : nullptr,
+                                          keep_kept ? h->d_kept_pr : nullptr, keep_kept ? h->d_kept_n : nullptr, b->d_status(), h->scan_sums, h->stream);
     if (e != 0) return fail(h, FSB_ERR_CUDA, "merge kernel launch: %s", cudaGetErrorString((cudaError_t)e));
     h->counters.kernel_launches++;
     b->launched = true;
@@ -1024,7 +1142,7 @@ int fsb_batch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out) {
     if (!b->launched) return fail(h, FSB_ERR_INVALID, "the batch has not been launched");
     cudaSetDevice(h->device);
     const int rc = fetch_tokens(h, b, tokens_out);
-    if (rc == FSB_OK) count_rows(h, b, 0);
+    if (rc == FSB_OK) count_rows(h, b);
     return rc;
 }
 

@@ -94,7 +94,7 @@ class VocabShardedSampler:
     def __init__(self, engine, n_vocab: int, rank: int, world: int, group=None):
         self.engine, self.rank, self.world, self.group = engine, rank, world, group
         self.lo, self.hi = vocab_partition(n_vocab, world)[rank]
-        engine.set_vocab_offset(self.lo)
+        engine.set_vocab_shard(self.lo, n_vocab)
 
     @property
     def columns(self) -> tuple[int, int]:

@@ -63,7 +63,7 @@ enum {
     FSB_WRITE_BACK = 2u,     /* store the penalised logits back into the caller's rows, the reference's in-place side
                                 effect ("logits: [n_vocab], modified in place", src/sampler.h:26) */
     FSB_KEEP_KEPT_SET = 4u,  /* record every row's kept set (ids + probabilities) for fsb_last_kept */
-    FSB_APPEND_SAMPLED = 8u  /* fsb_sample_batch_resident only: append every row's token to its stream's resident history */
+    FSB_APPEND_SAMPLED = 8u  /* resident calls only: append the sampled tokens to their streams' resident histories */
 };
 
 /* Largest effective k (after the reference's clamp k = (0 < top_k < n_vocab) ? top_k : n_vocab) that
@@ -87,11 +87,11 @@ FSB_API int fsb_set_cuda_stream(fsb_handle* h, void* cuda_stream);
  * of src/model_gemma4.cpp:520-521).  cap = 0 turns it off (the default: the caller's logits are final). */
 FSB_API int fsb_set_softcap(fsb_handle* h, float cap);
 
-/* Diagnostics: when set to a device buffer of 8 uint64 per CTA (4096 CTAs at most), the streaming kernel writes
- * time stamps of its phases there: slot 0 the CTA's start in %globaltimer ns, slot 7 the start in SM cycles, and in
- * SM cycles: 1 barriers set up, 4 streaming done and final bound known (last segment), 2 element list built,
- * 5 candidates ordered and published or merged, 6 exit.  Slot 3 is unused.  NULL (the default) turns it off.
- * No reference counterpart. */
+/* Diagnostics: when set to a device buffer of 16 uint64 per CTA (one CTA per SM at most), the streaming kernel writes
+ * %globaltimer time stamps (ns) of its phases there: 0 CTA start, 1 first work item handed over, 2 first tile in
+ * shared memory, 4 last tile of an item consumed, 5 the item's candidates gathered, 6 ordered, 7 published and ticket
+ * drawn, 8 the row's lists merged, 9 epilogue done (4-9: the CTA's last item that got there), 10 exit; slot 3 = work
+ * items the CTA processed.  NULL (the default) turns it off.  No reference counterpart. */
 FSB_API int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer);
 
 /* Overlap of consecutive launches (off by default).  When on, fsb_batch_launch starts the streaming kernel with
@@ -102,8 +102,20 @@ FSB_API int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer);
  * read anything, so they gain nothing.  No reference counterpart. */
 FSB_API int fsb_set_launch_overlap(fsb_handle* h, int on);
 
-/* Column offset of this device's vocabulary shard: local column c is token id c + offset (vocab sharding). */
+/* Epilogue sums (off by default).  The reference adds the candidates' probabilities one after the other in
+ * candidate order (src/sampler.cpp:41,44,46); by default one thread does the same, so the sums carry the reference's
+ * own rounding.  When on, the two sums of a row are warp prefix scans: a few hundred nanoseconds faster per row, the
+ * probabilities differ from the reference's in the last bits (~1e-16, against the 1e-6 the parity contract allows), and
+ * a draw can differ only if its uniform lands that close to a boundary of the cumulative distribution.
+ * No reference counterpart. */
+FSB_API int fsb_set_scan_sums(fsb_handle* h, int on);
+
+/* Column offset of this device's vocabulary shard: local column c is token id c + offset (vocab sharding).
+ * fsb_set_vocab_shard also tells the engine how many columns the whole row has, so that a row's candidate count
+ * follows the whole row (k = (0 < top_k < global_vocab) ? top_k : global_vocab, src/sampler.cpp:27) even when top_k
+ * exceeds the shard's width; global_vocab = 0 means "this engine holds whole rows". */
 FSB_API int fsb_set_vocab_offset(fsb_handle* h, int32_t offset);
+FSB_API int fsb_set_vocab_shard(fsb_handle* h, int32_t offset, int32_t global_vocab);
 
 /* Reference defaults (src/sampler.h:13-20) and the range check of the reference's request parser
  * (src/server.cpp:1071: temperature >= 0, 0 < top_p <= 1, top_k >= 0, repetition_penalty > 0, repeat_last_n >= -1)
@@ -161,6 +173,16 @@ FSB_API int fsb_sample_batch_resident(fsb_handle* h, int n_rows, const int* stre
 FSB_API int fsb_verify_windows(fsb_handle* h, int n_streams, const int* stream_ids, const int* row_off, const int32_t* rows_flat,
                        const float* logits, int64_t ld, int n_vocab, const int32_t* hist_flat, const int64_t* hist_off,
                        const int* max_accept, int32_t* tokens_out, int* acc_out, int* confirmed_out, unsigned flags);
+
+/* fsb_verify_windows with every stream's history taken from its resident history (fsb_stream_history_*): a
+ * speculative step then uploads the drafts only.  The drafts are written behind the stream's history in the id pool
+ * before the launch (the pool must have room for history + window rows per stream).  With FSB_APPEND_SAMPLED the
+ * sampled tokens of the accepted rows are appended to the stream's history (what gen_token does next,
+ * src/server.cpp:342): on the device by a small kernel that walks the same accept loop, in the mirror after the
+ * read-back; a window may then hold at most 66 drafts.  Without the flag the histories are left as they were. */
+FSB_API int fsb_verify_windows_resident(fsb_handle* h, int n_streams, const int* stream_ids, const int* row_off, const int32_t* rows_flat,
+                                        const float* logits, int64_t ld, int n_vocab, const int* max_accept, int32_t* tokens_out,
+                                        int* acc_out, int* confirmed_out, unsigned flags);
 
 /* Kept set of row `row` of the most recent call made with FSB_KEEP_KEPT_SET: the candidates that survived
  * min-p / top-p in (logit descending, id ascending) order with their probabilities (normalised over the k
