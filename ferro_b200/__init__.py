@@ -44,6 +44,7 @@ API_SYMBOLS = [
     "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap", "fsb_batch_shard_launch", "fsb_batch_merge_launch", "fsb_argmax_rows_static", "fsb_stream_history_set", "fsb_stream_history_append", "fsb_stream_history_len",
     "fsb_sample_batch_resident",
     "fsb_set_trace_buffer", "fsb_set_scan_sums", "fsb_set_vocab_shard", "fsb_verify_windows_resident",
+    "fsb_server_defaults_init", "fsb_params_from_request", "fsb_params_apply_cli_flag",
     "fsb_params_default", "fsb_params_validate", "fsb_stream_open", "fsb_stream_close", "fsb_stream_params",
     "fsb_stream_state_get", "fsb_stream_state_set", "fsb_sample_batch", "fsb_verify_windows", "fsb_last_kept",
     "fsb_batch_prepare", "fsb_batch_redraw", "fsb_batch_launch", "fsb_batch_tokens", "fsb_batch_kernel_count",
@@ -97,6 +98,10 @@ def load_library(build_if_missing: bool = True):
     L.fsb_verify_windows_resident.argtypes = [vp, i32, vp, vp, vp, vp, i64, i32, vp, vp, vp, vp, u32]
     L.fsb_params_default.argtypes = [vp]
     L.fsb_params_default.restype = None
+    L.fsb_server_defaults_init.argtypes = [vp]
+    L.fsb_server_defaults_init.restype = None
+    L.fsb_params_from_request.argtypes = [vp, vp, C.c_int32, vp]
+    L.fsb_params_apply_cli_flag.argtypes = [vp, vp, C.c_char_p, C.c_char_p]
     L.fsb_params_validate.argtypes = [vp]
     L.fsb_stream_open.argtypes = [vp, vp, C.POINTER(i32)]
     L.fsb_stream_close.argtypes = [vp, i32]
@@ -121,7 +126,7 @@ def load_library(build_if_missing: bool = True):
     L.fsb_sample_batch_resident.argtypes = [vp, i32, vp, vp, i64, i32, vp, u32]
     L.fsb_argmax_rows_static.argtypes = [C.c_int, vp, i64, i32, i32, vp, vp, u32]
     for name in API_SYMBOLS:
-        if name not in ("fsb_last_error", "fsb_params_default"):
+        if name not in ("fsb_last_error", "fsb_params_default", "fsb_server_defaults_init"):
             getattr(L, name).restype = i32
     _lib = L
     return L

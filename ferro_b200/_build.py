@@ -13,7 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libferro_sampler_b200.so")
-SOURCES = ["fsb_kernels.cu", "fsb_fullrow.cu", "fsb_shim.cpp"]
+SOURCES = ["fsb_kernels.cu", "fsb_fullrow.cu", "fsb_shim.cpp", "fsb_request.cpp"]
 HEADERS = ["fsb_internal.h", "fsb_device.cuh", os.path.join("..", "..", "include", "ferro_sampler_b200.h")]
 
 NVCC_FLAGS = [

@@ -131,7 +131,7 @@ struct SharedCtl {
     u64 item_free[2];                 // "the consumers are done with the item's descriptor and bitmap"
     u64 red[2 * kNumWarps];           // cross-warp reduction scratch
     double dsum;
-    alignas(16) float wbound[kNumWarps];   // per-warp admission bounds (see the streaming kernel); read with 16-byte loads
+    alignas(16) u64 wbound[kNumWarps];     // per-warp admission bounds (see the streaming kernel): item tag << 32 | float bits
     int wcount[kMaxChunks];           // lengths of a row's ordered candidate lists while they are merged
     int sum[3];                       // rotating counters of the selection steps
     int out_cnt;
@@ -140,6 +140,7 @@ struct SharedCtl {
     int imax, imin1, imin2;
     int abort;                        // a wait ran out of time: every later wait is cut short, the kernel winds down
     RowDesc cur;                      // descriptor of the item whose end-of-item work is running
+    RowDesc prev;                     // descriptor of the row whose ticket is still on its way (see the streaming kernel)
     ItemCtx item[2];
 };
 
@@ -269,80 +270,28 @@ __device__ __forceinline__ u64 warp_sort32_desc(u64 v) {
 }
 
 // Orders the k largest of buf[0..n) (distinct composites in shared memory; fewer if n < k) into out[0..kk),
-// descending, and returns kk = min(n, k).  Lists longer than kListCap are first cut down to k by bisection.  The
-// list is cut into runs of 32: warp w sorts runs w and w + 16 in registers and puts them back; then the thread that
-// holds entry i of a run finds by binary search how many entries of every other run are larger - the sum, plus i,
-// is the entry's rank.  buf is overwritten (with room for the last run's padding: 32 * ceil(n / 32) entries); `out`
-// has room for kMaxK composites and must not overlap buf.  All consumer threads must call, after a barrier that
-// made buf visible; out is visible to all on return.
+// descending, and returns kk = min(n, k).  Lists longer than kThreads entries are first cut down to k by bisection.
+// The rank of an entry is the number of entries above it: entry i is counted by kThreads / n' neighbouring threads
+// (n' = n rounded up to a power of two), each over its share of the list (every load is a broadcast), and their
+// counts are added with shuffles.  buf is overwritten only by the cut; `out` has room for kMaxK composites and must
+// not overlap buf.  All consumer threads must call, after a barrier that made buf visible; out is visible on return.
 static __device__ __forceinline__ int topk_sorted(u64* buf, int n, int k, u64* out, SharedCtl* ctl) {
-    static_assert(kListCap <= 64 * kNumWarps, "two runs per warp");
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (n > kListCap) n = select_list_topk(buf, n, k, out, ctl);
-    const int runs = (n + 31) >> 5;
-    u64 c[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int r = warp + h * kNumWarps;
-        c[h] = 0ull;   // 0 is below every composite: padding sorts to the end of the last run
-        if (r < runs) {
-            const int i = 32 * r + lane;
-            c[h] = warp_sort32_desc(i < n ? buf[i] : 0ull);
-            buf[i] = c[h];
-        }
-    }
-    consumer_sync();
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        if (c[h] == 0ull) continue;
-        const int mine = warp + h * kNumWarps;
-        int rank = lane;
-#pragma unroll 1
-        for (int r2 = 0; r2 < runs; ++r2) {
-            if (r2 == mine) continue;
-            const u64* run = buf + 32 * r2;   // descending: count its entries above c
-            int lo = 0;
-#pragma unroll
-            for (int step = 16; step > 0; step >>= 1)
-                if (run[lo + step - 1] > c[h]) lo += step;
-            if (run[lo] > c[h]) ++lo;
-            rank += lo;
-        }
-        if (rank < k) out[rank] = c[h];
-    }
+    const int tid = threadIdx.x;
+    if (n > kThreads) n = select_list_topk(buf, n, k, out, ctl);
+    int shift = 0;   // log2 of the threads per entry
+    while ((n << (shift + 1)) <= kThreads && shift < 5) ++shift;
+    const int P = 1 << shift;
+    const int i = tid >> shift, part = tid & (P - 1);
+    const int len = (n + P - 1) >> shift;
+    const int j0 = part * len, j1 = min(n, j0 + len);
+    const u64 c = i < n ? buf[i] : ~0ull;
+    int cnt = 0;
+#pragma unroll 4
+    for (int j = j0; j < j1; ++j) cnt += buf[j] > c ? 1 : 0;
+    for (int o = 1; o < P; o <<= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+    if (i < n && part == 0 && cnt < k) out[cnt] = c;
     consumer_sync();
     return n < k ? n : k;
-}
-
-// Merges n_lists descending lists of composites that lie k entries apart in buf (list s at buf + s * k, its length
-// in ctl->wcount[s], at most k) into out[0..kk), descending, kk = min(total, k): the rank of an entry is its place in
-// its own list plus, for every other list, the number of entries above it (binary search).  All consumer threads
-// must call, after a barrier that made buf and the counts visible; out is visible on return.
-static __device__ __forceinline__ int merge_sorted_lists(const u64* buf, int n_lists, int k, u64* out, SharedCtl* ctl) {
-    const int tid = threadIdx.x;
-    const int span = n_lists * k;
-    int total = 0;
-    for (int s2 = 0; s2 < n_lists; ++s2) total += ctl->wcount[s2];
-    for (int e = tid; e < span; e += kThreads) {
-        const int s1 = e / k, i1 = e - s1 * k;
-        if (i1 >= ctl->wcount[s1]) continue;
-        const u64 c = buf[e];
-        int rank = i1;
-        for (int s2 = 0; s2 < n_lists && rank < k; ++s2) {
-            if (s2 == s1) continue;
-            const u64* run = buf + s2 * k;
-            int lo = 0, hi = ctl->wcount[s2];
-            while (lo < hi) {
-                const int mid = (lo + hi) >> 1;
-                if (run[mid] > c) lo = mid + 1;
-                else hi = mid;
-            }
-            rank += lo;
-        }
-        if (rank < k) out[rank] = c;
-    }
-    consumer_sync();
-    return total < k ? total : k;
 }
 
 // srt[0..kk) holds the row's candidates in order (largest first).  Either hands them out (vocabulary-sharded mode)

@@ -86,6 +86,7 @@ struct StreamArgs {
     float softcap;             // 0 = off
     int32_t overlap;           // launch with programmatic stream serialization (see fsb_set_launch_overlap)
     int32_t scan_sums;         // epilogue: 0 = sums in candidate order by one thread (the reference's order), 1 = warp prefix scan
+    int32_t debug;             // development switches (wrong results): 1 admit nothing, 2 skip the end-of-item work, 4 skip the penalty
     uint8_t chunk_len[kMaxChunks];
 };
 

@@ -15,19 +15,19 @@ namespace {
 
 constexpr int kWarps = kThreads / 32;
 constexpr int kWTile = kTile / kWarps;          // 512 logits: a warp's part of a CTA tile
-constexpr int kCopyWarp = kWarps;               // issues the bulk copies
-constexpr int kSetupWarp = kWarps + 1;          // fetches work items, builds their penalty bitmaps
-constexpr int kBlockThreads = kThreads + 64;
+constexpr int kCopyWarp = kWarps;               // fetches work items, issues the bulk copies
+constexpr int kSetupWarp0 = kWarps + 1;         // two set-up warps (one per hand-over slot): descriptors, penalty bitmaps
+constexpr int kBlockThreads = kThreads + 96;
 
 constexpr size_t kSmemStage = (size_t)kStages * kTile * sizeof(float);
 constexpr size_t kSmemPools = (size_t)kWarps * kPoolCap * sizeof(u64);          // the warps' candidate pools; a row's lists while they are merged
 constexpr size_t kSmemBitmap = 2 * (size_t)kItemBitmapWords * sizeof(unsigned);   // penalty bitmaps of two work items
-constexpr size_t kSmemList = (size_t)kListCap * sizeof(u64);                    // an item's candidates; the epilogue's doubles
+constexpr size_t kSmemList = (size_t)kListCap * sizeof(u64);                    // an item's candidates
 constexpr size_t kSmemSorted = (size_t)kMaxK * sizeof(u64);                     // ordered candidates
-constexpr size_t kSmemTotal = kSmemStage + kSmemPools + kSmemBitmap + kSmemList + kSmemSorted + sizeof(SharedCtl);
+constexpr size_t kSmemWork = 2 * (size_t)kMaxK * sizeof(double);                // the epilogue's doubles
+constexpr size_t kSmemTotal = kSmemStage + kSmemPools + kSmemBitmap + kSmemList + kSmemSorted + kSmemWork + sizeof(SharedCtl);
 static_assert(kSmemTotal <= 227 * 1024, "one CTA per SM");
 static_assert(kSmemPools >= (size_t)kRowScratch * sizeof(u64), "a row's published lists fit into the pools' memory");
-static_assert(kSmemList >= 2 * (size_t)kMaxK * sizeof(double), "the epilogue's arrays live in the list's memory");
 static_assert(kWTile == 512, "a lane owns four float4 of a warp tile");
 static_assert(kPoolCap >= kMaxK + 128, "a warp keeps its k best and still has room for the candidates of 128 cells");
 static_assert(kPoolCap % 32 == 0 && kPoolCap / 32 <= 12, "a warp holds its pool in twelve registers per lane when it selects");
@@ -42,10 +42,11 @@ constexpr long long kWaitCycles = 2000000000ll;   // about 1 s: a wait that has 
 // every row, then the second, ...): the small chunks at the end of the schedule even out the finish.
 //
 // A CTA has three kinds of warps, which meet only at mbarriers:
-//   * the set-up warp fetches the next item, reads the row's descriptor and builds the bitmap of the item's
-//     penalised columns from the row's window ids - one item ahead of the consumers;
-//   * the copy warp brings the item's tiles into a ring of kStages shared-memory slots, one 1-D bulk copy per
-//     tile, so every logit is read from HBM exactly once; it runs ahead of the consumers across item borders;
+//   * the copy warp draws the items and brings their tiles into a ring of kStages shared-memory slots, one 1-D
+//     bulk copy per tile, so every logit is read from HBM exactly once; it runs ahead of the consumers across item
+//     borders;
+//   * two set-up warps, one per hand-over slot, read the item's row descriptor and build the bitmap of the item's
+//     penalised columns from the row's window ids - while the consumers work on the items before;
 //   * sixteen consumer warps each own one sixteenth (512 logits) of every tile.  A lane owns four cells (float4)
 //     per tile.  It takes each cell's maximum; a warp whose lanes all stay below the admission bound is done with
 //     the tile.  Otherwise the logits that reach the bound go, as composites, into the warp's pool in shared memory
@@ -55,9 +56,10 @@ constexpr long long kWaitCycles = 2000000000ll;   // about 1 s: a wait that has 
 //     earlier chunks have left in global memory.  A warp whose pool fills up drops what the bound has overtaken
 //     and, if that is not enough (rows of equal values), keeps exactly its k best - ties by token id.
 // At the end of an item the warps' surviving candidates are gathered, ordered, and the k best published in the
-// item's part of the row's scratch; the CTA that publishes the row's last chunk (a ticket) merges the ordered
-// lists and runs the epilogue.  No CTA ever waits for another CTA; waits for this CTA's own copies and
-// hand-overs are bounded.
+// item's part of the row's scratch, and a ticket is drawn for the row.  The ticket's value is looked at one item
+// later (its round trip to L2 overlaps the next item): the CTA that drew the row's last ticket merges the row's
+// lists and runs the epilogue.  No CTA ever waits for another CTA; waits for this CTA's own copies and hand-overs
+// are bounded.
 
 // The shared memory of a CTA.
 struct Smem {
@@ -66,6 +68,7 @@ struct Smem {
     unsigned* bitmap;   // [2][kItemBitmapWords]
     u64* list;          // [kListCap] the item's candidates
     u64* sorted;        // [kMaxK] the k best, in order
+    double* work;       // [2 * kMaxK] the epilogue's arrays
     SharedCtl* ctl;
 };
 __device__ __forceinline__ Smem smem_view() {
@@ -82,6 +85,8 @@ __device__ __forceinline__ Smem smem_view() {
     p += kSmemList;
     m.sorted = reinterpret_cast<u64*>(p);
     p += kSmemSorted;
+    m.work = reinterpret_cast<double*>(p);
+    p += kSmemWork;
     m.ctl = reinterpret_cast<SharedCtl*>(p);
     return m;
 }
@@ -129,51 +134,48 @@ __device__ __forceinline__ void patch_tile(float* st, int len, int col0, int ite
     __syncwarp();
 }
 
-// The r-th largest (r = 1..32) of the 32 lane values of a warp: a bitonic sort across the lanes.
-__device__ __forceinline__ unsigned warp_rth_largest(unsigned v, int r) {
-    const int lane = threadIdx.x & 31;
-#pragma unroll
-    for (int k = 2; k <= 32; k <<= 1) {
-#pragma unroll
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            const unsigned o = __shfl_xor_sync(0xffffffffu, v, j);
-            const bool up = (lane & k) == 0;   // k == 32: every lane, the final order is ascending
-            const bool low = (lane & j) == 0;
-            v = (up == low) ? min(v, o) : max(v, o);
-        }
-    }
-    return __shfl_sync(0xffffffffu, v, 32 - r);
-}
-
 // A bound that at least r = min(32, ceil(k / warps)) logits of this warp's stream reach: the r-th largest of the
-// lanes' running maxima (each is a logit of its own).
+// lanes' running maxima (each is a logit of its own) - r rounds of a warp-wide maximum, the holder drops out.
 __device__ __forceinline__ float warp_bound(float run_max, int k) {
     const int r = min(32, (k + kWarps - 1) / kWarps);
-    const unsigned key = warp_rth_largest(float_key(run_max), r);
-    return key_float(key);
+    const unsigned lane = threadIdx.x & 31;
+    unsigned key = float_key(run_max), m = 0u;
+#pragma unroll 1
+    for (int j = 0; j < r; ++j) {
+        m = __reduce_max_sync(0xffffffffu, key);
+        const unsigned holders = __ballot_sync(0xffffffffu, key == m);
+        if (lane == (unsigned)__ffs(holders) - 1u) key = 0u;   // below the key of every float
+    }
+    return key_float(m);
 }
 
 // Admission bound of the CTA: at least k logits of the item reach the smallest of the warps' bounds (sixteen
 // warps, at least ceil(k / 16) logits each, or 32 * 16 >= kMaxK), so no logit below it is among the item's k
-// best.  Each warp posts its value; within an item values only grow, so a reader may use another warp's older
-// value without a barrier.
-__device__ __forceinline__ float min_warp_bounds(SharedCtl* ctl) {
+// best.  Each warp posts its value with the item's tag; within an item values only grow, so a reader may use
+// another warp's older value without a barrier - but only values of the same item: until every warp has posted
+// for this item there is no bound (-inf).
+__device__ __forceinline__ void post_warp_bound(SharedCtl* ctl, unsigned tag, float wb) {
+    if ((threadIdx.x & 31) == 0) *reinterpret_cast<volatile u64*>(&ctl->wbound[threadIdx.x >> 5]) = ((u64)tag << 32) | (u64)__float_as_uint(wb);
+}
+__device__ __forceinline__ float min_warp_bounds(SharedCtl* ctl, unsigned tag) {
     float m = __int_as_float(0x7f800000);
+    bool all = true;
 #pragma unroll
-    for (int w = 0; w < kWarps; w += 4) {
-        float4 v;   // volatile: re-read on every call
-        asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(&ctl->wbound[w])));
-        m = fminf(m, fminf(fminf(v.x, v.y), fminf(v.z, v.w)));
+    for (int w = 0; w < kWarps; w += 2) {
+        u64 a, b;   // volatile: re-read on every call
+        asm volatile("ld.volatile.shared.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(smem_u32(&ctl->wbound[w])));
+        all = all && (unsigned)(a >> 32) == tag && (unsigned)(b >> 32) == tag;
+        m = fminf(m, fminf(__uint_as_float((unsigned)a), __uint_as_float((unsigned)b)));
     }
-    return m;
+    return all ? m : -__int_as_float(0x7f800000);
 }
 
 // Diagnostics: time stamps of CTA phases (see fsb_set_trace_buffer).
 __device__ __forceinline__ void trace_mark(const StreamArgs& a, int slot) {
     if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
 }
-__device__ __forceinline__ void trace_set(const StreamArgs& a, int slot, u64 v) {
-    if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 16 + slot] = v;
+__device__ __forceinline__ void trace_add(const StreamArgs& a, int slot, u64 v) {
+    if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 16 + slot] += v;
 }
 
 // ---- a warp's pool of admitted candidates ----------------------------------------------------------------------
@@ -238,8 +240,8 @@ struct PoolState {
 // Makes room in a pool that is nearly full: refresh the bound, drop what it has overtaken; if the pool is still
 // too full (many equal values, or a stream that keeps rising), keep exactly the warp's k best - no logit of this
 // warp's stream below the k-th of them can be among the item's k best.
-__device__ __noinline__ PoolState compact_pool(u64* pool, int n, float thr, u64 wcomp, int k, SharedCtl* ctl) {
-    thr = fmaxf(thr, min_warp_bounds(ctl));
+__device__ __noinline__ PoolState compact_pool(u64* pool, int n, float thr, u64 wcomp, int k, SharedCtl* ctl, unsigned tag) {
+    thr = fmaxf(thr, min_warp_bounds(ctl, tag));
     n = filter_pool(pool, n, max(comp_floor_of(thr), wcomp));
     if (n > kPoolCap - 128) {
         const u64 L = warp_kth_largest(pool, n, k);
@@ -285,118 +287,51 @@ __device__ __noinline__ int overflow_select(u64* pool, int pn, int k, u64* list,
     return min(ctl->n_el, kListCap);
 }
 
-// ---- the set-up warp ------------------------------------------------------------------------------------------
-// Fetches work items (the first is the CTA's own number, the others come from the counter), reads the row's
-// descriptor, builds the bitmap of the item's penalised columns, and hands the item over: first to the copy warp
-// (as soon as the item's place is known), then to the consumers.
-__device__ __forceinline__ void setup_loop(const StreamArgs& a, const Smem& m) {
-    SharedCtl* ctl = m.ctl;
-    const int lane = threadIdx.x & 31;
-    int next_idx = (int)blockIdx.x;   // lane 0's copy counts
-    bool waited = !a.overlap;         // without launch overlap there is nothing to wait for
-    for (int seq = 0;; ++seq) {
-        const int b = seq & 1;
-        ItemCtx* ic = &ctl->item[b];
-        bool ok = true;
-        if (seq >= 2) ok = mbar_wait_bounded(&ctl->item_free[b], (unsigned)(((seq >> 1) - 1) & 1), ctl);
-        if (!ok && lane == 0) report_timeout(ctl, a.status);
-        const int idx = __shfl_sync(0xffffffffu, next_idx, 0);
-        if (!ok || idx >= a.n_items || *reinterpret_cast<volatile int*>(&ctl->abort)) {
-            if (lane == 0) {
-                ic->done = 1;
-                mbar_arrive(&ctl->item_posted[b]);
-                mbar_arrive(&ctl->item_ready[b]);
-            }
-            break;
-        }
-        const int chunk = idx / a.n_rows, row = idx - chunk * a.n_rows;
-        int tile0 = 0;
-        for (int c = 0; c < chunk; ++c) tile0 += a.chunk_len[c];
-        const int nt = a.chunk_len[chunk];
-        if (lane == 0) {
-            ic->done = 0;
-            ic->row = row;
-            ic->chunk = chunk;
-            ic->tile0 = tile0;
-            ic->ntiles = nt;
-            ic->row_ptr = a.logits + (a.row_ld >= 0 ? (int64_t)row * a.row_ld : a.rows[row].logits_off);
-            mbar_arrive(&ctl->item_posted[b]);   // the copies may start
-        }
-        // the row's descriptor: four lanes, 16 bytes each
-        if (lane < 4) reinterpret_cast<uint4*>(&ic->d)[lane] = __ldg(reinterpret_cast<const uint4*>(a.rows + row) + lane);
-        __syncwarp();
-        const RowDesc& d = ic->d;
-        if (lane == 0) {
-            // a bound the row's earlier chunks have left (never read before the previous launch is complete: it resets it)
-            unsigned key = 0u;
-            if (a.n_chunks > 1 && waited) key = __ldcg(a.row_bound + row);
-            ic->thr0 = key ? key_float(key) : -__int_as_float(0x7f800000);
-        }
-        if (d.flags & kRowPenalty) {
-            const int lo = tile0 * kTile, hi = min(a.n_vocab, (tile0 + nt) * kTile);
-            unsigned* bm = m.bitmap + (size_t)b * kItemBitmapWords;
-            const int words4 = ((hi - lo + 31) / 32 + 3) / 4;
-            for (int i = lane; i < words4; i += 32) reinterpret_cast<uint4*>(bm)[i] = make_uint4(0u, 0u, 0u, 0u);
-            __syncwarp();
-            const int32_t* h = a.hist + d.hist_begin;
-            const int n = d.hist_len;
-            for (int i0 = 0; i0 < n; i0 += 32 * 8) {   // eight loads in flight per lane
-                int c[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int i = i0 + 32 * u + lane;
-                    c[u] = i < n ? __ldg(h + i) - a.vocab_offset : -1;
-                }
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (c[u] >= lo && c[u] < hi) atomicOr(&bm[(c[u] - lo) >> 5], 1u << ((c[u] - lo) & 31));
-            }
-        }
-        __syncwarp();
-        if (lane == 0) {
-            mbar_arrive(&ctl->item_ready[b]);   // releases the warp's writes to the waiting consumers
-            // the next item's number, fetched now so that it is there when this item has been handed over
-            if (!waited) {
-                pdl_wait_prior();   // the counter belongs to the previous launch until that is complete
-                waited = true;
-            }
-            next_idx = (int)gridDim.x + (int)atomicAdd(a.work, 1u);
-        }
-    }
-    if (lane == 0) {
-        // the CTA that leaves last puts the counters back for the next launch (every CTA has drawn its last number)
-        if (!waited) pdl_wait_prior();
-        if (ticket_add_acq_rel(a.work + 1, 1u) == gridDim.x - 1u) {
-            a.work[0] = 0u;
-            a.work[1] = 0u;
-        }
-    }
-}
-
 // ---- the copy warp --------------------------------------------------------------------------------------------
-// One lane brings the items' tiles in, one 1-D bulk copy per tile (large copies: the copy engine's cost is per
-// request), into a ring of kStages slots.  A slot is refilled once all consumer warps have handed it back.
+// One lane draws the work items (the first is the CTA's own number, the others come from the counter in global
+// memory, fetched one item ahead), posts each item's place in the matrix to the set-up warp of its slot, and brings
+// the item's tiles in, one 1-D bulk copy per tile (large copies: the copy engine's cost is per request), into a
+// ring of kStages slots.  A slot is refilled once all consumer warps have handed it back.
 __device__ __forceinline__ void copy_loop(const StreamArgs& a, const Smem& m) {
     if ((threadIdx.x & 31) != 0) return;
     SharedCtl* ctl = m.ctl;
     const int V = a.n_vocab;
-    int it = 0;
-    for (int seq = 0;; ++seq) {
+    int next_idx = (int)blockIdx.x;
+    bool waited = !a.overlap;   // without launch overlap there is nothing to wait for
+    int it = 0, seq = 0;
+    bool ok = true;
+    for (;; ++seq) {
         const int b = seq & 1;
-        if (!mbar_wait_bounded(&ctl->item_posted[b], (unsigned)((seq >> 1) & 1), ctl)) {
-            report_timeout(ctl, a.status);
-            return;
+        ItemCtx* ic = &ctl->item[b];
+        // the slot is free once the consumers have looked at the last tile of the item two before
+        if (seq >= 2 && !mbar_wait_bounded(&ctl->item_free[b], (unsigned)(((seq >> 1) - 1) & 1), ctl)) ok = false;
+        const int idx = next_idx;
+        if (!ok || idx >= a.n_items || *reinterpret_cast<volatile int*>(&ctl->abort)) break;
+        const int chunk = idx / a.n_rows, row = idx - chunk * a.n_rows;
+        int tile0 = 0;
+        for (int c = 0; c < chunk; ++c) tile0 += a.chunk_len[c];
+        const int nt = a.chunk_len[chunk];
+        const float* row_ptr = a.logits + (a.row_ld >= 0 ? (int64_t)row * a.row_ld : a.rows[row].logits_off);
+        ic->done = 0;
+        ic->row = row;
+        ic->chunk = chunk;
+        ic->tile0 = tile0;
+        ic->ntiles = nt;
+        ic->row_ptr = row_ptr;
+        mbar_arrive(&ctl->item_posted[b]);   // the slot's set-up warp may start
+        // the next item's number: the round trip to the counter overlaps this item's copies
+        if (!waited) {
+            pdl_wait_prior();   // the counter belongs to the previous launch until that is complete
+            waited = true;
         }
-        const ItemCtx* ic = &ctl->item[b];
-        if (ic->done) return;
-        const float* row_ptr = ic->row_ptr;
-        const int tile0 = ic->tile0, nt = ic->ntiles;
-        for (int j = 0; j < nt; ++j, ++it) {
+        next_idx = (int)gridDim.x + (int)atomicAdd(a.work, 1u);
+        if (!a.bulk_ok) continue;   // rows not on 16-byte boundaries: the consumers load their tiles themselves
+        for (int j = 0; j < nt && ok; ++j, ++it) {
             const int slot = it % kStages;
             // the first kStages tiles find their slots free; later ones wait for the consumers' hand-back
             if (it >= kStages && !mbar_wait_bounded(&ctl->empty[slot], (unsigned)((it / kStages - 1) & 1), ctl)) {
-                report_timeout(ctl, a.status);
-                return;
+                ok = false;
+                break;
             }
             const int col0 = (tile0 + j) * kTile;
             const int len = min(kTile, V - col0);   // >= 1
@@ -412,22 +347,193 @@ __device__ __forceinline__ void copy_loop(const StreamArgs& a, const Smem& m) {
                 mbar_arrive(&ctl->full[slot]);
             }
         }
+        if (!ok) {
+            ++seq;
+            break;
+        }
+    }
+    if (!ok) report_timeout(ctl, a.status);
+    // no more work: both slots say so (the consumers stop at the first, the other releases its set-up warp)
+    for (int e = 0; e < 2; ++e, ++seq) {
+        const int b = seq & 1;
+        if (e == 1 && seq >= 2) mbar_wait_bounded(&ctl->item_free[b], (unsigned)(((seq >> 1) - 1) & 1), ctl);
+        ctl->item[b].done = 1;
+        mbar_arrive(&ctl->item_posted[b]);
+    }
+    // the CTA that leaves last puts the counters back for the next launch (every CTA has drawn its last number)
+    if (!waited) pdl_wait_prior();
+    if (ticket_add_acq_rel(a.work + 1, 1u) == gridDim.x - 1u) {
+        a.work[0] = 0u;
+        a.work[1] = 0u;
+    }
+}
+
+// ---- the set-up warps -----------------------------------------------------------------------------------------
+// Warp `b` serves hand-over slot b (items 0, 2, 4, ... or 1, 3, 5, ... of the CTA): once the copy warp has posted
+// the item, it reads the row's descriptor and the bound the row's earlier chunks have left, builds the bitmap of
+// the item's penalised columns, and hands the item to the consumers.
+__device__ __forceinline__ void setup_loop(const StreamArgs& a, const Smem& m, int b) {
+    SharedCtl* ctl = m.ctl;
+    const int lane = threadIdx.x & 31;
+    ItemCtx* ic = &ctl->item[b];
+    unsigned* bm = m.bitmap + (size_t)b * kItemBitmapWords;
+    for (int n = 0;; ++n) {
+        const bool ok = mbar_wait_bounded(&ctl->item_posted[b], (unsigned)(n & 1), ctl);
+        if (!ok && lane == 0) report_timeout(ctl, a.status);
+        if (!ok || ic->done) {
+            if (lane == 0) {
+                ic->done = 1;
+                mbar_arrive(&ctl->item_ready[b]);
+            }
+            return;
+        }
+        const int row = ic->row, tile0 = ic->tile0, nt = ic->ntiles;
+        // the row's descriptor (four lanes, 16 bytes each) and the row's bound, all loads in flight together.  The bound
+        // is not read by the first item of a launch that overlaps its predecessor (which resets it when it completes).
+        uint4 dq = make_uint4(0u, 0u, 0u, 0u);
+        unsigned key = 0u;
+        if (lane < 4) dq = __ldg(reinterpret_cast<const uint4*>(a.rows + row) + lane);
+        if (lane == 4 && a.n_chunks > 1 && (!a.overlap || n > 0 || b > 0)) key = __ldcg(a.row_bound + row);
+        if (lane < 4) reinterpret_cast<uint4*>(&ic->d)[lane] = dq;
+        if (lane == 4) ic->thr0 = key ? key_float(key) : -__int_as_float(0x7f800000);
+        __syncwarp();
+        const RowDesc& d = ic->d;
+        if (d.flags & kRowPenalty) {
+            const int lo = tile0 * kTile, hi = min(a.n_vocab, (tile0 + nt) * kTile);
+            const int32_t* h = a.hist + d.hist_begin;
+            const int nh = d.hist_len;
+            int c[16];   // the first 512 window ids: loads issued before the bitmap is cleared
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int i = 32 * u + lane;
+                c[u] = i < nh ? __ldg(h + i) - a.vocab_offset : -1;
+            }
+            const int words4 = ((hi - lo + 31) / 32 + 3) / 4;
+            for (int i = lane; i < words4; i += 32) reinterpret_cast<uint4*>(bm)[i] = make_uint4(0u, 0u, 0u, 0u);
+            __syncwarp();
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
+                if (c[u] >= lo && c[u] < hi) atomicOr(&bm[(c[u] - lo) >> 5], 1u << ((c[u] - lo) & 31));
+            for (int i0 = 512; i0 < nh; i0 += 512) {
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    const int i = i0 + 32 * u + lane;
+                    c[u] = i < nh ? __ldg(h + i) - a.vocab_offset : -1;
+                }
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    if (c[u] >= lo && c[u] < hi) atomicOr(&bm[(c[u] - lo) >> 5], 1u << ((c[u] - lo) & 31));
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->item_ready[b]);   // releases the warp's writes to the waiting consumers
     }
 }
 
 // ---- the end of an item ---------------------------------------------------------------------------------------
-// All consumer threads call it once they have looked at the item's last tile: the final bound, the warps'
-// surviving candidates gathered into the list, the k best in order, published; in the CTA that publishes the
-// row's last chunk, the merge of the row's lists and the epilogue.
-__device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64* pool, int pn, float thr, u64 wcomp, float run_max, int row,
-                                         int chunk) {
+// What the consumers carry from one item's end to the next: the row whose ticket is on its way (-1: none) and,
+// in thread 0 only, the ticket.
+struct Pending {
+    int row;
+    unsigned ticket;
+};
+
+// The ticket of the row in `pend` has had an item's time to arrive: if it was the row's last, all chunks of the row
+// have published, and this CTA merges their ordered lists and runs the epilogue.  All consumer threads call.  Uses
+// the pools' memory (idle between items), the list, the ordered-candidate array and the epilogue's arrays.
+__device__ __forceinline__ void resolve_pending(const StreamArgs& a, const Smem& m, Pending& pend) {
     SharedCtl* ctl = m.ctl;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int k = ctl->cur.k;
-    const float wb = warp_bound(run_max, k);
-    if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int row = pend.row;
+    if (row < 0) return;
+    if (tid == 0) ctl->last = (pend.ticket == (unsigned)(a.n_chunks - 1)) ? 1 : 0;
+    pend.row = -1;
     consumer_sync();
-    thr = fmaxf(thr, min_warp_bounds(ctl));
+    if (!ctl->last) return;
+    trace_mark(a, 7);
+    const RowDesc d = ctl->prev;
+    const int k = d.k, nl = a.n_chunks;
+    const u64* src = reinterpret_cast<const u64*>(a.scratch) + (size_t)row * (size_t)a.scratch_stride;
+    if (tid == 0) {
+        a.ticket[row] = 0u;   // ready for the next launch
+        a.row_bound[row] = 0u;
+    }
+    // Every chunk's list is ordered, so entry p - 1 of each (p = ceil(k / lists)) bounds the row's k best from below:
+    // at least p entries of every list reach the smallest of them.  Lists, counts and those entries are read in one
+    // go (L2 reads, never L1); entries past a list's count are stale and dropped below.
+    const int p = (k + nl - 1) / nl;
+    u64* lists = m.pools;
+    const int span = nl * k;
+    for (int e = tid; e < span; e += kThreads) lists[e] = __ldcg(src + e);
+    if (tid < nl) {
+        const int cnt = min((int)__ldcg(src + a.scratch_stride - 1 - tid), k);
+        ctl->wcount[tid] = cnt;
+        const u64 bj = __ldcg(src + (size_t)tid * k + (p - 1));
+        ctl->red[tid] = cnt >= p ? bj : 0ull;   // a list shorter than p: no bound at all
+    }
+    if (tid == 0) ctl->n_el = 0;
+    consumer_sync();
+    u64 bound = ~0ull;
+    for (int s = 0; s < nl; ++s) bound = min(bound, ctl->red[s]);
+    // the entries that reach the bound go to the list (at least k of them, a few dozen more as a rule)
+    for (int e0 = 0; e0 < span; e0 += kThreads) {
+        const int e = e0 + tid;
+        u64 c = 0ull;
+        bool take = false;
+        if (e < span) {
+            const int s1 = e / k, i1 = e - s1 * k;
+            c = lists[e];
+            take = i1 < ctl->wcount[s1] && c >= bound;
+        }
+        const unsigned bmask = __ballot_sync(0xffffffffu, take);
+        int base = 0;
+        if (lane == 0 && bmask) base = atomicAdd(&ctl->n_el, __popc(bmask));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        const int at = base + __popc(bmask & ((1u << lane) - 1u));
+        if (take && at < kListCap) m.list[at] = c;
+    }
+    consumer_sync();
+    int n = ctl->n_el;
+    if (n > kListCap) {
+        // more than the list holds (short lists, so no bound): close the gaps between the lists (a list never moves
+        // past its own start), then select among all entries where they lie.  Rare.
+        int total = 0;
+        for (int s = 0; s < nl; ++s) {
+            const int cnt = ctl->wcount[s];
+            for (int i0 = 0; i0 < cnt; i0 += kThreads) {
+                const int i = i0 + tid;
+                const u64 v = i < cnt ? lists[s * k + i] : 0ull;
+                consumer_sync();
+                if (i < cnt) lists[total + i] = v;
+                consumer_sync();
+            }
+            total += cnt;
+        }
+        n = select_list_topk(lists, total, k, m.sorted, ctl);
+        for (int i = tid; i < n; i += kThreads) m.list[i] = lists[i];
+        consumer_sync();
+    }
+    if (tid == 0) ctl->n_el = 0;
+    const int kk = topk_sorted(m.list, n, k, m.sorted, ctl);
+    trace_mark(a, 8);
+    const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
+    const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index, a.scan_sums};
+    row_epilogue(m.sorted, kk, rt, m.work, tout);
+    trace_mark(a, 9);
+    consumer_sync();   // the list, the ordered candidates and the pools may be written again
+}
+
+// All consumer threads call it once they have looked at the item's last tile: the final bound, the warps'
+// surviving candidates gathered into the list, the k best in order - and, for a row that is one chunk, the
+// epilogue; otherwise the k best are published and a ticket is drawn, whose value the next call looks at.
+__device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64* pool, int pn, float thr, u64 wcomp, float run_max, int row,
+                                         int chunk, unsigned tag, Pending& pend) {
+    SharedCtl* ctl = m.ctl;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int k = ctl->cur.k;
+    post_warp_bound(ctl, tag, warp_bound(run_max, k));
+    consumer_sync();
+    thr = fmaxf(thr, min_warp_bounds(ctl, tag));
     pn = filter_pool(pool, pn, max(comp_floor_of(thr), wcomp));
     int base = 0;
     if (lane == 0 && pn) base = atomicAdd(&ctl->n_el, pn);
@@ -438,49 +544,43 @@ __device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64
     int n_el = ctl->n_el;
     if (n_el > kListCap) n_el = overflow_select(pool, pn, k, m.list, ctl);
     trace_mark(a, 5);
-    int kk = topk_sorted(m.list, n_el, k, m.sorted, ctl);
+    // the list is complete and the pools are idle: the row whose ticket has been on its way since the item before
+    if (pend.row >= 0) {
+        // (the merge uses the list: this item's candidates wait in the pools' upper half meanwhile - n_el <= kListCap entries)
+        u64* park = m.pools + (size_t)kRowScratch;
+        static_assert((size_t)kRowScratch + kListCap <= (size_t)kWarps * kPoolCap, "room to park an item's candidates during a merge");
+        for (int i = tid; i < n_el; i += kThreads) park[i] = m.list[i];
+        consumer_sync();
+        resolve_pending(a, m, pend);
+        for (int i = tid; i < n_el; i += kThreads) m.list[i] = park[i];
+        consumer_sync();
+    }
     if (tid == 0) ctl->n_el = 0;   // for the next item (barriers follow)
+    const int kk = topk_sorted(m.list, n_el, k, m.sorted, ctl);
     trace_mark(a, 6);
     pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
-    bool finish_here = true;
     if (a.n_chunks > 1) {
         // chunk c of a row publishes its ordered candidates at entries [c * k, c * k + count) of the row's scratch, the
         // count in entry stride - 1 - c, and leaves the bound they prove for the row's later chunks; then it draws a
-        // ticket, and the CTA that draws the row's last ticket merges.  The planner keeps chunks * (k + 1) within the stride.
+        // ticket.  The planner keeps chunks * (k + 1) within the stride.
         u64* dst = reinterpret_cast<u64*>(a.scratch) + (size_t)row * (size_t)a.scratch_stride;
         for (int i = tid; i < kk; i += kThreads) dst[chunk * k + i] = m.sorted[i];
         if (tid == 0) {
             dst[a.scratch_stride - 1 - chunk] = (u64)kk;
             if (kk == k) atomicMax(a.row_bound + row, (unsigned)(m.sorted[k - 1] >> 32));
+            ctl->prev = ctl->cur;
         }
         consumer_sync();   // orders the CTA's stores before the ticket, whose release publishes them to the device
-        if (tid == 0) ctl->last = (ticket_add_acq_rel(a.ticket + row, 1u) == (unsigned)(a.n_chunks - 1)) ? 1 : 0;
-        consumer_sync();
-        finish_here = ctl->last != 0;
-        trace_mark(a, 7);
-        if (finish_here) {   // all chunks of the row have published (L2 reads, never L1)
-            if (tid == 0) {
-                a.ticket[row] = 0u;   // ready for the next launch
-                a.row_bound[row] = 0u;
-            }
-            const int nl = a.n_chunks;
-            if (tid < nl) ctl->wcount[tid] = min((int)__ldcg(dst + a.scratch_stride - 1 - tid), k);
-            const int span = nl * k;
-            u64* lists = m.pools;   // the pools are idle until the next item starts
-            for (int e = tid; e < span; e += kThreads) lists[e] = __ldcg(dst + e);
-            consumer_sync();
-            kk = merge_sorted_lists(lists, nl, k, m.sorted, ctl);
-            trace_mark(a, 8);
-        }
-    }
-    if (finish_here) {
+        if (tid == 0) pend.ticket = ticket_add_acq_rel(a.ticket + row, 1u);   // not looked at before the next item's end
+        pend.row = row;
+    } else {
         const RowDesc& d = ctl->cur;
         const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
         const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index, a.scan_sums};
-        row_epilogue(m.sorted, kk, rt, reinterpret_cast<double*>(m.list), tout);
+        row_epilogue(m.sorted, kk, rt, m.work, tout);
         trace_mark(a, 9);
+        consumer_sync();   // the ordered candidates and the epilogue's arrays may be written again
     }
-    consumer_sync();   // the list, the ordered candidates and the pools may be written again
 }
 
 template <bool SOFTCAP>
@@ -503,6 +603,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
             mbar_init(&ctl->item_ready[b], 1u);
             mbar_init(&ctl->item_free[b], (unsigned)kWarps);
         }
+        for (int w = 0; w < kWarps; ++w) ctl->wbound[w] = 0ull;
         ctl->abort = 0;
         ctl->n_el = 0;
         fence_mbar_init();
@@ -512,12 +613,12 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
         }
     }
     __syncthreads();   // the only barrier all warps take part in
-    if (warp == kSetupWarp) {
-        setup_loop(a, m);
+    if (warp == kCopyWarp) {
+        copy_loop(a, m);
         return;
     }
-    if (warp == kCopyWarp) {
-        if (a.bulk_ok) copy_loop(a, m);
+    if (warp > kCopyWarp) {
+        setup_loop(a, m, warp - kSetupWarp0);
         return;
     }
     if (a.write_back) pdl_wait_prior();   // this launch stores into the logits while it streams
@@ -529,10 +630,15 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
     float* const st_warp = m.stage + warp * kWTile;
     int it = 0;        // tiles of this CTA looked at so far (the position in the ring)
     int n_items = 0;
+    Pending pend{-1, 0u};
+    long long t_wait = 0, t_ready = 0;
     for (int seq = 0;; ++seq) {
         const int b = seq & 1;
+        const unsigned tag = (unsigned)seq + 1u;
         const ItemCtx* ic = &ctl->item[b];
+        const long long tr0 = a.trace ? clock64() : 0;
         if (!mbar_wait_bounded(&ctl->item_ready[b], (unsigned)((seq >> 1) & 1), ctl) && lane == 0) report_timeout(ctl, a.status);
+        if (a.trace) t_ready += clock64() - tr0;
         if (tid == 0 && !ctl->abort && !ic->done) ctl->cur = ic->d;   // the end-of-item work outlives the hand-over slot
         consumer_sync();   // every warp takes the same way out
         if (*reinterpret_cast<volatile int*>(&ctl->abort) || ic->done) break;
@@ -544,7 +650,8 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
         const bool has_pen = (ic->d.flags & kRowPenalty) != 0;
         const unsigned* bitmap = m.bitmap + (size_t)b * kItemBitmapWords;
         const int item_lo = tile0 * kTile;
-        float thr = ic->thr0, run_max = ninf;
+        const float thr0 = ic->thr0;
+        float thr = thr0, run_max = ninf;
         u64 wcomp = 0ull;   // composite bound of this warp after it had to keep its k best (0: none)
         int pn = 0;         // entries in this warp's pool (the same value in every lane)
         int col0 = item_lo + warp * kWTile;   // first column of this warp's part of the tile
@@ -555,7 +662,9 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
             float* st = st_warp + slot * kTile;              // this warp's part of the CTA tile
             const int len = min(kWTile, V - col0);            // may be <= 0 in a row's last tile
             if (a.bulk_ok) {
+                const long long tw0 = a.trace ? clock64() : 0;
                 if (!mbar_wait_bounded(&ctl->full[slot], par, ctl) && lane == 0) report_timeout(ctl, a.status);   // carry on with what is there
+                if (a.trace) t_wait += clock64() - tw0;
             } else if (len > 0) {   // rows not on 16-byte boundaries: the warp loads its part of the tile itself
                 const float* src = row_ptr + col0;
                 for (int e = lane; e < len; e += 32) st[e] = src[e];
@@ -565,7 +674,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
             if (SOFTCAP) {
                 if (len > 0) softcap_tile(st, len, a.softcap, wb_row ? wb_row + col0 : nullptr);
             }
-            if (has_pen && len > 0) patch_tile(st, len, col0, item_lo, pen, bitmap, wb_row);
+            if (has_pen && len > 0 && !(a.debug & 4)) patch_tile(st, len, col0, item_lo, pen, bitmap, wb_row);
             if (len < kWTile) {   // what lies past the end of a ragged row is made NaN: never a maximum, never reaches a bound
                 for (int e = max(len, 0) + lane; e < kWTile; e += 32) st[e] = __int_as_float(0x7fc00000);
                 __syncwarp();
@@ -582,18 +691,17 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
             __syncwarp();
             if (lane == 0 && a.bulk_ok) mbar_arrive(&ctl->empty[slot]);   // the slot goes back to the copy warp
 
-            // ---- the admission bound: set at the item's first tile (all warps must have posted: one barrier per
-            // item), then refreshed without a barrier at tiles 1, 2, 4 of the item
+            // ---- the admission bound: posted at the item's first tile - with a barrier when the row has left no bound
+            // yet, so that the first tile is not admitted wholesale - and refreshed without one at tiles 1, 2, 4
             if ((s & (s - 1)) == 0) {   // s = 0, 1, 2, 4, 8, ...
-                const float wb = warp_bound(run_max, k);
-                if (lane == 0) *reinterpret_cast<volatile float*>(&ctl->wbound[warp]) = wb;
-                if (s == 0) consumer_sync();
+                post_warp_bound(ctl, tag, warp_bound(run_max, k));
+                if (s == 0 && thr0 == ninf) consumer_sync();
                 else __syncwarp();
-                thr = fmaxf(thr, min_warp_bounds(ctl));
+                thr = fmaxf(thr, min_warp_bounds(ctl, tag));
             }
 
             // ---- admit the logits that reach the bound (padding past the end of a row never does)
-            if (__any_sync(0xffffffffu, mt >= thr)) {
+            if (!(a.debug & 1) && __any_sync(0xffffffffu, mt >= thr)) {
                 const int id_lane = col0 + 4 * lane + a.vocab_offset;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -601,7 +709,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
                     const float mq = q == 0 ? m0 : q == 1 ? m1 : q == 2 ? m2 : m3;
                     if (!__any_sync(0xffffffffu, mq >= thr)) continue;
                     if (pn > kPoolCap - 128) {
-                        const PoolState ps = compact_pool(pool, pn, thr, wcomp, k, ctl);
+                        const PoolState ps = compact_pool(pool, pn, thr, wcomp, k, ctl, tag);
                         pn = ps.n;
                         thr = ps.thr;
                         wcomp = ps.wcomp;
@@ -619,12 +727,24 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->item_free[b]);   // descriptor slot and bitmap go back to the set-up warp
+        if (lane == 0) mbar_arrive(&ctl->item_free[b]);   // descriptor slot and bitmap go back
         ++n_items;
         trace_mark(a, 4);
-        item_end(a, m, pool, pn, thr, wcomp, run_max, row, chunk);
+        const long long te0 = a.trace ? clock64() : 0;
+        if (a.debug & 2) {
+            consumer_sync();
+            continue;
+        }
+        item_end(a, m, pool, pn, thr, wcomp, run_max, row, chunk, tag, pend);
+        if (a.trace) trace_add(a, 13, (u64)(clock64() - te0));
     }
-    trace_set(a, 3, (u64)n_items);
+    // the last ticket this CTA drew may have been its row's last
+    resolve_pending(a, m, pend);
+    if (a.trace && tid == 0) {
+        a.trace[(size_t)blockIdx.x * 16 + 3] = (u64)n_items;
+        a.trace[(size_t)blockIdx.x * 16 + 11] = (u64)t_wait;
+        a.trace[(size_t)blockIdx.x * 16 + 12] = (u64)t_ready;
+    }
     trace_mark(a, 10);
 }
 

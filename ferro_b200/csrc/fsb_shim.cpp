@@ -308,6 +308,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.softcap = h->softcap;
         a.overlap = h->launch_overlap;
         a.scan_sums = h->scan_sums;
+        if (const char* dbg = std::getenv("FSB_DEBUG")) a.debug = std::atoi(dbg);
         const int e = fsb::launch_stream_kernel(a, b->plan.grid, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         h->counters.kernel_launches++;

@@ -1,26 +1,36 @@
-"""Request fields -> sampling parameters, with the reference server's defaults, aliases and range errors.
+"""Request fields and command-line flags -> sampling parameters: a binding of the C ABI's front end.
 
-Mirrors what paragontasx/ferro's chat-completion handler does before it constructs a sampler
-(src/server.cpp:1060-1072) and the server options that feed it (src/server.h:35-37, flags in src/main.cpp:249-251):
+``fsb_params_from_request`` and ``fsb_params_apply_cli_flag`` (ferro_b200/csrc/fsb_request.cpp) restate what
+paragontasx/ferro's chat-completion handler does before it constructs a sampler (src/server.cpp:1060-1072), the
+server options that feed it (src/server.h:35-37) and the flags of the binary (src/main.cpp:250-262); a C++ server
+calls them directly.  This module only marshals a decoded JSON body into ``fsb_request_fields``:
 
 * a field is used only if it is a JSON number (an integer or a float; strings, booleans and null fall back to the
-  default, as the reference's ``jnum`` does);
-* ``repetition_penalty`` falls back to ``repeat_penalty``, then to the server default (``--repeat-penalty`` if
-  positive), then to the struct default 1.05; ``repeat_last_n`` falls back to ``penalty_last_n``, then to the server
-  default (``--repeat-last-n``, -1);
-* ``penalize_prompt`` (a JSON boolean; server default ``--penalty-scope all``) = false sets ``penalty_from`` to the
-  prompt length, so the penalty window never reaches into the prompt;
-* ``seed`` defaults to 0 (= nondeterministic);
-* temperature < 0, top_p outside (0, 1], top_k < 0, repetition_penalty <= 0 or repeat_last_n < -1 is a bad request.
+  default, as the reference's ``jnum`` does); ``penalize_prompt`` only if it is a JSON boolean;
+* everything else - aliases, server defaults, ``penalty_from``, the range errors - happens in the C function.
 
 ``min_p`` is not range-checked by the reference; the C ABI additionally wants 0 <= min_p <= 1 (fsb_params_validate)
 and reports that when the stream is opened.
 """
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 
 import numpy as np
+
+_FIELDS = ["temperature", "top_p", "top_k", "min_p", "repetition_penalty", "repeat_penalty", "repeat_last_n", "penalty_last_n"]
+_BITS = {name: 1 << i for i, name in enumerate(_FIELDS)}
+_BITS["penalize_prompt"] = 1 << 8
+_BITS["seed"] = 1 << 9
+
+
+class _RequestFields(C.Structure):      # fsb_request_fields
+    _fields_ = [("present", C.c_uint32), ("penalize_prompt", C.c_int32)] + [(n, C.c_double) for n in _FIELDS + ["seed"]]
+
+
+class _ServerDefaults(C.Structure):     # fsb_server_defaults
+    _fields_ = [("repeat_penalty", C.c_float), ("repeat_last_n", C.c_int32), ("penalize_prompt", C.c_int32)]
 
 
 class BadRequest(ValueError):
@@ -34,35 +44,49 @@ class ServerDefaults:
     repeat_last_n: int = -1
     penalize_prompt: bool = True
 
-
-def _num(body: dict, key: str, default):
-    v = body.get(key)
-    if isinstance(v, bool) or not isinstance(v, (int, float)):
-        return default
-    return v
+    def _c(self) -> _ServerDefaults:
+        return _ServerDefaults(self.repeat_penalty, self.repeat_last_n, 1 if self.penalize_prompt else 0)
 
 
 def params_from_request(body: dict, prompt_tokens: int = 0, defaults: ServerDefaults | None = None) -> np.ndarray:
     """One-row parameter record (``ferro_b200.PARAMS_DTYPE`` layout = ``ferro_sampler_params``) for a request body."""
-    from . import make_params
-    d = defaults or ServerDefaults()
-    p = make_params(1)                                    # the struct defaults (src/sampler.h:13-20)
-    f32 = np.float32
-    temperature = f32(_num(body, "temperature", float(p["temperature"][0])))
-    top_p = f32(_num(body, "top_p", float(p["top_p"][0])))
-    top_k = int(_num(body, "top_k", int(p["top_k"][0])))
-    min_p = f32(_num(body, "min_p", float(p["min_p"][0])))
-    server_pen = d.repeat_penalty if d.repeat_penalty > 0 else float(p["repetition_penalty"][0])
-    penalty = f32(_num(body, "repetition_penalty", _num(body, "repeat_penalty", server_pen)))
-    last_n = int(_num(body, "repeat_last_n", _num(body, "penalty_last_n", d.repeat_last_n)))
-    pen_prompt = d.penalize_prompt
+    from . import PARAMS_DTYPE, load_library
+    f = _RequestFields()
+    for name in _FIELDS + ["seed"]:
+        v = body.get(name)
+        if isinstance(v, bool) or not isinstance(v, (int, float)):
+            continue
+        f.present |= _BITS[name]
+        setattr(f, name, float(v))
     if isinstance(body.get("penalize_prompt"), bool):
-        pen_prompt = body["penalize_prompt"]
-    seed = _num(body, "seed", 0)
-    if temperature < 0 or top_p <= 0 or top_p > 1 or top_k < 0 or penalty <= 0 or last_n < -1:
+        f.present |= _BITS["penalize_prompt"]
+        f.penalize_prompt = 1 if body["penalize_prompt"] else 0
+    d = (defaults or ServerDefaults())._c()
+    p = np.zeros(1, dtype=PARAMS_DTYPE)
+    rc = load_library().fsb_params_from_request(C.byref(f), C.byref(d), int(prompt_tokens), p.ctypes.data)
+    if rc == -2:
         raise BadRequest("sampling parameter out of range")
-    p["temperature"], p["top_p"], p["top_k"], p["min_p"] = temperature, top_p, top_k, min_p
-    p["repetition_penalty"], p["repeat_last_n"] = penalty, last_n
-    p["penalty_from"] = 0 if pen_prompt else int(prompt_tokens)
-    p["seed"] = np.uint64(int(seed) & 0xFFFFFFFFFFFFFFFF)
+    if rc != 0:
+        raise ValueError(f"fsb_params_from_request failed with {rc}")
     return p
+
+
+def apply_cli_flags(argv, params: np.ndarray | None = None, defaults: ServerDefaults | None = None):
+    """Walks `argv` as the reference's binary does (src/main.cpp:250-262) and applies the sampling flags.
+    Returns (params record, ServerDefaults, the arguments that are not sampling flags)."""
+    from . import make_params, load_library
+    lib = load_library()
+    p = make_params(1) if params is None else params.copy()
+    d = (defaults or ServerDefaults())._c()
+    rest, i = [], 0
+    while i < len(argv):
+        value = argv[i + 1] if i + 1 < len(argv) else None
+        rc = lib.fsb_params_apply_cli_flag(p.ctypes.data, C.byref(d), argv[i].encode(), value.encode() if value is not None else None)
+        if rc == 1:
+            i += 2
+        elif rc == 0:
+            rest.append(argv[i])
+            i += 1
+        else:
+            raise BadRequest(f"bad value for {argv[i]}")
+    return p, ServerDefaults(float(d.repeat_penalty), int(d.repeat_last_n), bool(d.penalize_prompt)), rest

@@ -123,6 +123,43 @@ FSB_API int fsb_set_vocab_shard(fsb_handle* h, int32_t offset, int32_t global_vo
 FSB_API void fsb_params_default(ferro_sampler_params* p);
 FSB_API int fsb_params_validate(const ferro_sampler_params* p);
 
+/* ---- request front end --------------------------------------------------------------------------------- */
+
+/* The request fields the reference's chat-completion handler reads before it constructs a sampler
+ * (src/server.cpp:1060-1072).  The reference takes a field only when it is a JSON number (its jnum falls back to the
+ * default for strings, booleans and null; penalize_prompt only when it is a JSON boolean): the caller sets the
+ * field's bit in `present` in exactly those cases.  Numbers are doubles, as jnum returns them. */
+enum {
+    FSB_REQ_TEMPERATURE = 1u << 0, FSB_REQ_TOP_P = 1u << 1, FSB_REQ_TOP_K = 1u << 2, FSB_REQ_MIN_P = 1u << 3,
+    FSB_REQ_REPETITION_PENALTY = 1u << 4, FSB_REQ_REPEAT_PENALTY = 1u << 5, /* alias, used when the first is absent */
+    FSB_REQ_REPEAT_LAST_N = 1u << 6, FSB_REQ_PENALTY_LAST_N = 1u << 7,       /* alias, used when the first is absent */
+    FSB_REQ_PENALIZE_PROMPT = 1u << 8, FSB_REQ_SEED = 1u << 9
+};
+typedef struct fsb_request_fields {
+    uint32_t present;
+    int32_t penalize_prompt;
+    double temperature, top_p, top_k, min_p, repetition_penalty, repeat_penalty, repeat_last_n, penalty_last_n, seed;
+} fsb_request_fields;
+/* The server options that act as per-request defaults (src/server.h:35-37; flags --repeat-penalty, --repeat-last-n,
+ * --penalty-scope, src/main.cpp:250-252). */
+typedef struct fsb_server_defaults {
+    float repeat_penalty;    /* <= 0: the sampler's own default 1.05 */
+    int32_t repeat_last_n;   /* -1 whole context, 0 off, N last tokens */
+    int32_t penalize_prompt; /* 1 = "--penalty-scope all" (default), 0 = "generated" */
+} fsb_server_defaults;
+FSB_API void fsb_server_defaults_init(fsb_server_defaults* d);
+/* src/server.cpp:1060-1072: struct defaults, overridden by the request; repetition_penalty falls back to repeat_penalty,
+ * then to the server default, then to 1.05; repeat_last_n to penalty_last_n, then to the server default; with
+ * penalize_prompt false penalty_from = prompt_tokens; seed defaults to 0.  FSB_ERR_RANGE where the reference answers
+ * 400 "sampling parameter out of range" (temperature < 0, top_p outside (0, 1], top_k < 0, repetition_penalty <= 0,
+ * repeat_last_n < -1).  `d` may be NULL (the defaults of fsb_server_defaults_init). */
+FSB_API int fsb_params_from_request(const fsb_request_fields* f, const fsb_server_defaults* d, int32_t prompt_tokens, ferro_sampler_params* out);
+/* One command-line flag of the reference's binary (src/main.cpp:250-262): --temp --top-k --top-p --min-p --rep-penalty
+ * --seed set the generate command's parameters `p`; --repeat-penalty --repeat-last-n --penalty-scope set the server
+ * defaults `d` (--repeat-last-n both).  Returns 1 if the flag was one of these, 0 if it is not a sampling flag,
+ * FSB_ERR_RANGE for a bad --penalty-scope value, FSB_ERR_INVALID for a missing value. */
+FSB_API int fsb_params_apply_cli_flag(ferro_sampler_params* p, fsb_server_defaults* d, const char* flag, const char* value);
+
 /* ---- streams: one per request, like `new Sampler(j.sp)` at src/server.cpp:545 ---------------------------- */
 
 /* Opens a stream: copies the parameters and seeds a std::mt19937_64 exactly as src/sampler.h:25 does. */

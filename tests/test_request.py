@@ -48,3 +48,40 @@ def test_result_passes_the_c_abi_validation():
     lib = fb.load_library()
     p = params_from_request({"temperature": 0.7, "top_k": 40, "top_p": 0.95, "min_p": 0.05, "repeat_penalty": 1.1, "seed": 7}, prompt_tokens=5)
     assert lib.fsb_params_validate(p.ctypes.data) == 0
+
+
+def test_command_line_flags_of_the_reference_binary():
+    # src/main.cpp:250-262: --temp --top-k --top-p --min-p --rep-penalty --seed go to the generate parameters,
+    # --repeat-penalty --repeat-last-n --penalty-scope to the server defaults (--repeat-last-n to both)
+    from ferro_b200.request import apply_cli_flags
+    argv = ["--temp", "0.7", "--top-k", "40", "--port", "8080", "--top-p", "0.9", "--min-p", "0.05", "--rep-penalty", "1.2", "--seed", "99",
+            "--repeat-penalty", "1.15", "--repeat-last-n", "256", "--penalty-scope", "generated", "--quiet"]
+    p, d, rest = apply_cli_flags(argv)
+    assert p["temperature"][0] == np.float32(0.7) and p["top_k"][0] == 40 and p["top_p"][0] == np.float32(0.9)
+    assert p["min_p"][0] == np.float32(0.05) and p["repetition_penalty"][0] == np.float32(1.2) and p["seed"][0] == 99
+    assert p["repeat_last_n"][0] == 256
+    assert d == ServerDefaults(repeat_penalty=np.float32(1.15), repeat_last_n=256, penalize_prompt=False)
+    assert rest == ["--port", "8080", "--quiet"]
+    # the server defaults then shape a request that names none of them
+    q = params_from_request({}, prompt_tokens=11, defaults=d)
+    assert q["repetition_penalty"][0] == np.float32(1.15) and q["repeat_last_n"][0] == 256 and q["penalty_from"][0] == 11
+    with pytest.raises(BadRequest):
+        apply_cli_flags(["--penalty-scope", "some"])
+    with pytest.raises(BadRequest):
+        apply_cli_flags(["--temp"])
+
+
+def test_front_end_is_callable_from_c_without_an_engine():
+    import ctypes as C
+    lib = fb.load_library()
+    from ferro_b200.request import _RequestFields, _ServerDefaults
+    d = _ServerDefaults()
+    lib.fsb_server_defaults_init(C.byref(d))
+    assert (d.repeat_penalty, d.repeat_last_n, d.penalize_prompt) == (0.0, -1, 1)
+    f = _RequestFields()
+    f.present = (1 << 5) | (1 << 9)          # repeat_penalty (the alias) and seed
+    f.repeat_penalty, f.seed = 1.3, 4242.0
+    p = fb.make_params(1)
+    assert lib.fsb_params_from_request(C.byref(f), None, 0, p.ctypes.data) == 0
+    assert p["repetition_penalty"][0] == np.float32(1.3) and p["seed"][0] == 4242 and p["top_k"][0] == 50
+    assert lib.fsb_params_from_request(None, None, 0, p.ctypes.data) == -1
