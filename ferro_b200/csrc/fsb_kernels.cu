@@ -441,7 +441,7 @@ struct Pending {
 // The ticket of the row in `pend` has had an item's time to arrive: if it was the row's last, all chunks of the row
 // have published, and this CTA merges their ordered lists and runs the epilogue.  All consumer threads call.  Uses
 // the pools' memory (idle between items), the list, the ordered-candidate array and the epilogue's arrays.
-__device__ __forceinline__ void resolve_pending(const StreamArgs& a, const Smem& m, Pending& pend) {
+__device__ __forceinline__ void resolve_pending(const StreamArgs& a, const Smem& m, Pending& pend, const RowDesc* desc) {
     SharedCtl* ctl = m.ctl;
     const int tid = threadIdx.x, lane = tid & 31;
     const int row = pend.row;
@@ -451,7 +451,7 @@ __device__ __forceinline__ void resolve_pending(const StreamArgs& a, const Smem&
     consumer_sync();
     if (!ctl->last) return;
     trace_mark(a, 7);
-    const RowDesc d = ctl->prev;
+    const RowDesc d = *desc;
     const int k = d.k, nl = a.n_chunks;
     const u64* src = reinterpret_cast<const u64*>(a.scratch) + (size_t)row * (size_t)a.scratch_stride;
     if (tid == 0) {
@@ -544,17 +544,6 @@ __device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64
     int n_el = ctl->n_el;
     if (n_el > kListCap) n_el = overflow_select(pool, pn, k, m.list, ctl);
     trace_mark(a, 5);
-    // the list is complete and the pools are idle: the row whose ticket has been on its way since the item before
-    if (pend.row >= 0) {
-        // (the merge uses the list: this item's candidates wait in the pools' upper half meanwhile - n_el <= kListCap entries)
-        u64* park = m.pools + (size_t)kRowScratch;
-        static_assert((size_t)kRowScratch + kListCap <= (size_t)kWarps * kPoolCap, "room to park an item's candidates during a merge");
-        for (int i = tid; i < n_el; i += kThreads) park[i] = m.list[i];
-        consumer_sync();
-        resolve_pending(a, m, pend);
-        for (int i = tid; i < n_el; i += kThreads) m.list[i] = park[i];
-        consumer_sync();
-    }
     if (tid == 0) ctl->n_el = 0;   // for the next item (barriers follow)
     const int kk = topk_sorted(m.list, n_el, k, m.sorted, ctl);
     trace_mark(a, 6);
@@ -568,11 +557,15 @@ __device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64
         if (tid == 0) {
             dst[a.scratch_stride - 1 - chunk] = (u64)kk;
             if (kk == k) atomicMax(a.row_bound + row, (unsigned)(m.sorted[k - 1] >> 32));
-            ctl->prev = ctl->cur;
         }
         consumer_sync();   // orders the CTA's stores before the ticket, whose release publishes them to the device
+        // the ticket drawn at the end of the item before has had this item's time to arrive; pools, list and ordered
+        // candidates are idle now
+        Pending prev = pend;
         if (tid == 0) pend.ticket = ticket_add_acq_rel(a.ticket + row, 1u);   // not looked at before the next item's end
         pend.row = row;
+        resolve_pending(a, m, prev, &ctl->prev);
+        if (tid == 0) ctl->prev = ctl->cur;
     } else {
         const RowDesc& d = ctl->cur;
         const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
@@ -631,7 +624,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
     int it = 0;        // tiles of this CTA looked at so far (the position in the ring)
     int n_items = 0;
     Pending pend{-1, 0u};
-    long long t_wait = 0, t_ready = 0;
+    long long t_ready = 0;
     for (int seq = 0;; ++seq) {
         const int b = seq & 1;
         const unsigned tag = (unsigned)seq + 1u;
@@ -662,9 +655,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
             float* st = st_warp + slot * kTile;              // this warp's part of the CTA tile
             const int len = min(kWTile, V - col0);            // may be <= 0 in a row's last tile
             if (a.bulk_ok) {
-                const long long tw0 = a.trace ? clock64() : 0;
                 if (!mbar_wait_bounded(&ctl->full[slot], par, ctl) && lane == 0) report_timeout(ctl, a.status);   // carry on with what is there
-                if (a.trace) t_wait += clock64() - tw0;
             } else if (len > 0) {   // rows not on 16-byte boundaries: the warp loads its part of the tile itself
                 const float* src = row_ptr + col0;
                 for (int e = lane; e < len; e += 32) st[e] = src[e];
@@ -699,29 +690,48 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
                 else __syncwarp();
                 thr = fmaxf(thr, min_warp_bounds(ctl, tag));
             }
-
-            // ---- admit the logits that reach the bound (padding past the end of a row never does)
+            // ---- admit the logits that reach the bound (padding past the end of a row never does).  As a rule one or two
+            // cells of a warp tile hold such a logit: their lanes are visited one after the other, lanes 0..3 each taking
+            // one logit of the cell.  When many cells qualify (the first tiles of a row, masked or constant stretches) all
+            // lanes work on their own cells at once.
             if (!(a.debug & 1) && __any_sync(0xffffffffu, mt >= thr)) {
                 const int id_lane = col0 + 4 * lane + a.vocab_offset;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const float4 x = q == 0 ? x0 : q == 1 ? x1 : q == 2 ? x2 : x3;
                     const float mq = q == 0 ? m0 : q == 1 ? m1 : q == 2 ? m2 : m3;
-                    if (!__any_sync(0xffffffffu, mq >= thr)) continue;
+                    unsigned hits = __ballot_sync(0xffffffffu, mq >= thr);
+                    if (hits == 0u) continue;
                     if (pn > kPoolCap - 128) {
                         const PoolState ps = compact_pool(pool, pn, thr, wcomp, k, ctl, tag);
                         pn = ps.n;
                         thr = ps.thr;
                         wcomp = ps.wcomp;
                     }
-                    const float xs[4] = {x.x, x.y, x.z, x.w};
+                    if (__popc(hits) <= 4) {
+                        do {
+                            const int src = __ffs(hits) - 1;
+                            hits &= hits - 1u;
+                            // the cell of lane `src`: lane e < 4 takes its logit e
+                            const float v0 = __shfl_sync(0xffffffffu, x.x, src), v1 = __shfl_sync(0xffffffffu, x.y, src);
+                            const float v2 = __shfl_sync(0xffffffffu, x.z, src), v3 = __shfl_sync(0xffffffffu, x.w, src);
+                            const float v = lane == 0 ? v0 : lane == 1 ? v1 : lane == 2 ? v2 : v3;
+                            const u64 c = make_comp(v, col0 + a.vocab_offset + 4 * src + 128 * q + lane);
+                            const bool ok = lane < 4 && v >= thr && c >= wcomp;
+                            const unsigned be = __ballot_sync(0xffffffffu, ok);
+                            if (ok) pool[pn + __popc(be & lt)] = c;
+                            pn += __popc(be);
+                        } while (hits);
+                    } else {
+                        const float xs[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const u64 c = make_comp(xs[e], id_lane + 128 * q + e);
-                        const bool ok = xs[e] >= thr && c >= wcomp;
-                        const unsigned be = __ballot_sync(0xffffffffu, ok);
-                        if (ok) pool[pn + __popc(be & lt)] = c;
-                        pn += __popc(be);
+                        for (int e = 0; e < 4; ++e) {
+                            const u64 c = make_comp(xs[e], id_lane + 128 * q + e);
+                            const bool ok = xs[e] >= thr && c >= wcomp;
+                            const unsigned be = __ballot_sync(0xffffffffu, ok);
+                            if (ok) pool[pn + __popc(be & lt)] = c;
+                            pn += __popc(be);
+                        }
                     }
                 }
             }
@@ -739,10 +749,9 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
         if (a.trace) trace_add(a, 13, (u64)(clock64() - te0));
     }
     // the last ticket this CTA drew may have been its row's last
-    resolve_pending(a, m, pend);
+    resolve_pending(a, m, pend, &ctl->prev);
     if (a.trace && tid == 0) {
         a.trace[(size_t)blockIdx.x * 16 + 3] = (u64)n_items;
-        a.trace[(size_t)blockIdx.x * 16 + 11] = (u64)t_wait;
         a.trace[(size_t)blockIdx.x * 16 + 12] = (u64)t_ready;
     }
     trace_mark(a, 10);
@@ -906,8 +915,9 @@ int plan_chunks(int n_rows, int n_vocab, int kmax, int slots, int64_t stride, ui
     const int max_chunks = (int)(by_scratch < kMaxChunks ? by_scratch : kMaxChunks);
     if (max_chunks < 1) return 0;
     const double per_cta = (double)n_rows * T / (slots > 1 ? slots : 1);   // tiles a CTA streams on average
-    // About three items per CTA keep the dynamic hand-out balanced; an item never spans more than kItemTilesMax tiles.
-    int q = (int)(per_cta / 3.0 + 0.5);
+    // Two to three items per CTA keep the dynamic hand-out balanced at little end-of-item work; an item never spans
+    // more than kItemTilesMax tiles.
+    int q = (int)(per_cta / 2.5 + 0.5);
     q = q < 1 ? 1 : (q > kItemTilesMax ? kItemTilesMax : q);
     while ((T + q - 1) / q > max_chunks && q < kItemTilesMax) ++q;
     if ((T + q - 1) / q > max_chunks) return 0;
