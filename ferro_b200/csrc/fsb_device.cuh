@@ -113,9 +113,9 @@ constexpr int kNumWarps = kThreads / 32;
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
 // One work item of the streaming kernel as its set-up warp hands it to the copy warp and the consumers.
-struct ItemCtx {
+struct alignas(16) ItemCtx {
+    alignas(16) RowDesc d;  // the row's descriptor (written with 16-byte stores)
     const float* row_ptr;   // the row's logits
-    RowDesc d;              // the row's descriptor
     int done;               // 1: there is no more work (the other fields are not set)
     int row;                // index of the row's descriptor
     int chunk;              // chunk of the row
@@ -123,7 +123,7 @@ struct ItemCtx {
     float thr0;             // a value that k logits of the row are already known to reach (-inf: none)
 };
 
-struct SharedCtl {
+struct alignas(16) SharedCtl {
     u64 full[kStages];                // "tile landed": completed by the copy (or by the copy warp for tiny tails)
     u64 empty[kStages];               // "tile consumed": every consumer warp hands the ring slot back
     u64 item_posted[2];               // "the item's place in the matrix is known": the copies may start
@@ -135,13 +135,14 @@ struct SharedCtl {
     int wcount[kMaxChunks];           // lengths of a row's ordered candidate lists while they are merged
     int sum[3];                       // rotating counters of the selection steps
     int out_cnt;
-    int n_el;                         // candidates of the current item gathered from the warps' pools
+    int n_el;                         // candidates of the current item written so far
     int last;
+    int bsel, nsel;                   // histogram selection: the bucket the k-th candidate lies in, candidates from there up
     int imax, imin1, imin2;
     int abort;                        // a wait ran out of time: every later wait is cut short, the kernel winds down
     RowDesc cur;                      // descriptor of the item whose end-of-item work is running
     RowDesc prev;                     // descriptor of the row whose ticket is still on its way (see the streaming kernel)
-    ItemCtx item[2];
+    alignas(16) ItemCtx item[2];
 };
 
 // ---------------------------------------------------------------------------------------------- top-k selection

@@ -10,12 +10,15 @@ constexpr int kThreads = 512;                 // consumer threads per CTA (16 wa
 constexpr int kTile = 8192;                   // fp32 logits per CTA tile (32 KiB, one bulk copy; 512 logits per warp)
 constexpr int kStages = 4;                    // tiles in flight per CTA
 constexpr int kMaxK = 256;                    // largest k of the candidate path (== FSB_MAX_CANDIDATE_K)
-constexpr int kPoolCap = 384;                 // candidates a consumer warp can hold before it must compact (>= kMaxK + 128)
+constexpr int kLaneQueue = 6;                 // cells (four logits and their first token id) a lane can note before room must be made
+constexpr int kPoolCap = 384;                 // candidates of a warp's overflow pool in global memory (>= kMaxK + 128)
 constexpr int kItemTilesMax = 8;              // tiles of the largest work item (a chunk of one row)
 constexpr int kItemBitmapWords = kItemTilesMax * kTile / 32;   // penalty bitmap of one work item
 constexpr int kMaxChunks = 32;                // chunks a row may be cut into
-constexpr int kListCap = 1024;                // candidates of one work item that are ordered without a selection first
-constexpr int kRowScratch = 4160;             // entries of a row's scratch in an engine: chunks * (k + 1) must fit
+constexpr int kListCap = 512;                 // candidates that are ordered by counting ranks (one thread per entry at most)
+constexpr int kGatherCap = kLaneQueue * kThreads * 2;   // 6144: candidates of all chunks of a row that the merging CTA gathers
+                                                        // (they land in the lanes' queue memory, 16 bytes per queue entry)
+constexpr int kRowScratch = kGatherCap + kMaxChunks;    // entries of a row's scratch in an engine: the chunks' slots, then their counts
 constexpr int kMergeCap = 2400;               // candidates the list-merge kernel (vocabulary sharding) gathers per row
 constexpr int kWindowTableInts = 72;          // int32 words per stream of a resident verification call: 6 + up to 66 drafts
 constexpr int kCounterWords = 4;              // work counters of a launch: [0] items handed out, [1] CTAs that have left
@@ -59,7 +62,9 @@ struct StreamArgs {
     const float* logits;       // base of the [rows][ld] matrix
     const RowDesc* rows;       // n_rows descriptors (only rows of the candidate path)
     const int32_t* hist;       // packed penalty-window ids
-    uint64_t* scratch;         // [n_rows][scratch_stride]: chunk c of a row publishes k ordered candidates at c * k, its count at the end
+    uint64_t* scratch;         // [n_rows][scratch_stride]: chunk c of a row publishes its candidates in slot c (slot_cap entries),
+                               // their number in entry scratch_stride - 1 - c
+    uint64_t* pools;           // [grid][16][pool_cap] overflow pools of the consumer warps (touched on hostile data only)
     uint32_t* ticket;          // [n_rows] chunks of the row that have finished (self-resetting)
     uint32_t* row_bound;       // [n_rows] order-preserving key of a value that k logits of the row are known to reach (self-resetting)
     uint32_t* work;            // [kCounterWords] dynamic work counter and exit counter (self-resetting)
@@ -80,6 +85,8 @@ struct StreamArgs {
     int32_t tiles_per_row;
     int32_t n_chunks;
     int32_t n_items;           // n_rows * n_chunks
+    int32_t slot_cap;          // entries of a chunk's slot in the row's scratch (>= the largest k of the launch)
+    int32_t pool_cap;          // entries of a warp's overflow pool (>= the largest k of the launch + 128)
     int32_t bulk_ok;           // rows start on 16-byte boundaries: tiles can come by bulk async copy
     int32_t write_back;        // store penalised values into the caller's rows
     int32_t vocab_offset;      // token id of column 0
@@ -95,8 +102,9 @@ size_t stream_kernel_smem_bytes();
 int prepare_device_kernels(int* ctas_per_sm);
 int launch_stream_kernel(const StreamArgs& a, int grid, void* stream);
 // How every row of a launch is cut into work items (chunk_len[c] tiles each); returns the number of chunks, 0 if
-// the rows cannot be scheduled within `stride` scratch entries per row.  `slots` = CTAs that run at once.
-int plan_chunks(int n_rows, int n_vocab, int kmax, int slots, int64_t stride, uint8_t* chunk_len);
+// the rows cannot be scheduled: at most max_chunks chunks, each with a slot of at least kmax of the gather_cap
+// entries the merging CTA can take.  `slots` = CTAs that run at once.  *slot_cap = entries per chunk slot.
+int plan_chunks(int n_rows, int n_vocab, int kmax, int slots, int gather_cap, int max_chunks, uint8_t* chunk_len, int* slot_cap);
 int launch_append_tokens(const RowDesc* rows, int n_rows, const int32_t* tokens, int32_t* pool, void* stream);
 int launch_merge_lists(const void* lists, const int32_t* list_n, int n_lists, int list_stride, int n_rows, const RowDesc* rows, int32_t* tokens,
                        int32_t* kept_ids, double* kept_pr, int32_t* kept_n, uint32_t* status, int scan_sums, void* stream);

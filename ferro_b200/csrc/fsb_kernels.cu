@@ -7,6 +7,8 @@
 // How it works is described above the kernel below.
 #include <cuda_runtime.h>
 
+#include <cstddef>
+
 #include "../../include/ferro_sampler_b200.h"
 #include "fsb_device.cuh"
 
@@ -20,16 +22,23 @@ constexpr int kSetupWarp0 = kWarps + 1;         // two set-up warps (one per han
 constexpr int kBlockThreads = kThreads + 96;
 
 constexpr size_t kSmemStage = (size_t)kStages * kTile * sizeof(float);
-constexpr size_t kSmemPools = (size_t)kWarps * kPoolCap * sizeof(u64);          // the warps' candidate pools; a row's lists while they are merged
+constexpr size_t kSmemQv = (size_t)kLaneQueue * kThreads * sizeof(float4);     // the lanes' queues of noted cells: the four logits ...
+constexpr size_t kSmemQc = (size_t)kLaneQueue * kThreads * sizeof(int);        // ... and the token id of the first
 constexpr size_t kSmemBitmap = 2 * (size_t)kItemBitmapWords * sizeof(unsigned);   // penalty bitmaps of two work items
-constexpr size_t kSmemList = (size_t)kListCap * sizeof(u64);                    // an item's candidates
+constexpr size_t kSmemList = (size_t)kListCap * sizeof(u64);                    // candidates about to be ordered
 constexpr size_t kSmemSorted = (size_t)kMaxK * sizeof(u64);                     // ordered candidates
 constexpr size_t kSmemWork = 2 * (size_t)kMaxK * sizeof(double);                // the epilogue's doubles
-constexpr size_t kSmemTotal = kSmemStage + kSmemPools + kSmemBitmap + kSmemList + kSmemSorted + kSmemWork + sizeof(SharedCtl);
+constexpr size_t kSmemHist = 256 * sizeof(unsigned);                            // histogram of the selection
+constexpr size_t kSmemTotal = kSmemStage + kSmemQv + kSmemQc + kSmemBitmap + kSmemList + kSmemSorted + kSmemWork + kSmemHist + sizeof(SharedCtl);
 static_assert(kSmemTotal <= 227 * 1024, "one CTA per SM");
-static_assert(kSmemPools >= (size_t)kRowScratch * sizeof(u64), "a row's published lists fit into the pools' memory");
+static_assert((kSmemStage + kSmemQv + kSmemQc + kSmemBitmap + kSmemList + kSmemSorted + kSmemWork + kSmemHist) % 16 == 0, "the control block starts on a 16-byte boundary");
+static_assert(offsetof(SharedCtl, item) % 16 == 0 && offsetof(ItemCtx, d) % 16 == 0 && sizeof(ItemCtx) % 16 == 0, "descriptors are written with 16-byte stores");
+static_assert(offsetof(SharedCtl, wbound) % 16 == 0, "the warps' bounds are read with 16-byte loads");
+static_assert(kSmemStage % 16 == 0 && (kSmemStage + kSmemQv + kSmemQc) % 16 == 0, "queue entries and bitmaps are written with 16-byte stores");
+static_assert(kSmemQv >= (size_t)kGatherCap * sizeof(u64), "a row's published candidates fit into the queues' memory");
 static_assert(kWTile == 512, "a lane owns four float4 of a warp tile");
-static_assert(kPoolCap >= kMaxK + 128, "a warp keeps its k best and still has room for the candidates of 128 cells");
+static_assert(kLaneQueue > 4, "a lane may note four cells per tile");
+static_assert(kPoolCap >= kMaxK + 128, "a warp keeps its k best and still has room for the candidates of 32 cells");
 static_assert(kPoolCap % 32 == 0 && kPoolCap / 32 <= 12, "a warp holds its pool in twelve registers per lane when it selects");
 
 constexpr long long kWaitCycles = 2000000000ll;   // about 1 s: a wait that has not ended by then is reported, not continued
@@ -39,7 +48,12 @@ constexpr long long kWaitCycles = 2000000000ll;   // about 1 s: a wait that has 
 // to kItemTilesMax tiles.  A work item is one chunk of one row.  The grid is one CTA per SM (or fewer, for small
 // batches); CTA b starts with item b and draws further items from a counter in global memory, so that the CTAs
 // finish together however unevenly the SMs are served.  Items are numbered chunk by chunk (the first chunk of
-// every row, then the second, ...): the small chunks at the end of the schedule even out the finish.
+// every row, then the second, ...).
+//
+// The SM's instruction issue rate, not its memory bandwidth, is what the consumers have to respect: a tile is
+// 32 KiB every ~0.75 us per SM at full HBM rate, which leaves sixteen warps a few hundred instructions each.  So the
+// per-tile work is a handful of instructions per cell, and whatever is rare or happens once per item is kept out
+// of the tile loop.
 //
 // A CTA has three kinds of warps, which meet only at mbarriers:
 //   * the copy warp draws the items and brings their tiles into a ring of kStages shared-memory slots, one 1-D
@@ -48,27 +62,31 @@ constexpr long long kWaitCycles = 2000000000ll;   // about 1 s: a wait that has 
 //   * two set-up warps, one per hand-over slot, read the item's row descriptor and build the bitmap of the item's
 //     penalised columns from the row's window ids - while the consumers work on the items before;
 //   * sixteen consumer warps each own one sixteenth (512 logits) of every tile.  A lane owns four cells (float4)
-//     per tile.  It takes each cell's maximum; a warp whose lanes all stay below the admission bound is done with
-//     the tile.  Otherwise the logits that reach the bound go, as composites, into the warp's pool in shared memory
-//     (ballot-compacted: no atomics).  The bound is the smallest, over the warps, of the r-th largest of a warp's 32
-//     lane maxima (r = ceil(k / 16)): at least k logits of the item reach it.  It is set at the item's first tile
-//     and refreshed at tiles 1, 2, 4 without a barrier; a later chunk of a row starts from the bound the row's
-//     earlier chunks have left in global memory.  A warp whose pool fills up drops what the bound has overtaken
-//     and, if that is not enough (rows of equal values), keeps exactly its k best - ties by token id.
-// At the end of an item the warps' surviving candidates are gathered, ordered, and the k best published in the
-// item's part of the row's scratch, and a ticket is drawn for the row.  The ticket's value is looked at one item
-// later (its round trip to L2 overlaps the next item): the CTA that drew the row's last ticket merges the row's
-// lists and runs the epilogue.  No CTA ever waits for another CTA; waits for this CTA's own copies and hand-overs
-// are bounded.
+//     per tile.  It takes each cell's maximum and, where that reaches the admission bound, notes the cell - its four
+//     logits and its first token id - in a queue only this lane writes: a compare, two predicated stores and a
+//     predicated increment, no branch.  The bound is the smallest, over the warps, of the r-th largest of a warp's
+//     32 lane maxima (r = ceil(k / 16)): at least k logits of the item reach it.  It is set at the item's first
+//     tile and refreshed at tiles 1, 2, 4 without a barrier; a later chunk of a row starts from the bound the row's
+//     earlier chunks have left in global memory.  A warp with a nearly full queue drops the cells the bound has
+//     overtaken, evens the rest out over its lanes, and only if that is not enough (rows of equal values, masked
+//     stretches) moves their logits to an overflow pool in global memory, of which it keeps exactly its k best -
+//     ties by token id.
+// At the end of an item the logits of the noted cells that reach the final bound are written, unordered, into
+// the item's slot of the row's scratch, and a ticket is drawn for the row.  The ticket's value is looked at one
+// item later (its round trip to L2 overlaps the next item): the CTA that drew the row's last ticket gathers the
+// row's candidates, selects the k best (a histogram over the candidates' keys, then ranks by counting), and runs
+// the epilogue.  No CTA ever waits for another CTA; waits for this CTA's own copies and hand-overs are bounded.
 
 // The shared memory of a CTA.
 struct Smem {
     float* stage;       // [kStages][kTile] ring of CTA tiles
-    u64* pools;         // [kWarps][kPoolCap] candidates the warps have admitted; a row's published lists while they are merged
+    float4* qv;         // [kLaneQueue][kThreads] noted cells; the gathered candidates of a row while it is finished
+    int* qc;            // [kLaneQueue][kThreads] token id of a noted cell's first logit
     unsigned* bitmap;   // [2][kItemBitmapWords]
-    u64* list;          // [kListCap] the item's candidates
+    u64* list;          // [kListCap] candidates about to be ordered
     u64* sorted;        // [kMaxK] the k best, in order
     double* work;       // [2 * kMaxK] the epilogue's arrays
+    unsigned* hist;     // [256]
     SharedCtl* ctl;
 };
 __device__ __forceinline__ Smem smem_view() {
@@ -77,8 +95,10 @@ __device__ __forceinline__ Smem smem_view() {
     unsigned char* p = smem_raw;
     m.stage = reinterpret_cast<float*>(p);
     p += kSmemStage;
-    m.pools = reinterpret_cast<u64*>(p);
-    p += kSmemPools;
+    m.qv = reinterpret_cast<float4*>(p);
+    p += kSmemQv;
+    m.qc = reinterpret_cast<int*>(p);
+    p += kSmemQc;
     m.bitmap = reinterpret_cast<unsigned*>(p);
     p += kSmemBitmap;
     m.list = reinterpret_cast<u64*>(p);
@@ -87,6 +107,8 @@ __device__ __forceinline__ Smem smem_view() {
     p += kSmemSorted;
     m.work = reinterpret_cast<double*>(p);
     p += kSmemWork;
+    m.hist = reinterpret_cast<unsigned*>(p);
+    p += kSmemHist;
     m.ctl = reinterpret_cast<SharedCtl*>(p);
     return m;
 }
@@ -178,7 +200,25 @@ __device__ __forceinline__ void trace_add(const StreamArgs& a, int slot, u64 v) 
     if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 16 + slot] += v;
 }
 
-// ---- a warp's pool of admitted candidates ----------------------------------------------------------------------
+// ---- noting a cell -----------------------------------------------------------------------------------------------
+// Notes a cell in this lane's queue if its maximum reaches the bound: a compare, two address computations, two
+// predicated stores and a predicated increment - no branch.  `qv_base` / `qc_base` are the shared-memory addresses
+// of the lane's entry 0; entries of one lane are kThreads entries apart.
+__device__ __forceinline__ void note_cell_if(const float4 x, float mx, float thr, int id0, unsigned qv_base, unsigned qc_base, int& qn) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .u32 av, ac;\n\t"
+        "setp.ge.f32 p, %1, %2;\n\t"
+        "mad.lo.u32 av, %0, %10, %3;\n\t"
+        "mad.lo.u32 ac, %0, %11, %4;\n\t"
+        "@p st.shared.v4.f32 [av], {%5, %6, %7, %8};\n\t"
+        "@p st.shared.u32 [ac], %9;\n\t"
+        "@p add.s32 %0, %0, 1;\n\t}"
+        : "+r"(qn)
+        : "f"(mx), "f"(thr), "r"(qv_base), "r"(qc_base), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w), "r"(id0), "n"(kThreads * 16), "n"(kThreads * 4)
+        : "memory");
+}
+
+// ---- a warp's overflow pool (global memory; hostile data only) ------------------------------------------------------
 // Keeps the entries of the warp's pool that are >= floor_c, in place and in order; returns their number.
 __device__ __forceinline__ int filter_pool(u64* pool, int n, u64 floor_c) {
     const int lane = threadIdx.x & 31;
@@ -231,60 +271,212 @@ __device__ __forceinline__ u64 warp_kth_largest(const u64* pool, int n, int k) {
     return pfx;
 }
 
-// What a warp knows about its pool: entries, the value bound and the composite bound (0: none) they passed.
-struct PoolState {
-    int n;
+// What a warp carries through an item: cells in this lane's queue; and, the same in every lane, the value bound, the
+// composite bound its pool's entries passed (0: none) and the number of pool entries.
+struct WarpState {
+    int qn;
     float thr;
     u64 wcomp;
+    int pn;
 };
-// Makes room in a pool that is nearly full: refresh the bound, drop what it has overtaken; if the pool is still
-// too full (many equal values, or a stream that keeps rising), keep exactly the warp's k best - no logit of this
-// warp's stream below the k-th of them can be among the item's k best.
-__device__ __noinline__ PoolState compact_pool(u64* pool, int n, float thr, u64 wcomp, int k, SharedCtl* ctl, unsigned tag) {
-    thr = fmaxf(thr, min_warp_bounds(ctl, tag));
-    n = filter_pool(pool, n, max(comp_floor_of(thr), wcomp));
-    if (n > kPoolCap - 128) {
-        const u64 L = warp_kth_largest(pool, n, k);
-        n = filter_pool(pool, n, L);
-        wcomp = max(wcomp, L);
-        thr = fmaxf(thr, comp_floor_value(L));
+
+// Makes room in a pool that is nearly full: drop what the bound has overtaken; if the pool is still too full, keep
+// exactly the warp's k best - no logit of this warp's stream below the k-th of them can be among the item's k best.
+__device__ __forceinline__ void compact_pool(u64* pool, WarpState& st, int k, int pool_cap) {
+    st.pn = filter_pool(pool, st.pn, max(comp_floor_of(st.thr), st.wcomp));
+    if (st.pn > pool_cap - 128) {
+        const u64 L = warp_kth_largest(pool, st.pn, k);
+        st.pn = filter_pool(pool, st.pn, L);
+        st.wcomp = max(st.wcomp, L);
+        st.thr = fmaxf(st.thr, comp_floor_value(L));
     }
-    return PoolState{n, thr, wcomp};
 }
 
-// More candidates than the list holds have survived the final bound (many equal values): the CTA finds the k-th
-// largest over all pools by bisection and the list gets exactly the k best.  All consumer threads call; returns the
-// number of entries of the list.
-__device__ __noinline__ int overflow_select(u64* pool, int pn, int k, u64* list, SharedCtl* ctl) {
+// Moves the logits of this warp's noted cells that reach the bounds into the warp's pool; the queues are empty after.
+__device__ __forceinline__ void flush_queues_to_pool(const Smem& m, u64* pool, WarpState& st, int k, int pool_cap) {
     const int tid = threadIdx.x, lane = tid & 31;
-    u64 v[kPoolCap / 32];
-    u64 mn = ~0ull, mx = 0ull;
+    const unsigned lt = (1u << lane) - 1u;
+    pdl_wait_prior();   // the pools are the engine's: the previous launch in the stream may still be using them
+    const int rounds = __reduce_max_sync(0xffffffffu, st.qn);
+    for (int j = 0; j < rounds; ++j) {
+        if (st.pn > pool_cap - 128) compact_pool(pool, st, k, pool_cap);
+        const bool have = j < st.qn;
+        const float4 v = have ? m.qv[j * kThreads + tid] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const int id0 = have ? m.qc[j * kThreads + tid] : 0;
+        const float xs[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int j = 0; j < kPoolCap / 32; ++j) {
-        const int i = lane + 32 * j;
-        v[j] = i < pn ? pool[i] : 0ull;
-        if (i < pn) {
-            mn = min(mn, v[j]);
-            mx = max(mx, v[j]);
+        for (int e = 0; e < 4; ++e) {
+            const u64 c = make_comp(xs[e], id0 + e);
+            const bool ok = have && xs[e] >= st.thr && c >= st.wcomp;
+            const unsigned be = __ballot_sync(0xffffffffu, ok);
+            if (ok) pool[st.pn + __popc(be & lt)] = c;
+            st.pn += __popc(be);
         }
     }
-    cta_minmax(mn, mx, ctl);
-    const u64 L = bisect_bound(k, mn, mx, ctl, [&](u64 t) {
-        int c = 0;
+    __syncwarp();
+    st.qn = 0;
+}
+
+// A lane's queue is nearly full.  The warp refreshes its bound and drops the noted cells it has overtaken; if a lane
+// is still short of room, the cells are evened out over the warp's lanes (a cell carries its token id, so any lane
+// may hold it); and if the warp holds more live cells than that leaves room for, their logits move to the pool.
+__device__ __noinline__ WarpState make_room(WarpState st, int k, unsigned tag, u64* pool, int pool_cap) {
+    const Smem m = smem_view();
+    const int tid = threadIdx.x, lane = tid & 31;
+    const unsigned lt = (1u << lane) - 1u;
+    st.thr = fmaxf(st.thr, min_warp_bounds(m.ctl, tag));
+    int w = 0;
+    for (int i = 0; i < st.qn; ++i) {
+        const float4 v = m.qv[i * kThreads + tid];
+        if (fmaxf(max3(v.x, v.y, v.z), v.w) >= st.thr) {
+            if (w != i) {
+                m.qv[w * kThreads + tid] = v;
+                m.qc[w * kThreads + tid] = m.qc[i * kThreads + tid];
+            }
+            ++w;
+        }
+    }
+    st.qn = w;
+    if (!__any_sync(0xffffffffu, st.qn > kLaneQueue - 4)) return st;
+    const int wbase = tid & ~31;
+    int total = 0;
+    for (int j = 0; j < kLaneQueue; ++j) {
+        const bool have = j < st.qn;
+        const float4 v = have ? m.qv[j * kThreads + tid] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const int c = have ? m.qc[j * kThreads + tid] : 0;
+        const unsigned bm = __ballot_sync(0xffffffffu, have);   // every lane has read its entry j by now
+        if (have) {
+            const int p = total + __popc(bm & lt);   // p < 32 * (j + 1): the target row is at most j
+            m.qv[(p >> 5) * kThreads + wbase + (p & 31)] = v;
+            m.qc[(p >> 5) * kThreads + wbase + (p & 31)] = c;
+        }
+        total += __popc(bm);
+        __syncwarp();
+    }
+    st.qn = total > lane ? (total - lane + 31) >> 5 : 0;
+    if (total > 32 * (kLaneQueue - 4)) flush_queues_to_pool(m, pool, st, k, pool_cap);
+    return st;
+}
+
+// ---- selection and order of a row's candidates ----------------------------------------------------------------------
+// The candidates lie in `buf` (shared memory) in n_parts parts, part c at buf + c * stride with ctl->wcount[c]
+// entries, unordered, `total` in all.  Orders the k best into m.sorted and returns their number.  Few candidates are
+// ranked by counting right away; otherwise a 256-bucket histogram over the range of their value keys finds the
+// bucket the k-th lies in, and only the candidates from that bucket up (k and a few more, as a rule) are ranked.
+// All consumer threads must call, after a barrier that made buf and the counts visible.
+__device__ __forceinline__ int select_and_order(const Smem& m, const u64* buf, int n_parts, int stride, int total, int k) {
+    SharedCtl* ctl = m.ctl;
+    const int tid = threadIdx.x, lane = tid & 31;
+    if (total <= 0) return 0;
+    int n = total;
+    // where the candidates that are ranked go: the list - or, when they come from the list, the epilogue's arrays
+    u64* rk = buf == m.list ? reinterpret_cast<u64*>(m.work) : m.list;
+    static_assert(kSmemWork >= kSmemList, "the epilogue's arrays can hold a list");
+    if (buf == m.list && total <= 160) {
+        rk = m.list;   // ranked where they lie
+    } else if (total <= 160) {
+        // (the parts are copied into the list one after the other)
+        int at = 0;
+        for (int c = 0; c < n_parts; ++c) {
+            const int cnt = ctl->wcount[c];
+            for (int i = tid; i < cnt; i += kThreads) rk[at + i] = buf[(size_t)c * stride + i];
+            at += cnt;
+        }
+        consumer_sync();
+    } else {
+        unsigned kmn = 0xFFFFFFFFu, kmx = 0u;
+        for (int c = 0; c < n_parts; ++c) {
+            const int cnt = ctl->wcount[c];
+            for (int i = tid; i < cnt; i += kThreads) {
+                const unsigned key = (unsigned)(buf[(size_t)c * stride + i] >> 32);
+                kmn = min(kmn, key);
+                kmx = max(kmx, key);
+            }
+        }
+        u64 mn = kmn, mx = kmx;
+        if (tid < 256) m.hist[tid] = 0u;
+        if (tid == 0) ctl->n_el = 0;
+        cta_minmax(mn, mx, ctl);   // two barriers
+        kmn = (unsigned)mn;
+        kmx = (unsigned)mx;
+        const unsigned range = kmx - kmn;
+        const int sh = range >= 256u ? (32 - __clz(range)) - 8 : 0;
+        for (int c = 0; c < n_parts; ++c) {
+            const int cnt = ctl->wcount[c];
+            for (int i = tid; i < cnt; i += kThreads) atomicAdd(&m.hist[((unsigned)(buf[(size_t)c * stride + i] >> 32) - kmn) >> sh], 1u);
+        }
+        consumer_sync();
+        if (tid < 32) {   // the highest bucket b with at least min(k, total) candidates in buckets >= b
+            unsigned mine = 0u, h[8];
 #pragma unroll
-        for (int j = 0; j < kPoolCap / 32; ++j) c += v[j] >= t ? 1 : 0;
-        return c;
-    });
-    if (tid == 0) ctl->n_el = 0;
-    consumer_sync();
-    pn = filter_pool(pool, pn, L);
-    int base = 0;
-    if (lane == 0 && pn) base = atomicAdd(&ctl->n_el, pn);
-    base = __shfl_sync(0xffffffffu, base, 0);
-    for (int i = lane; i < pn; i += 32)
-        if (base + i < kListCap) list[base + i] = pool[i];
-    consumer_sync();
-    return min(ctl->n_el, kListCap);
+            for (int j = 0; j < 8; ++j) {
+                h[j] = m.hist[8 * lane + j];
+                mine += h[j];
+            }
+            unsigned above = mine;   // candidates in this lane's buckets and all higher ones
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned t = __shfl_down_sync(0xffffffffu, above, o);
+                if (lane + o < 32) above += t;
+            }
+            const unsigned want = (unsigned)min(k, total);
+            const unsigned ok = __ballot_sync(0xffffffffu, above >= want);
+            const int sel = 31 - __clz(ok);   // lane 0 always qualifies
+            if (lane == sel) {
+                unsigned run = above - mine;
+                int b = 8 * lane + 7;
+                for (; b > 8 * lane; --b) {
+                    if (run + h[b - 8 * lane] >= want) break;
+                    run += h[b - 8 * lane];
+                }
+                ctl->bsel = b;
+                ctl->nsel = (int)(run + h[b - 8 * lane]);
+            }
+        }
+        consumer_sync();
+        const unsigned bsel = (unsigned)ctl->bsel;
+        n = ctl->nsel;
+        if (n > kListCap) {
+            // many equal values around the k-th: the exact selection by bisection, over a flat copy of the candidates
+            // (the parts are moved together first; a part never moves past its own start)
+            u64* flat = const_cast<u64*>(buf);
+            int at = 0;
+            for (int c = 0; c < n_parts; ++c) {
+                const int cnt = ctl->wcount[c];
+                for (int i0 = 0; i0 < cnt; i0 += kThreads) {
+                    const int i = i0 + tid;
+                    const u64 v = i < cnt ? buf[(size_t)c * stride + i] : 0ull;
+                    consumer_sync();
+                    if (i < cnt) flat[at + i] = v;
+                    consumer_sync();
+                }
+                at += cnt;
+            }
+            n = select_list_topk(flat, total, k, m.sorted, ctl);
+            rk = flat;
+        } else {
+            for (int c = 0; c < n_parts; ++c) {
+                const int cnt = ctl->wcount[c];
+                for (int i0 = 0; i0 < cnt; i0 += kThreads) {
+                    const int i = i0 + tid;
+                    u64 v = 0ull;
+                    bool take = false;
+                    if (i < cnt) {
+                        v = buf[(size_t)c * stride + i];
+                        take = (((unsigned)(v >> 32) - kmn) >> sh) >= bsel;
+                    }
+                    const unsigned bm = __ballot_sync(0xffffffffu, take);
+                    int base = 0;
+                    if (lane == 0 && bm) base = atomicAdd(&ctl->n_el, __popc(bm));
+                    base = __shfl_sync(0xffffffffu, base, 0);
+                    if (take) rk[base + __popc(bm & ((1u << lane) - 1u))] = v;
+                }
+            }
+            consumer_sync();
+        }
+        if (tid == 0) ctl->n_el = 0;
+    }
+    return topk_sorted(rk, n, k, m.sorted, ctl);
 }
 
 // ---- the copy warp --------------------------------------------------------------------------------------------
@@ -430,7 +622,7 @@ __device__ __forceinline__ void setup_loop(const StreamArgs& a, const Smem& m, i
     }
 }
 
-// ---- the end of an item ---------------------------------------------------------------------------------------
+// ---- the end of a row -----------------------------------------------------------------------------------------
 // What the consumers carry from one item's end to the next: the row whose ticket is on its way (-1: none) and,
 // in thread 0 only, the ticket.
 struct Pending {
@@ -438,12 +630,23 @@ struct Pending {
     unsigned ticket;
 };
 
+// Orders the row's candidates (see select_and_order) and runs the epilogue.  All consumer threads call.
+__device__ __forceinline__ void finish_row(const StreamArgs& a, const Smem& m, const u64* buf, int n_parts, int stride, int total, const RowDesc& d) {
+    const int kk = select_and_order(m, buf, n_parts, stride, total, d.k);
+    trace_mark(a, 8);
+    const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
+    const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index, a.scan_sums};
+    row_epilogue(m.sorted, kk, rt, m.work, tout);
+    trace_mark(a, 9);
+    consumer_sync();   // the list, the ordered candidates and the gathered candidates may be written again
+}
+
 // The ticket of the row in `pend` has had an item's time to arrive: if it was the row's last, all chunks of the row
-// have published, and this CTA merges their ordered lists and runs the epilogue.  All consumer threads call.  Uses
-// the pools' memory (idle between items), the list, the ordered-candidate array and the epilogue's arrays.
+// have published, and this CTA gathers their candidates and finishes the row.  All consumer threads call, between
+// items (the lanes' queues are empty then: the gathered candidates take their memory).
 __device__ __forceinline__ void resolve_pending(const StreamArgs& a, const Smem& m, Pending& pend, const RowDesc* desc) {
     SharedCtl* ctl = m.ctl;
-    const int tid = threadIdx.x, lane = tid & 31;
+    const int tid = threadIdx.x;
     const int row = pend.row;
     if (row < 0) return;
     if (tid == 0) ctl->last = (pend.ticket == (unsigned)(a.n_chunks - 1)) ? 1 : 0;
@@ -452,127 +655,162 @@ __device__ __forceinline__ void resolve_pending(const StreamArgs& a, const Smem&
     if (!ctl->last) return;
     trace_mark(a, 7);
     const RowDesc d = *desc;
-    const int k = d.k, nl = a.n_chunks;
+    const int nl = a.n_chunks, cap = a.slot_cap;
     const u64* src = reinterpret_cast<const u64*>(a.scratch) + (size_t)row * (size_t)a.scratch_stride;
     if (tid == 0) {
         a.ticket[row] = 0u;   // ready for the next launch
         a.row_bound[row] = 0u;
     }
-    // Every chunk's list is ordered, so entry p - 1 of each (p = ceil(k / lists)) bounds the row's k best from below:
-    // at least p entries of every list reach the smallest of them.  Lists, counts and those entries are read in one
-    // go (L2 reads, never L1); entries past a list's count are stale and dropped below.
-    const int p = (k + nl - 1) / nl;
-    u64* lists = m.pools;
-    const int span = nl * k;
-    for (int e = tid; e < span; e += kThreads) lists[e] = __ldcg(src + e);
-    if (tid < nl) {
-        const int cnt = min((int)__ldcg(src + a.scratch_stride - 1 - tid), k);
-        ctl->wcount[tid] = cnt;
-        const u64 bj = __ldcg(src + (size_t)tid * k + (p - 1));
-        ctl->red[tid] = cnt >= p ? bj : 0ull;   // a list shorter than p: no bound at all
-    }
-    if (tid == 0) ctl->n_el = 0;
+    // Slots and counts are read in one go (L2 reads, never L1): what lies past a slot's count is stale and never looked at.
+    u64* gathered = reinterpret_cast<u64*>(m.qv);
+    const int span = nl * cap;
+    for (int e = tid; e < span; e += kThreads) gathered[e] = __ldcg(src + e);
+    if (tid < nl) ctl->wcount[tid] = min((int)__ldcg(src + a.scratch_stride - 1 - tid), cap);
     consumer_sync();
-    u64 bound = ~0ull;
-    for (int s = 0; s < nl; ++s) bound = min(bound, ctl->red[s]);
-    // the entries that reach the bound go to the list (at least k of them, a few dozen more as a rule)
-    for (int e0 = 0; e0 < span; e0 += kThreads) {
-        const int e = e0 + tid;
-        u64 c = 0ull;
-        bool take = false;
-        if (e < span) {
-            const int s1 = e / k, i1 = e - s1 * k;
-            c = lists[e];
-            take = i1 < ctl->wcount[s1] && c >= bound;
-        }
-        const unsigned bmask = __ballot_sync(0xffffffffu, take);
-        int base = 0;
-        if (lane == 0 && bmask) base = atomicAdd(&ctl->n_el, __popc(bmask));
-        base = __shfl_sync(0xffffffffu, base, 0);
-        const int at = base + __popc(bmask & ((1u << lane) - 1u));
-        if (take && at < kListCap) m.list[at] = c;
-    }
-    consumer_sync();
-    int n = ctl->n_el;
-    if (n > kListCap) {
-        // more than the list holds (short lists, so no bound): close the gaps between the lists (a list never moves
-        // past its own start), then select among all entries where they lie.  Rare.
-        int total = 0;
-        for (int s = 0; s < nl; ++s) {
-            const int cnt = ctl->wcount[s];
-            for (int i0 = 0; i0 < cnt; i0 += kThreads) {
-                const int i = i0 + tid;
-                const u64 v = i < cnt ? lists[s * k + i] : 0ull;
-                consumer_sync();
-                if (i < cnt) lists[total + i] = v;
-                consumer_sync();
-            }
-            total += cnt;
-        }
-        n = select_list_topk(lists, total, k, m.sorted, ctl);
-        for (int i = tid; i < n; i += kThreads) m.list[i] = lists[i];
-        consumer_sync();
-    }
-    if (tid == 0) ctl->n_el = 0;
-    const int kk = topk_sorted(m.list, n, k, m.sorted, ctl);
-    trace_mark(a, 8);
-    const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
-    const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index, a.scan_sums};
-    row_epilogue(m.sorted, kk, rt, m.work, tout);
-    trace_mark(a, 9);
-    consumer_sync();   // the list, the ordered candidates and the pools may be written again
+    int total = 0;
+    for (int c = 0; c < nl; ++c) total += ctl->wcount[c];
+    finish_row(a, m, gathered, nl, cap, total, d);
 }
 
-// All consumer threads call it once they have looked at the item's last tile: the final bound, the warps'
-// surviving candidates gathered into the list, the k best in order - and, for a row that is one chunk, the
-// epilogue; otherwise the k best are published and a ticket is drawn, whose value the next call looks at.
-__device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64* pool, int pn, float thr, u64 wcomp, float run_max, int row,
-                                         int chunk, unsigned tag, Pending& pend) {
+// ---- the end of an item ---------------------------------------------------------------------------------------
+// More candidates than the item's slot holds have reached the final bound (many equal values): every warp moves its
+// noted cells' logits to its pool and keeps its k best, the CTA finds the k-th largest over all pools by bisection,
+// and exactly the k best are written.  All consumer threads call; returns the number written.
+__device__ __noinline__ int overflow_exact(WarpState st, u64* pool, int pool_cap, int k, u64* dst) {
+    const Smem m = smem_view();
+    SharedCtl* ctl = m.ctl;
+    const int tid = threadIdx.x, lane = tid & 31;
+    flush_queues_to_pool(m, pool, st, k, pool_cap);
+    compact_pool(pool, st, k, pool_cap);
+    if (st.pn > k) {   // the warp's k best are all the item can need from it
+        const u64 L = warp_kth_largest(pool, st.pn, k);
+        st.pn = filter_pool(pool, st.pn, L);
+    }
+    u64 v[kPoolCap / 32];
+    u64 mn = ~0ull, mx = 0ull;
+    int mine = 0;
+#pragma unroll
+    for (int j = 0; j < kPoolCap / 32; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = i < st.pn ? pool[i] : 0ull;
+        if (i < st.pn) {
+            mn = min(mn, v[j]);
+            mx = max(mx, v[j]);
+            ++mine;
+        }
+    }
+    if (tid == 0) ctl->sum[0] = 0;
+    cta_minmax(mn, mx, ctl);
+    const int wsum = __reduce_add_sync(0xffffffffu, mine);
+    if (lane == 0 && wsum) atomicAdd(&ctl->sum[0], wsum);
+    consumer_sync();
+    const int total = ctl->sum[0];
+    consumer_sync();
+    u64 L = 0ull;
+    if (total > k)
+        L = bisect_bound(k, mn, mx, ctl, [&](u64 t) {
+            int c = 0;
+#pragma unroll
+            for (int j = 0; j < kPoolCap / 32; ++j) c += v[j] >= t ? 1 : 0;
+            return c;
+        });
+    if (tid == 0) ctl->n_el = 0;
+    consumer_sync();
+    st.pn = filter_pool(pool, st.pn, L);
+    int base = 0;
+    if (lane == 0 && st.pn) base = atomicAdd(&ctl->n_el, st.pn);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    for (int i = lane; i < st.pn; i += 32) dst[base + i] = pool[i];   // k entries at most in all: they fit every slot
+    consumer_sync();
+    return ctl->n_el;
+}
+
+// All consumer threads call it once they have looked at the item's last tile: the final bound; the logits of the
+// noted cells (and of the overflow pool, if it was used) that reach it are written - unordered - to the item's slot
+// of the row's scratch and a ticket is drawn, whose value the next call looks at; a row that is a single chunk is
+// finished right away.
+__device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64* pool, WarpState st, float run_max, int row, int chunk,
+                                         unsigned tag, Pending& pend) {
     SharedCtl* ctl = m.ctl;
     const int tid = threadIdx.x, lane = tid & 31;
     const int k = ctl->cur.k;
+    const bool single = a.n_chunks == 1;
     post_warp_bound(ctl, tag, warp_bound(run_max, k));
     consumer_sync();
-    thr = fmaxf(thr, min_warp_bounds(ctl, tag));
-    pn = filter_pool(pool, pn, max(comp_floor_of(thr), wcomp));
-    int base = 0;
-    if (lane == 0 && pn) base = atomicAdd(&ctl->n_el, pn);
-    base = __shfl_sync(0xffffffffu, base, 0);
-    if (base + pn <= kListCap)
-        for (int i = lane; i < pn; i += 32) m.list[base + i] = pool[i];
+    st.thr = fmaxf(st.thr, min_warp_bounds(ctl, tag));
+    pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
+    u64* dst = single ? m.list : reinterpret_cast<u64*>(a.scratch) + (size_t)row * (size_t)a.scratch_stride + (size_t)chunk * a.slot_cap;
+    const int cap = single ? kListCap : a.slot_cap;
+    // one noted cell per lane and round: the logits that reach the bounds are counted, the warp reserves room for them
+    // with one shared-memory atomic, and every lane writes its own
+    const int rounds = __reduce_max_sync(0xffffffffu, st.qn);
+    for (int j = 0; j < rounds; ++j) {
+        unsigned mask = 0u;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        int id0 = 0;
+        if (j < st.qn) {
+            v = m.qv[j * kThreads + tid];
+            id0 = m.qc[j * kThreads + tid];
+            const float xs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (xs[e] >= st.thr && (st.wcomp == 0ull || make_comp(xs[e], id0 + e) >= st.wcomp)) mask |= 1u << e;
+        }
+        const int cnt = __popc(mask);
+        int inc = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        const int wtotal = __shfl_sync(0xffffffffu, inc, 31);
+        if (wtotal == 0) continue;
+        int base = 0;
+        if (lane == 31) base = atomicAdd(&ctl->n_el, wtotal);
+        base = __shfl_sync(0xffffffffu, base, 31);
+        int p = base + inc - cnt;
+        const float xs[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (mask & (1u << e)) {
+                if (p < cap) dst[p] = make_comp(xs[e], id0 + e);
+                ++p;
+            }
+    }
+    if (st.pn > 0) {
+        st.pn = filter_pool(pool, st.pn, max(comp_floor_of(st.thr), st.wcomp));
+        int base = 0;
+        if (lane == 0 && st.pn) base = atomicAdd(&ctl->n_el, st.pn);
+        base = __shfl_sync(0xffffffffu, base, 0);
+        for (int i = lane; i < st.pn; i += 32)
+            if (base + i < cap) dst[base + i] = pool[i];
+    }
     consumer_sync();
     int n_el = ctl->n_el;
-    if (n_el > kListCap) n_el = overflow_select(pool, pn, k, m.list, ctl);
+    if (n_el > cap) n_el = overflow_exact(st, pool, a.pool_cap, k, dst);
     trace_mark(a, 5);
-    if (tid == 0) ctl->n_el = 0;   // for the next item (barriers follow)
-    const int kk = topk_sorted(m.list, n_el, k, m.sorted, ctl);
-    trace_mark(a, 6);
-    pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
-    if (a.n_chunks > 1) {
-        // chunk c of a row publishes its ordered candidates at entries [c * k, c * k + count) of the row's scratch, the
-        // count in entry stride - 1 - c, and leaves the bound they prove for the row's later chunks; then it draws a
-        // ticket.  The planner keeps chunks * (k + 1) within the stride.
-        u64* dst = reinterpret_cast<u64*>(a.scratch) + (size_t)row * (size_t)a.scratch_stride;
-        for (int i = tid; i < kk; i += kThreads) dst[chunk * k + i] = m.sorted[i];
+    if (!single) {
         if (tid == 0) {
-            dst[a.scratch_stride - 1 - chunk] = (u64)kk;
-            if (kk == k) atomicMax(a.row_bound + row, (unsigned)(m.sorted[k - 1] >> 32));
+            ctl->n_el = 0;   // for the next item (barriers follow)
+            u64* rowp = reinterpret_cast<u64*>(a.scratch) + (size_t)row * (size_t)a.scratch_stride;
+            rowp[a.scratch_stride - 1 - chunk] = (u64)n_el;
+            atomicMax(a.row_bound + row, float_key(st.thr));   // at least k logits of the row reach this item's final bound
         }
         consumer_sync();   // orders the CTA's stores before the ticket, whose release publishes them to the device
-        // the ticket drawn at the end of the item before has had this item's time to arrive; pools, list and ordered
-        // candidates are idle now
+        // the ticket drawn at the end of the item before has had this item's time to arrive
         Pending prev = pend;
         if (tid == 0) pend.ticket = ticket_add_acq_rel(a.ticket + row, 1u);   // not looked at before the next item's end
         pend.row = row;
         resolve_pending(a, m, prev, &ctl->prev);
         if (tid == 0) ctl->prev = ctl->cur;
+        trace_mark(a, 6);
     } else {
-        const RowDesc& d = ctl->cur;
-        const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
-        const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index, a.scan_sums};
-        row_epilogue(m.sorted, kk, rt, m.work, tout);
-        trace_mark(a, 9);
-        consumer_sync();   // the ordered candidates and the epilogue's arrays may be written again
+        if (tid == 0) {
+            ctl->n_el = 0;
+            ctl->wcount[0] = n_el;
+        }
+        consumer_sync();
+        finish_row(a, m, m.list, 1, 0, n_el, ctl->cur);
     }
 }
 
@@ -618,9 +856,9 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
 
     // ------------------------------------------------------------------------------------------ consumers
     const float ninf = -__int_as_float(0x7f800000);
-    const unsigned lt = (1u << lane) - 1u;
-    u64* const pool = m.pools + (size_t)warp * kPoolCap;
+    u64* const pool = reinterpret_cast<u64*>(a.pools) + ((size_t)blockIdx.x * kWarps + warp) * (size_t)a.pool_cap;
     float* const st_warp = m.stage + warp * kWTile;
+    const unsigned qv_base = smem_u32(m.qv + tid), qc_base = smem_u32(m.qc + tid);
     int it = 0;        // tiles of this CTA looked at so far (the position in the ring)
     int n_items = 0;
     Pending pend{-1, 0u};
@@ -644,41 +882,39 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
         const unsigned* bitmap = m.bitmap + (size_t)b * kItemBitmapWords;
         const int item_lo = tile0 * kTile;
         const float thr0 = ic->thr0;
-        float thr = thr0, run_max = ninf;
-        u64 wcomp = 0ull;   // composite bound of this warp after it had to keep its k best (0: none)
-        int pn = 0;         // entries in this warp's pool (the same value in every lane)
+        WarpState st{0, thr0, 0ull, 0};
+        float run_max = ninf;
         int col0 = item_lo + warp * kWTile;   // first column of this warp's part of the tile
         if (seq == 0) trace_mark(a, 1);
 
         for (int s = 0; s < nt; ++s, ++it, col0 += kTile) {
             const unsigned slot = (unsigned)it % kStages, par = ((unsigned)it / kStages) & 1u;
-            float* st = st_warp + slot * kTile;              // this warp's part of the CTA tile
+            float* stg = st_warp + slot * kTile;              // this warp's part of the CTA tile
             const int len = min(kWTile, V - col0);            // may be <= 0 in a row's last tile
             if (a.bulk_ok) {
                 if (!mbar_wait_bounded(&ctl->full[slot], par, ctl) && lane == 0) report_timeout(ctl, a.status);   // carry on with what is there
             } else if (len > 0) {   // rows not on 16-byte boundaries: the warp loads its part of the tile itself
                 const float* src = row_ptr + col0;
-                for (int e = lane; e < len; e += 32) st[e] = src[e];
+                for (int e = lane; e < len; e += 32) stg[e] = src[e];
                 __syncwarp();
             }
             if (seq == 0 && s == 0) trace_mark(a, 2);
             if (SOFTCAP) {
-                if (len > 0) softcap_tile(st, len, a.softcap, wb_row ? wb_row + col0 : nullptr);
+                if (len > 0) softcap_tile(stg, len, a.softcap, wb_row ? wb_row + col0 : nullptr);
             }
-            if (has_pen && len > 0 && !(a.debug & 4)) patch_tile(st, len, col0, item_lo, pen, bitmap, wb_row);
+            if (has_pen && len > 0 && !(a.debug & 4)) patch_tile(stg, len, col0, item_lo, pen, bitmap, wb_row);
             if (len < kWTile) {   // what lies past the end of a ragged row is made NaN: never a maximum, never reaches a bound
-                for (int e = max(len, 0) + lane; e < kWTile; e += 32) st[e] = __int_as_float(0x7fc00000);
+                for (int e = max(len, 0) + lane; e < kWTile; e += 32) stg[e] = __int_as_float(0x7fc00000);
                 __syncwarp();
             }
             // ---- look: the lane's four cells go to registers (four independent 16-byte loads)
-            const float4* st4 = reinterpret_cast<const float4*>(st);
+            const float4* st4 = reinterpret_cast<const float4*>(stg);
             const float4 x0 = st4[lane], x1 = st4[lane + 32], x2 = st4[lane + 64], x3 = st4[lane + 96];
             const float m0 = fmaxf(max3(x0.x, x0.y, x0.z), x0.w);
             const float m1 = fmaxf(max3(x1.x, x1.y, x1.z), x1.w);
             const float m2 = fmaxf(max3(x2.x, x2.y, x2.z), x2.w);
             const float m3 = fmaxf(max3(x3.x, x3.y, x3.z), x3.w);
-            const float mt = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-            run_max = fmaxf(run_max, mt);
+            run_max = fmaxf(max3(run_max, m0, m1), fmaxf(m2, m3));
             __syncwarp();
             if (lane == 0 && a.bulk_ok) mbar_arrive(&ctl->empty[slot]);   // the slot goes back to the copy warp
 
@@ -688,52 +924,16 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
                 post_warp_bound(ctl, tag, warp_bound(run_max, k));
                 if (s == 0 && thr0 == ninf) consumer_sync();
                 else __syncwarp();
-                thr = fmaxf(thr, min_warp_bounds(ctl, tag));
+                st.thr = fmaxf(st.thr, min_warp_bounds(ctl, tag));
             }
-            // ---- admit the logits that reach the bound (padding past the end of a row never does).  As a rule one or two
-            // cells of a warp tile hold such a logit: their lanes are visited one after the other, lanes 0..3 each taking
-            // one logit of the cell.  When many cells qualify (the first tiles of a row, masked or constant stretches) all
-            // lanes work on their own cells at once.
-            if (!(a.debug & 1) && __any_sync(0xffffffffu, mt >= thr)) {
+            // ---- note the cells whose maximum reaches the bound (padding past the end of a row never does)
+            if (__any_sync(0xffffffffu, st.qn > kLaneQueue - 4)) st = make_room(st, k, tag, pool, a.pool_cap);
+            if (!(a.debug & 1)) {
                 const int id_lane = col0 + 4 * lane + a.vocab_offset;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 x = q == 0 ? x0 : q == 1 ? x1 : q == 2 ? x2 : x3;
-                    const float mq = q == 0 ? m0 : q == 1 ? m1 : q == 2 ? m2 : m3;
-                    unsigned hits = __ballot_sync(0xffffffffu, mq >= thr);
-                    if (hits == 0u) continue;
-                    if (pn > kPoolCap - 128) {
-                        const PoolState ps = compact_pool(pool, pn, thr, wcomp, k, ctl, tag);
-                        pn = ps.n;
-                        thr = ps.thr;
-                        wcomp = ps.wcomp;
-                    }
-                    if (__popc(hits) <= 4) {
-                        do {
-                            const int src = __ffs(hits) - 1;
-                            hits &= hits - 1u;
-                            // the cell of lane `src`: lane e < 4 takes its logit e
-                            const float v0 = __shfl_sync(0xffffffffu, x.x, src), v1 = __shfl_sync(0xffffffffu, x.y, src);
-                            const float v2 = __shfl_sync(0xffffffffu, x.z, src), v3 = __shfl_sync(0xffffffffu, x.w, src);
-                            const float v = lane == 0 ? v0 : lane == 1 ? v1 : lane == 2 ? v2 : v3;
-                            const u64 c = make_comp(v, col0 + a.vocab_offset + 4 * src + 128 * q + lane);
-                            const bool ok = lane < 4 && v >= thr && c >= wcomp;
-                            const unsigned be = __ballot_sync(0xffffffffu, ok);
-                            if (ok) pool[pn + __popc(be & lt)] = c;
-                            pn += __popc(be);
-                        } while (hits);
-                    } else {
-                        const float xs[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const u64 c = make_comp(xs[e], id_lane + 128 * q + e);
-                            const bool ok = xs[e] >= thr && c >= wcomp;
-                            const unsigned be = __ballot_sync(0xffffffffu, ok);
-                            if (ok) pool[pn + __popc(be & lt)] = c;
-                            pn += __popc(be);
-                        }
-                    }
-                }
+                note_cell_if(x0, m0, st.thr, id_lane, qv_base, qc_base, st.qn);
+                note_cell_if(x1, m1, st.thr, id_lane + 128, qv_base, qc_base, st.qn);
+                note_cell_if(x2, m2, st.thr, id_lane + 256, qv_base, qc_base, st.qn);
+                note_cell_if(x3, m3, st.thr, id_lane + 384, qv_base, qc_base, st.qn);
             }
         }
         __syncwarp();
@@ -745,7 +945,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
             consumer_sync();
             continue;
         }
-        item_end(a, m, pool, pn, thr, wcomp, run_max, row, chunk, tag, pend);
+        item_end(a, m, pool, st, run_max, row, chunk, tag, pend);
         if (a.trace) trace_add(a, 13, (u64)(clock64() - te0));
     }
     // the last ticket this CTA drew may have been its row's last
@@ -907,20 +1107,28 @@ int launch_gather_patched(const float* logits, const RowDesc* rows, int n_rows, 
     return (int)cudaGetLastError();
 }
 
-// The chunk schedule of a launch: how every row is cut into work items.  `slots` = CTAs that run at once, `stride` =
-// entries of a row's scratch.  Returns the number of chunks (0: the rows cannot be scheduled within the scratch).
-int plan_chunks(int n_rows, int n_vocab, int kmax, int slots, int64_t stride, uint8_t* chunk_len) {
+// The chunk schedule of a launch: how every row is cut into work items.  `slots` = CTAs that run at once; a row may
+// have at most max_chunks chunks, and every chunk gets a slot of gather_cap / chunks entries (at least 3 k where
+// possible: about 2.3 k candidates reach an item's final bound, as a rule; never fewer than k).  Returns the number
+// of chunks (0: the rows cannot be scheduled) and the slot size.
+int plan_chunks(int n_rows, int n_vocab, int kmax, int slots, int gather_cap, int max_chunks, uint8_t* chunk_len, int* slot_cap) {
     const int T = (n_vocab + kTile - 1) / kTile;
-    const int64_t by_scratch = stride / ((kmax > 1 ? kmax : 1) + 1);
-    const int max_chunks = (int)(by_scratch < kMaxChunks ? by_scratch : kMaxChunks);
-    if (max_chunks < 1) return 0;
+    kmax = kmax > 1 ? kmax : 1;
+    max_chunks = max_chunks < kMaxChunks ? max_chunks : kMaxChunks;
+    const int want = 3 * kmax > 96 ? 3 * kmax : 96;             // the slot size aimed at
+    int by_slot = gather_cap / want;
+    const int hard = gather_cap / kmax;                          // more chunks than this and a slot could not hold k
+    const int min_chunks = (T + kItemTilesMax - 1) / kItemTilesMax;
+    if (by_slot < min_chunks) by_slot = min_chunks;              // long rows: smaller slots rather than no plan
+    if (by_slot < max_chunks) max_chunks = by_slot;
+    if (hard < max_chunks) max_chunks = hard;
+    if (max_chunks < 1 || min_chunks > max_chunks) return 0;
     const double per_cta = (double)n_rows * T / (slots > 1 ? slots : 1);   // tiles a CTA streams on average
     // Two to three items per CTA keep the dynamic hand-out balanced at little end-of-item work; an item never spans
     // more than kItemTilesMax tiles.
     int q = (int)(per_cta / 2.5 + 0.5);
     q = q < 1 ? 1 : (q > kItemTilesMax ? kItemTilesMax : q);
     while ((T + q - 1) / q > max_chunks && q < kItemTilesMax) ++q;
-    if ((T + q - 1) / q > max_chunks) return 0;
     // The last tiles of a row are cut into pieces that halve down to single tiles: the items the CTAs draw last are
     // short, so the CTAs finish together (pointless when a CTA works on one item only).
     int taper = (per_cta > q && q > 1) ? (q < T / 4 ? q : T / 4) : 0;
@@ -928,14 +1136,21 @@ int plan_chunks(int n_rows, int n_vocab, int kmax, int slots, int64_t stride, ui
         int n = 0;
         const int main_tiles = T - taper;
         const int n_main = (main_tiles + q - 1) / q;
-        for (int i = 0; i < n_main; ++i) chunk_len[n++] = (uint8_t)(main_tiles / n_main + (i < main_tiles % n_main ? 1 : 0));
-        for (int t = taper; t > 0 && n < kMaxChunks;) {
+        for (int i = 0; i < n_main && n < kMaxChunks; ++i) chunk_len[n++] = (uint8_t)(main_tiles / n_main + (i < main_tiles % n_main ? 1 : 0));
+        bool fits = n_main <= kMaxChunks;
+        for (int t = taper; t > 0;) {
             const int h = t > 1 ? (t + 1) / 2 : 1;
+            if (n == kMaxChunks) {
+                fits = false;
+                break;
+            }
             chunk_len[n++] = (uint8_t)h;
             t -= h;
-            if (t > 0 && n == kMaxChunks) n = kMaxChunks + 1;
         }
-        if (n <= max_chunks) return n;
+        if (fits && n <= max_chunks) {
+            *slot_cap = gather_cap / n;
+            return n;
+        }
         if (taper == 0) return 0;
         taper = 0;   // no room for the short pieces
     }
@@ -950,12 +1165,18 @@ namespace fsb {
 namespace {
 
 constexpr int kStaticMaxRows = FSB_STATIC_MAX_ROWS;
-constexpr int kStaticStride = 2 * kMaxChunks;   // a greedy row publishes one candidate and one count per chunk
+constexpr int kStaticChunks = 16;                // chunks a row is cut into at most (rows of up to a million logits)
+constexpr int kStaticSlot = 64;                  // a greedy item leaves a few dozen candidates at most
+constexpr int kStaticGather = kStaticChunks * kStaticSlot;
+constexpr int kStaticStride = kStaticGather + kStaticChunks;   // a row's slots, then its counts
+constexpr int kStaticPoolCap = 160;              // overflow pool of a warp: k = 1 and the candidates of 32 cells
+constexpr int kStaticMaxCtas = 160;              // CTAs of a launch (one per SM)
 constexpr size_t kStaticRowsOff = 0;                                                                   // RowDesc[kStaticMaxRows]
 constexpr size_t kStaticCountersOff = kStaticRowsOff + sizeof(RowDesc) * kStaticMaxRows;               // ticket[], row_bound[], work[]
 constexpr size_t kStaticStatusOff = kStaticCountersOff + sizeof(uint32_t) * (2 * kStaticMaxRows + kCounterWords);   // status word
 constexpr size_t kStaticScratchOff = 8192;                                                             // [kStaticMaxRows][kStaticStride] candidates
-constexpr size_t kStaticBytes = kStaticScratchOff + sizeof(u64) * (size_t)kStaticStride * kStaticMaxRows;
+constexpr size_t kStaticPoolsOff = kStaticScratchOff + sizeof(u64) * (size_t)kStaticStride * kStaticMaxRows;
+constexpr size_t kStaticBytes = kStaticPoolsOff + sizeof(u64) * (size_t)kStaticPoolCap * (kThreads / 32) * kStaticMaxCtas;
 static_assert(kStaticStatusOff + sizeof(uint32_t) <= kStaticScratchOff, "descriptors, counters and status fit below the candidates");
 
 // Zero when the library is loaded (static storage); every call starts by putting counters and status back to zero.
@@ -1027,6 +1248,8 @@ extern "C" int fsb_argmax_rows_static(int device, const float* logits_dev, int64
         a.hist = nullptr;
         a.scratch = reinterpret_cast<uint64_t*>(base + kStaticScratchOff);
         a.scratch_stride = kStaticStride;
+        a.pools = reinterpret_cast<uint64_t*>(base + kStaticPoolsOff);
+        a.pool_cap = kStaticPoolCap;
         a.ticket = counters;
         a.row_bound = counters + kStaticMaxRows;
         a.work = counters + 2 * kStaticMaxRows;
@@ -1036,13 +1259,17 @@ extern "C" int fsb_argmax_rows_static(int device, const float* logits_dev, int64
         a.n_rows = n_rows;
         a.n_vocab = n_vocab;
         a.tiles_per_row = (n_vocab + kTile - 1) / kTile;
-        a.n_chunks = plan_chunks(n_rows, n_vocab, 1, sd.slots, kStaticStride, a.chunk_len);
+        const int slots = sd.slots < kStaticMaxCtas ? sd.slots : kStaticMaxCtas;
+        int slot_cap = 0;
+        a.n_chunks = plan_chunks(n_rows, n_vocab, 1, slots, kStaticGather, kStaticChunks, a.chunk_len, &slot_cap);
+        a.slot_cap = slot_cap < kStaticSlot ? slot_cap : kStaticSlot;   // (the merging CTA's loads stay within a row's slots)
+        if (a.n_chunks > 0 && a.slot_cap * a.n_chunks > kStaticGather) a.n_chunks = 0;
         a.n_items = n_rows * a.n_chunks;
         a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (ld & 3) == 0) ? 1 : 0;
         if (rc != FSB_OK) {
         } else if (a.n_chunks <= 0) {
             rc = FSB_ERR_CAPACITY;   // more chunks per row than a row's scratch has entries
-        } else if (launch_stream_kernel(a, a.n_items < sd.slots ? a.n_items : sd.slots, st) != 0) {
+        } else if (launch_stream_kernel(a, a.n_items < slots ? a.n_items : slots, st) != 0) {
             rc = FSB_ERR_CUDA;
         } else if (flags & FSB_STATIC_WAIT) {
             uint32_t status = 0;

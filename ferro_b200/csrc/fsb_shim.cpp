@@ -41,7 +41,7 @@ struct Stream {
 };
 
 struct Plan {
-    int tiles_per_row = 0, n_chunks = 0, grid = 0;
+    int tiles_per_row = 0, n_chunks = 0, grid = 0, slot_cap = 0;
     uint8_t chunk_len[fsb::kMaxChunks] = {};
 };
 
@@ -97,7 +97,8 @@ struct fsb_handle {
     std::vector<Stream> streams;
     std::vector<int> free_ids;
     // device scratch shared by all batches of this handle
-    uint64_t* d_scratch = nullptr;     // [max_rows][kRowScratch] published candidate lists
+    uint64_t* d_scratch = nullptr;     // [max_rows][kRowScratch] published candidates
+    uint64_t* d_pools = nullptr;       // [CTAs][16][kPoolCap] overflow pools of the streaming kernel's warps
     uint32_t* d_counters = nullptr;    // [max_rows] tickets, [max_rows] row bounds, [kCounterWords] work counters: all zero between launches
     int32_t* d_kept_ids = nullptr;
     double* d_kept_pr = nullptr;
@@ -156,7 +157,7 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
     const int T = (n_vocab + fsb::kTile - 1) / fsb::kTile;
     pl.tiles_per_row = T;
     const int slots = std::max(1, h->sm_count * std::max(1, h->ctas_per_sm));
-    pl.n_chunks = fsb::plan_chunks(n_rows, n_vocab, kmax, slots, fsb::kRowScratch, pl.chunk_len);
+    pl.n_chunks = fsb::plan_chunks(n_rows, n_vocab, kmax, slots, fsb::kGatherCap, fsb::kMaxChunks, pl.chunk_len, &pl.slot_cap);
     if (const char* env = std::getenv("FSB_PLAN")) {
         uint8_t tmp[fsb::kMaxChunks];
         int n = 0, sum = 0;
@@ -172,8 +173,9 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
                 if (*end && *end != ',') ok = false;
             }
         }
-        if (ok && sum == T && (int64_t)n * (std::max(1, kmax) + 1) <= fsb::kRowScratch) {
+        if (ok && sum == T && fsb::kGatherCap / n >= std::max(1, kmax)) {
             pl.n_chunks = n;
+            pl.slot_cap = fsb::kGatherCap / n;
             std::memcpy(pl.chunk_len, tmp, (size_t)n);
         }
     }
@@ -301,6 +303,9 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.tiles_per_row = b->plan.tiles_per_row;
         a.n_chunks = b->plan.n_chunks;
         a.n_items = b->n_cand * b->plan.n_chunks;
+        a.slot_cap = b->plan.slot_cap;
+        a.pools = h->d_pools;
+        a.pool_cap = fsb::kPoolCap;
         std::memcpy(a.chunk_len, b->plan.chunk_len, sizeof a.chunk_len);
         a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (b->ld & 3) == 0) ? 1 : 0;
         a.write_back = (b->flags & FSB_WRITE_BACK) ? 1 : 0;
@@ -605,6 +610,7 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
     h->logits_stage_elems = (size_t)max_rows * (size_t)max_vocab;
     h->weights_elems = (size_t)max_rows * (size_t)max_vocab;
     if (cudaMalloc(reinterpret_cast<void**>(&h->d_scratch), sizeof(uint64_t) * (size_t)max_rows * fsb::kRowScratch) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_pools), sizeof(uint64_t) * (size_t)h->sm_count * h->ctas_per_sm * (fsb::kThreads / 32) * fsb::kPoolCap) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_counters), sizeof(uint32_t) * h->counter_words()) != cudaSuccess ||
         cudaMemset(h->d_counters, 0, sizeof(uint32_t) * h->counter_words()) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_ids), sizeof(int32_t) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
@@ -629,6 +635,7 @@ int fsb_destroy(fsb_handle* h) {
     }
     if (h->d_scratch) cudaFree(h->d_scratch);
     if (h->d_counters) cudaFree(h->d_counters);
+    if (h->d_pools) cudaFree(h->d_pools);
     if (h->d_kept_ids) cudaFree(h->d_kept_ids);
     if (h->d_kept_pr) cudaFree(h->d_kept_pr);
     if (h->d_kept_n) cudaFree(h->d_kept_n);

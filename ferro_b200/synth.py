@@ -71,9 +71,16 @@ def zipf_ids(seed: int, stream: int, n: int, vocab: int, s: float = 1.1) -> np.n
     return permutation(seed, stream + 1, vocab)[np.minimum(ranks, vocab - 1)].astype(np.int32)
 
 
-def softcap_host(x: np.ndarray, cap: float) -> np.ndarray:
-    """cap * tanhf(x / cap) in float32, as the Gemma-4 forward applies it (src/model_gemma4.cpp:521 of the reference)."""
-    x = x.astype(np.float32)
+def softcap_host(x: np.ndarray, cap: float, tanhf=None) -> np.ndarray:
+    """cap * tanh(x / cap) in float32: the final-logit softcap the Gemma-4 forward applies (src/model_gemma4.cpp:521
+    of the reference).  `tanhf(array, cap)` - an in-place float32 softcap built on the C library's tanhf, which is what
+    the reference calls - is used when given; otherwise numpy's float32 tanh, which may differ from it in the last bit.
+    Callers that compare with the reference pass the C function; either way every consumer of one generated array
+    sees the same values."""
+    x = np.ascontiguousarray(x, dtype=np.float32).copy()
+    if tanhf is not None:
+        tanhf(x, cap)
+        return x
     c = np.float32(cap)
     return (c * np.tanh(x / c, dtype=np.float32)).astype(np.float32)
 
@@ -92,8 +99,14 @@ def exact_logits(seed: int, rows: int, vocab: int, scale_pow2: int = -13, ties: 
 
 # ------------------------------------------------------------------------------------------------ the five configurations
 def _params(n, **kw):
-    from . import make_params
-    return make_params(n, **kw)
+    """n parameter records with the reference's defaults (src/sampler.h:13-20); built without loading the CUDA library."""
+    from . import PARAMS_DTYPE
+    p = np.zeros(n, dtype=PARAMS_DTYPE)
+    p["temperature"], p["top_k"], p["top_p"], p["min_p"] = 0.05, 50, 1.0, 0.0
+    p["repetition_penalty"], p["repeat_last_n"], p["penalty_from"], p["seed"] = 1.05, -1, 0, 0
+    for k, v in kw.items():
+        p[k] = v
+    return p
 
 
 def config1(vocab: int = 65536):
@@ -123,15 +136,15 @@ def config2(vocab: int = 65536):
     return dict(logits=lg.astype(np.float32), params=p, hists=hists)
 
 
-def config3(rows: int = 64, vocab: int = 262144):
+def config3(rows: int = 64, vocab: int = 262144, tanhf=None):
     """Gemma-4-style large vocabulary: Student-t(3) * 4 softcapped at 30 on the host, T 1, top-k 64, top-p 0.95,
-    penalty 1.0 / 1.1 on alternating rows over 512-id uniform histories, seeds 7 + row."""
+    penalty 1.0 / 1.1 on alternating rows over 512-id uniform histories, seeds 7 + row.  `tanhf`: see softcap_host."""
     raw = (student_t3(7, 100, rows * vocab) * 4.0).astype(np.float32).reshape(rows, vocab)
     p = _params(rows, temperature=1.0, top_k=64, top_p=0.95, min_p=0.0, repetition_penalty=1.0, repeat_last_n=-1, penalty_from=0)
     p["repetition_penalty"][1::2] = 1.1
     p["seed"] = 7 + np.arange(rows)
     hists = [randint(7, 500 + r, 512, vocab).astype(np.int32) for r in range(rows)]
-    return dict(logits=softcap_host(raw, 30.0), raw_logits=raw, params=p, hists=hists)
+    return dict(logits=softcap_host(raw, 30.0, tanhf), raw_logits=raw, params=p, hists=hists)
 
 
 def config4(streams: int = 8, window: int = 17, vocab: int = 65536, penalty: float = 1.0, hist_len: int = 0):
@@ -155,9 +168,9 @@ def config4(streams: int = 8, window: int = 17, vocab: int = 65536, penalty: flo
     return dict(logits=lg, params=p, hists=hists, rows=rows)
 
 
-def config5(rows: int = 512, vocab: int = 262144):
+def config5(rows: int = 512, vocab: int = 262144, tanhf=None):
     """Box-scale serving batch: Student-t(3) * 4 softcapped at 30, top-k 40, top-p 0.9, T 0.8, penalty 1.1 over
-    1024-id Zipf histories, seeds 99 + row."""
+    1024-id Zipf histories, seeds 99 + row.  `tanhf`: see softcap_host."""
     raw = (student_t3(99, 100, rows * vocab) * 4.0).astype(np.float32).reshape(rows, vocab)
     p = _params(rows, temperature=0.8, top_k=40, top_p=0.9, min_p=0.0, repetition_penalty=1.1, repeat_last_n=-1, penalty_from=0)
     p["seed"] = 99 + np.arange(rows)
@@ -169,4 +182,4 @@ def config5(rows: int = 512, vocab: int = 262144):
     for r in range(rows):
         ranks = np.searchsorted(cdf, uniforms(99, 1000 + r, 1024), side="left")
         hists.append(perm[np.minimum(ranks, vocab - 1)].astype(np.int32))
-    return dict(logits=softcap_host(raw, 30.0), params=p, hists=hists)
+    return dict(logits=softcap_host(raw, 30.0, tanhf), raw_logits=raw, params=p, hists=hists)

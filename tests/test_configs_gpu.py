@@ -52,7 +52,7 @@ def test_config2_mixed_decode_batch(engine, oracle):
 
 
 def test_config3_large_vocabulary_headline_shape(engine, oracle):
-    check(engine, oracle, synth.config3())
+    check(engine, oracle, synth.config3(tanhf=oracle.softcap))
 
 
 def test_config3_fused_softcap_variant(engine, oracle):
@@ -77,7 +77,7 @@ def test_config3_fused_softcap_variant(engine, oracle):
 
 
 def test_config5_serving_batch(engine, oracle):
-    check(engine, oracle, synth.config5(rows=96))
+    check(engine, oracle, synth.config5(rows=96, tanhf=oracle.softcap))
 
 
 def window_case(engine, oracle, cfg, stochastic=False, max_accept=None):
