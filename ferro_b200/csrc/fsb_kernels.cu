@@ -196,6 +196,10 @@ __device__ __forceinline__ float min_warp_bounds(SharedCtl* ctl, unsigned tag) {
 __device__ __forceinline__ void trace_mark(const StreamArgs& a, int slot) {
     if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 16 + slot] = global_timer_ns();
 }
+#define TR(n)                                                                                              \
+    do {                                                                                               \
+        if (a.trace && blockIdx.x == 0 && threadIdx.x == 0) a.trace[148 * 16 + (n)] = (u64)clock64();   \
+    } while (0)
 __device__ __forceinline__ void trace_add(const StreamArgs& a, int slot, u64 v) {
     if (a.trace && threadIdx.x == 0) a.trace[(size_t)blockIdx.x * 16 + slot] += v;
 }
@@ -364,7 +368,7 @@ __device__ __noinline__ WarpState make_room(WarpState st, int k, unsigned tag, u
 // ranked by counting right away; otherwise a 256-bucket histogram over the range of their value keys finds the
 // bucket the k-th lies in, and only the candidates from that bucket up (k and a few more, as a rule) are ranked.
 // All consumer threads must call, after a barrier that made buf and the counts visible.
-__device__ __forceinline__ int select_and_order(const Smem& m, const u64* buf, int n_parts, int stride, int total, int k) {
+__device__ __forceinline__ int select_and_order(const StreamArgs& a, const Smem& m, const u64* buf, int n_parts, int stride, int total, int k) {
     SharedCtl* ctl = m.ctl;
     const int tid = threadIdx.x, lane = tid & 31;
     if (total <= 0) return 0;
@@ -396,7 +400,9 @@ __device__ __forceinline__ int select_and_order(const Smem& m, const u64* buf, i
         u64 mn = kmn, mx = kmx;
         if (tid < 256) m.hist[tid] = 0u;
         if (tid == 0) ctl->n_el = 0;
+        TR(13);
         cta_minmax(mn, mx, ctl);   // two barriers
+        TR(14);
         kmn = (unsigned)mn;
         kmx = (unsigned)mx;
         const unsigned range = kmx - kmn;
@@ -406,6 +412,7 @@ __device__ __forceinline__ int select_and_order(const Smem& m, const u64* buf, i
             for (int i = tid; i < cnt; i += kThreads) atomicAdd(&m.hist[((unsigned)(buf[(size_t)c * stride + i] >> 32) - kmn) >> sh], 1u);
         }
         consumer_sync();
+        TR(15);
         if (tid < 32) {   // the highest bucket b with at least min(k, total) candidates in buckets >= b
             unsigned mine = 0u, h[8];
 #pragma unroll
@@ -434,6 +441,7 @@ __device__ __forceinline__ int select_and_order(const Smem& m, const u64* buf, i
             }
         }
         consumer_sync();
+        TR(16);
         const unsigned bsel = (unsigned)ctl->bsel;
         n = ctl->nsel;
         if (n > kListCap) {
@@ -475,6 +483,8 @@ __device__ __forceinline__ int select_and_order(const Smem& m, const u64* buf, i
             consumer_sync();
         }
         if (tid == 0) ctl->n_el = 0;
+        TR(17);
+        if (a.trace && blockIdx.x == 0 && threadIdx.x == 0) a.trace[148 * 16 + 41] = (u64)n | ((u64)total << 32);
     }
     return topk_sorted(rk, n, k, m.sorted, ctl);
 }
@@ -632,13 +642,16 @@ struct Pending {
 
 // Orders the row's candidates (see select_and_order) and runs the epilogue.  All consumer threads call.
 __device__ __forceinline__ void finish_row(const StreamArgs& a, const Smem& m, const u64* buf, int n_parts, int stride, int total, const RowDesc& d) {
-    const int kk = select_and_order(m, buf, n_parts, stride, total, d.k);
+    const int kk = select_and_order(a, m, buf, n_parts, stride, total, d.k);
+    TR(20);
     trace_mark(a, 8);
     const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
     const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k, d.flags, d.out_index, a.scan_sums};
     row_epilogue(m.sorted, kk, rt, m.work, tout);
+    TR(21);
     trace_mark(a, 9);
     consumer_sync();   // the list, the ordered candidates and the gathered candidates may be written again
+    TR(22);
 }
 
 // The ticket of the row in `pend` has had an item's time to arrive: if it was the row's last, all chunks of the row
@@ -653,6 +666,7 @@ __device__ __forceinline__ void resolve_pending(const StreamArgs& a, const Smem&
     pend.row = -1;
     consumer_sync();
     if (!ctl->last) return;
+    TR(10);
     trace_mark(a, 7);
     const RowDesc d = *desc;
     const int nl = a.n_chunks, cap = a.slot_cap;
@@ -666,7 +680,9 @@ __device__ __forceinline__ void resolve_pending(const StreamArgs& a, const Smem&
     const int span = nl * cap;
     for (int e = tid; e < span; e += kThreads) gathered[e] = __ldcg(src + e);
     if (tid < nl) ctl->wcount[tid] = min((int)__ldcg(src + a.scratch_stride - 1 - tid), cap);
+    TR(11);
     consumer_sync();
+    TR(12);
     int total = 0;
     for (int c = 0; c < nl; ++c) total += ctl->wcount[c];
     finish_row(a, m, gathered, nl, cap, total, d);
@@ -735,9 +751,13 @@ __device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64
     const int tid = threadIdx.x, lane = tid & 31;
     const int k = ctl->cur.k;
     const bool single = a.n_chunks == 1;
+    TR(0);
     post_warp_bound(ctl, tag, warp_bound(run_max, k));
+    TR(1);
     consumer_sync();
+    TR(2);
     st.thr = fmaxf(st.thr, min_warp_bounds(ctl, tag));
+    TR(3);
     pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
     u64* dst = single ? m.list : reinterpret_cast<u64*>(a.scratch) + (size_t)row * (size_t)a.scratch_stride + (size_t)chunk * a.slot_cap;
     const int cap = single ? kListCap : a.slot_cap;
@@ -777,6 +797,7 @@ __device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64
                 ++p;
             }
     }
+    TR(4);
     if (st.pn > 0) {
         st.pn = filter_pool(pool, st.pn, max(comp_floor_of(st.thr), st.wcomp));
         int base = 0;
@@ -786,9 +807,11 @@ __device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64
             if (base + i < cap) dst[base + i] = pool[i];
     }
     consumer_sync();
+    TR(5);
     int n_el = ctl->n_el;
     if (n_el > cap) n_el = overflow_exact(st, pool, a.pool_cap, k, dst);
     trace_mark(a, 5);
+    if (a.trace && blockIdx.x == 0 && threadIdx.x == 0) a.trace[148 * 16 + 40] = (u64)n_el | ((u64)rounds << 32);
     if (!single) {
         if (tid == 0) {
             ctl->n_el = 0;   // for the next item (barriers follow)
@@ -797,12 +820,15 @@ __device__ __forceinline__ void item_end(const StreamArgs& a, const Smem& m, u64
             atomicMax(a.row_bound + row, float_key(st.thr));   // at least k logits of the row reach this item's final bound
         }
         consumer_sync();   // orders the CTA's stores before the ticket, whose release publishes them to the device
+        TR(6);
         // the ticket drawn at the end of the item before has had this item's time to arrive
         Pending prev = pend;
         if (tid == 0) pend.ticket = ticket_add_acq_rel(a.ticket + row, 1u);   // not looked at before the next item's end
         pend.row = row;
+        TR(7);
         resolve_pending(a, m, prev, &ctl->prev);
         if (tid == 0) ctl->prev = ctl->cur;
+        TR(8);
         trace_mark(a, 6);
     } else {
         if (tid == 0) {
@@ -1157,130 +1183,3 @@ int plan_chunks(int n_rows, int n_vocab, int kmax, int slots, int gather_cap, in
 }
 
 }  // namespace fsb
-
-// ---------------------------------------------------------------------------------------------- fsb_argmax_rows_static
-// Greedy tokens of device-resident rows with no allocation at all: the streaming kernel above, run with every piece
-// of device memory it needs taken from one array that is part of this library's image.
-namespace fsb {
-namespace {
-
-constexpr int kStaticMaxRows = FSB_STATIC_MAX_ROWS;
-constexpr int kStaticChunks = 16;                // chunks a row is cut into at most (rows of up to a million logits)
-constexpr int kStaticSlot = 64;                  // a greedy item leaves a few dozen candidates at most
-constexpr int kStaticGather = kStaticChunks * kStaticSlot;
-constexpr int kStaticStride = kStaticGather + kStaticChunks;   // a row's slots, then its counts
-constexpr int kStaticPoolCap = 160;              // overflow pool of a warp: k = 1 and the candidates of 32 cells
-constexpr int kStaticMaxCtas = 160;              // CTAs of a launch (one per SM)
-constexpr size_t kStaticRowsOff = 0;                                                                   // RowDesc[kStaticMaxRows]
-constexpr size_t kStaticCountersOff = kStaticRowsOff + sizeof(RowDesc) * kStaticMaxRows;               // ticket[], row_bound[], work[]
-constexpr size_t kStaticStatusOff = kStaticCountersOff + sizeof(uint32_t) * (2 * kStaticMaxRows + kCounterWords);   // status word
-constexpr size_t kStaticScratchOff = 8192;                                                             // [kStaticMaxRows][kStaticStride] candidates
-constexpr size_t kStaticPoolsOff = kStaticScratchOff + sizeof(u64) * (size_t)kStaticStride * kStaticMaxRows;
-constexpr size_t kStaticBytes = kStaticPoolsOff + sizeof(u64) * (size_t)kStaticPoolCap * (kThreads / 32) * kStaticMaxCtas;
-static_assert(kStaticStatusOff + sizeof(uint32_t) <= kStaticScratchOff, "descriptors, counters and status fit below the candidates");
-
-// Zero when the library is loaded (static storage); every call starts by putting counters and status back to zero.
-static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
-
-constexpr int kStaticMaxDevices = 64;
-struct StaticDevice {
-    void* base = nullptr;   // device address of g_static_scratch on this device
-    int slots = 0;          // CTAs of the streaming kernel that fit on the device at once
-};
-StaticDevice g_static_dev[kStaticMaxDevices];
-
-// Row descriptors of plain greedy rows (no penalty window): row r starts at r * ld, its token goes to tokens[r].
-// The first thread also clears the counters and the status word a previous call may have left set (a call that was
-// not waited for and whose kernel reported an error): stream order puts this before the streaming kernel.
-__global__ void static_greedy_rows_kernel(RowDesc* rows, int n_rows, int64_t ld, uint32_t* counters, int n_counter_words) {
-    const int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r < n_counter_words) counters[r] = 0u;
-    if (r >= n_rows) return;
-    RowDesc d{};
-    d.logits_off = (int64_t)r * ld;
-    d.k = 1;
-    d.temperature = 0.0f;
-    d.top_p = 1.0f;
-    d.penalty = 1.0f;
-    d.flags = kRowGreedy;
-    d.out_index = r;
-    d.k_global = 1;
-    rows[r] = d;
-}
-
-}  // namespace
-}  // namespace fsb
-
-extern "C" int fsb_argmax_rows_static(int device, const float* logits_dev, int64_t ld, int n_rows, int n_vocab, int32_t* tokens_dev,
-                                      void* cuda_stream, unsigned flags) {
-    using namespace fsb;
-    if (!logits_dev || !tokens_dev || n_rows < 0 || n_vocab <= 0 || ld < n_vocab || (flags & ~FSB_STATIC_WAIT)) return FSB_ERR_INVALID;
-    if (n_rows > kStaticMaxRows) return FSB_ERR_CAPACITY;   // the static array holds FSB_STATIC_MAX_ROWS rows of scratch, no more
-    if (device < 0 || device >= kStaticMaxDevices) return FSB_ERR_NO_DEVICE;
-    if (n_rows == 0) return FSB_OK;
-    int prev = -1;
-    if (cudaGetDevice(&prev) != cudaSuccess) return FSB_ERR_NO_DEVICE;
-    if (cudaSetDevice(device) != cudaSuccess) return FSB_ERR_NO_DEVICE;
-    int rc = FSB_OK;
-    StaticDevice& sd = g_static_dev[device];
-    if (!sd.base) {   // first call on this device (it is current): where the array lives, how many CTAs fit
-        void* p = nullptr;
-        int per_sm = 0, sms = 0;
-        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || !p) rc = FSB_ERR_CUDA;
-        if (rc == FSB_OK && prepare_device_kernels(&per_sm) != 0) rc = FSB_ERR_CUDA;
-        if (rc == FSB_OK && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) rc = FSB_ERR_CUDA;
-        if (rc == FSB_OK) {
-            sd.slots = (sms > 0 ? sms : 1) * (per_sm > 0 ? per_sm : 1);
-            sd.base = p;
-        }
-    }
-    if (rc == FSB_OK) {
-        unsigned char* base = static_cast<unsigned char*>(sd.base);
-        cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-        RowDesc* rows = reinterpret_cast<RowDesc*>(base + kStaticRowsOff);
-        uint32_t* counters = reinterpret_cast<uint32_t*>(base + kStaticCountersOff);
-        const int n_counter_words = 2 * kStaticMaxRows + kCounterWords + 1;   // tickets, bounds, work counters, status
-        static_greedy_rows_kernel<<<(n_counter_words + 63) / 64, 64, 0, st>>>(rows, n_rows, ld, counters, n_counter_words);
-        if (cudaGetLastError() != cudaSuccess) rc = FSB_ERR_CUDA;
-        StreamArgs a{};
-        a.logits = logits_dev;
-        a.rows = rows;
-        a.hist = nullptr;
-        a.scratch = reinterpret_cast<uint64_t*>(base + kStaticScratchOff);
-        a.scratch_stride = kStaticStride;
-        a.pools = reinterpret_cast<uint64_t*>(base + kStaticPoolsOff);
-        a.pool_cap = kStaticPoolCap;
-        a.ticket = counters;
-        a.row_bound = counters + kStaticMaxRows;
-        a.work = counters + 2 * kStaticMaxRows;
-        a.tokens = tokens_dev;
-        a.status = reinterpret_cast<uint32_t*>(base + kStaticStatusOff);
-        a.row_ld = ld;
-        a.n_rows = n_rows;
-        a.n_vocab = n_vocab;
-        a.tiles_per_row = (n_vocab + kTile - 1) / kTile;
-        const int slots = sd.slots < kStaticMaxCtas ? sd.slots : kStaticMaxCtas;
-        int slot_cap = 0;
-        a.n_chunks = plan_chunks(n_rows, n_vocab, 1, slots, kStaticGather, kStaticChunks, a.chunk_len, &slot_cap);
-        a.slot_cap = slot_cap < kStaticSlot ? slot_cap : kStaticSlot;   // (the merging CTA's loads stay within a row's slots)
-        if (a.n_chunks > 0 && a.slot_cap * a.n_chunks > kStaticGather) a.n_chunks = 0;
-        a.n_items = n_rows * a.n_chunks;
-        a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (ld & 3) == 0) ? 1 : 0;
-        if (rc != FSB_OK) {
-        } else if (a.n_chunks <= 0) {
-            rc = FSB_ERR_CAPACITY;   // more chunks per row than a row's scratch has entries
-        } else if (launch_stream_kernel(a, a.n_items < slots ? a.n_items : slots, st) != 0) {
-            rc = FSB_ERR_CUDA;
-        } else if (flags & FSB_STATIC_WAIT) {
-            uint32_t status = 0;
-            if (cudaMemcpyAsync(&status, a.status, sizeof status, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
-                cudaStreamSynchronize(st) != cudaSuccess) {
-                rc = FSB_ERR_CUDA;
-            } else if (status != 0u) {
-                rc = FSB_ERR_DEVICE;
-            }
-        }
-    }
-    if (prev >= 0 && prev != device) cudaSetDevice(prev);
-    return rc;
-}

@@ -19,10 +19,14 @@
 
 #include "../../include/ferro_sampler_b200.h"
 #include "fsb_internal.h"
+#include "fsb_pairs_internal.h"
 
 static_assert(sizeof(ferro_sampler_params) == 40, "parameter struct must match the reference's 40-byte SamplerParams");
 static_assert(offsetof(ferro_sampler_params, seed) == 32, "seed sits at offset 32 in the reference struct");
-static_assert(FSB_MAX_CANDIDATE_K == fsb::kMaxK, "header constant out of step with the kernel geometry");
+static_assert(FSB_MAX_CANDIDATE_K == fsb::kMaxK && fsb::kMaxK == fsb_pairs::kMaxK, "header constant out of step with the kernel geometry");
+static_assert(sizeof(fsb::RowDesc) == sizeof(fsb_pairs::RowDesc) && offsetof(fsb::RowDesc, out_index) == offsetof(fsb_pairs::RowDesc, out_index),
+              "both streaming kernels read the same descriptor array");
+static_assert(fsb_pairs::kMergeCap <= fsb::kRowScratch, "a row's scratch serves either kernel");
 
 namespace {
 
@@ -55,7 +59,9 @@ struct fsb_batch {
     int64_t cap_hist = 0;
     int n_cand = 0, n_full = 0;   // rows of the candidate kernel / of the full-row kernel
     int kmax = 1;
-    Plan plan;
+    Plan plan;                    // the persistent kernel's schedule
+    fsb_pairs::Plan pplan;        // the static-plan kernel's
+    bool use_pairs = true;        // which of the two streaming kernels samples the candidate rows
     int64_t hist_ids = 0;         // window ids staged with the batch
     int64_t gather_ids = 0;       // window values a write-back for a host caller brings back
     int64_t table_ints = 0;       // int32 words of the per-stream table of a resident verification call, staged behind the window ids
@@ -86,7 +92,8 @@ struct fsb_handle {
     int device = 0;
     int max_rows = 0, max_vocab = 0;
     int64_t max_hist = 0;
-    int sm_count = 0, ctas_per_sm = 0;
+    int sm_count = 0, ctas_per_sm = 0, pairs_ctas_per_sm = 0;
+    int pair_ok = 1;                   // clusters of CTAs can be launched on this device
     cudaStream_t stream = nullptr;
     bool own_stream = false;
     float softcap = 0.0f;
@@ -183,6 +190,19 @@ Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
     return pl;
 }
 
+// Which streaming kernel samples a batch's candidate rows.  The static-plan kernel (one segment per CTA, a row's
+// CTAs exchange candidates on chip) has the shorter end of a launch: it takes the batches that are one wave of CTAs.
+// The persistent kernel (work items drawn from a counter, row ends overlapped with streaming) takes batches of many
+// rows.  FSB_KERNEL=pairs|persistent in the environment forces one - a tuning aid of the benchmark.
+bool choose_pairs_kernel(const fsb_handle* h, int n_rows, int n_vocab) {
+    if (const char* env = std::getenv("FSB_KERNEL")) {
+        if (std::strcmp(env, "pairs") == 0) return true;
+        if (std::strcmp(env, "persistent") == 0) return false;
+    }
+    (void)n_vocab;
+    return n_rows < 2 * std::max(1, h->sm_count);
+}
+
 void free_batch_buffers(fsb_batch* b) {
     if (!b) return;
     if (b->h_in) cudaFreeHost(b->h_in);
@@ -265,7 +285,9 @@ int finalize_batch(fsb_handle* h, fsb_batch* b) {
     b->n_full = n_full;
     b->kmax = kmax;
     b->plan = make_plan(h, std::max(n_cand, 1), b->n_vocab, kmax);
-    if (n_cand > 0 && b->plan.n_chunks <= 0) return fail(h, FSB_ERR_CAPACITY, "rows of %d logits cannot be scheduled with k = %d", b->n_vocab, kmax);
+    b->pplan = fsb_pairs::make_plan(std::max(n_cand, 1), b->n_vocab, kmax, std::max(1, h->sm_count * std::max(1, h->pairs_ctas_per_sm)));
+    b->use_pairs = choose_pairs_kernel(h, std::max(n_cand, 1), b->n_vocab);
+    if (n_cand > 0 && !b->use_pairs && b->plan.n_chunks <= 0) return fail(h, FSB_ERR_CAPACITY, "rows of %d logits cannot be scheduled with k = %d", b->n_vocab, kmax);
     return FSB_OK;
 }
 
@@ -279,7 +301,41 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
     if (shard_out && b->n_full > 0)
         return fail(h, FSB_ERR_RANGE, "rows whose candidate count exceeds %d (top_k = 0 or large) cannot be sharded by vocabulary", fsb::kMaxK);
     const int32_t* hist = b->hist_dev ? b->hist_dev : b->d_hist();
-    if (b->n_cand > 0) {
+    if (b->n_cand > 0 && b->use_pairs) {
+        fsb_pairs::StreamArgs a{};
+        a.logits = logits_dev;
+        a.rows = reinterpret_cast<const fsb_pairs::RowDesc*>(b->d_rows());
+        a.hist = hist;
+        a.scratch = h->d_scratch;
+        a.ticket = h->d_counters;
+        a.tokens = b->d_tokens;
+        a.status = b->d_status();
+        a.kept_ids = keep_kept ? h->d_kept_ids : nullptr;
+        a.kept_pr = keep_kept ? h->d_kept_pr : nullptr;
+        a.kept_n = keep_kept ? h->d_kept_n : nullptr;
+        a.shard_out = shard_out;
+        a.shard_n = shard_n;
+        a.trace = h->d_trace;
+        a.row_ld = (b->n_full == 0) ? b->ld : -1;   // descriptors are in row order when every row takes this kernel
+        a.n_rows = b->n_cand;
+        a.n_vocab = b->n_vocab;
+        a.tiles_per_row = b->pplan.tiles_per_row;
+        a.tiles_per_cta = b->pplan.tiles_per_cta;
+        a.total_tiles = b->n_cand * b->pplan.tiles_per_row;
+        a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (b->ld & 3) == 0) ? 1 : 0;
+        a.write_back = (b->flags & FSB_WRITE_BACK) ? 1 : 0;
+        a.vocab_offset = h->vocab_offset;
+        a.softcap = h->softcap;
+        a.overlap = h->launch_overlap;
+        const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
+        // rows of exactly 2, 4 or 8 aligned segments: the CTAs of a row run as a cluster and exchange candidates on chip
+        a.pair = 0;
+        for (int c = 2; c <= 8; c *= 2)   // receive buffer: (c - 1) lists of kmax entries in 512
+            if (h->pair_ok && a.tiles_per_row == c * a.tiles_per_cta && grid == c * a.n_rows && (c - 1) * b->kmax <= 512) a.pair = c;
+        const int e = fsb_pairs::launch_stream_kernel(a, grid, h->stream);
+        if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+        h->counters.kernel_launches++;
+    } else if (b->n_cand > 0) {
         fsb::StreamArgs a{};
         a.logits = logits_dev;
         a.rows = b->d_rows();
@@ -602,6 +658,7 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
     if (prop.major < 10) return bail(FSB_ERR_NO_DEVICE);   // kernels are built for sm_100a only
     h->sm_count = prop.multiProcessorCount;
     if (fsb::prepare_device_kernels(&h->ctas_per_sm) != 0 || h->ctas_per_sm <= 0) return bail(FSB_ERR_CUDA);
+    if (fsb_pairs::prepare_device_kernels(&h->pairs_ctas_per_sm) != 0 || h->pairs_ctas_per_sm <= 0) return bail(FSB_ERR_CUDA);
     if (fsb::prepare_full_row_kernel(max_vocab) != 0) return bail(FSB_ERR_CUDA);
     if (cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(FSB_ERR_CUDA);
     h->own_stream = true;
