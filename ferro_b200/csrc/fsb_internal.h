@@ -116,8 +116,8 @@ int launch_gather_patched(const float* logits, const RowDesc* rows, int n_rows, 
 // Defined in fsb_fullrow.cu.
 size_t full_row_smem_bytes(int n_vocab);
 int prepare_full_row_kernel(int max_vocab);
-int launch_full_row_kernel(const float* logits, const RowDesc* rows, int n_rows, const int32_t* hist, uint64_t* weights, int32_t* tokens,
-                           int32_t* kept_ids, double* kept_pr, int32_t* kept_n, uint32_t* status, int n_vocab, int vocab_offset,
-                           int write_back, float softcap, void* stream);
+int launch_full_row_kernel(const float* logits, const RowDesc* rows, int n_rows, const int32_t* hist, int32_t* tokens, int32_t* kept_ids,
+                           double* kept_pr, int32_t* kept_n, int record, uint32_t* status, int n_vocab, int vocab_offset, int write_back,
+                           float softcap, uint64_t* trace, void* stream);
 
 }  // namespace fsb

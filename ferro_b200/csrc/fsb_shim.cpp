@@ -96,6 +96,8 @@ struct fsb_handle {
     int pair_ok = 1;                   // clusters of CTAs can be launched on this device
     cudaStream_t stream = nullptr;
     bool own_stream = false;
+    cudaStream_t side = nullptr;       // the full-vocabulary kernel of a mixed batch runs here, beside the streaming kernel
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     float softcap = 0.0f;
     int32_t vocab_offset = 0;
     int32_t global_vocab = 0;          // vocabulary sharding: columns of the whole row (0: this engine holds whole rows)
@@ -113,8 +115,6 @@ struct fsb_handle {
     bool kept_valid = false;
     float* d_logits_stage = nullptr;   // device copy of host logits: max_rows x max_vocab, allocated with the engine
     size_t logits_stage_elems = 0;
-    uint64_t* d_weights = nullptr;     // fixed-point weights of the full-row kernel: sized with the engine
-    size_t weights_elems = 0;
     uint64_t* d_trace = nullptr;       // caller-owned diagnostics buffer, or null
     fsb_batch* own = nullptr;          // the batch behind fsb_sample_batch / fsb_verify_windows
     int32_t* d_pool = nullptr;         // resident histories: max_hist ids, carved into power-of-two regions
@@ -303,6 +303,23 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
     if (shard_out && b->n_full > 0)
         return fail(h, FSB_ERR_RANGE, "rows whose candidate count exceeds %d (top_k = 0 or large) cannot be sharded by vocabulary", fsb::kMaxK);
     const int32_t* hist = b->hist_dev ? b->hist_dev : b->d_hist();
+    // A mixed batch runs its two kernels side by side (they touch different rows): the full-vocabulary kernel, the
+    // longer of the two, goes first, on the side stream, behind everything already queued on the engine's stream.
+    const bool side_by_side = b->n_full > 0 && b->n_cand > 0;
+    if (b->n_full > 0) {
+        cudaStream_t where = h->stream;
+        if (side_by_side) {
+            FSB_CUDA(h, cudaEventRecord(h->ev_fork, h->stream));
+            FSB_CUDA(h, cudaStreamWaitEvent(h->side, h->ev_fork, 0));
+            where = h->side;
+        }
+        const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, hist, b->d_tokens,
+                                                  h->d_kept_ids, h->d_kept_pr, h->d_kept_n, keep_kept ? 1 : 0, b->d_status(), b->n_vocab, h->vocab_offset,
+                                                  (b->flags & FSB_WRITE_BACK) ? 1 : 0, h->softcap, h->d_trace ? h->d_trace + 4096 * 8 : nullptr, where);
+        if (e != 0) return fail(h, FSB_ERR_CUDA, "full-row kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+        h->counters.kernel_launches++;
+        if (side_by_side) FSB_CUDA(h, cudaEventRecord(h->ev_join, h->side));
+    }
     if (b->n_cand > 0 && b->use_pairs) {
         fsb_pairs::StreamArgs a{};
         a.logits = logits_dev;
@@ -376,15 +393,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         h->counters.kernel_launches++;
     }
-    if (b->n_full > 0) {   // rows whose candidate set does not fit on chip: the multi-pass full-row kernel
-        if ((size_t)b->n_full * (size_t)b->n_vocab > h->weights_elems) return fail(h, FSB_ERR_CAPACITY, "full-vocabulary rows exceed the engine's scratch");
-        const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, hist, h->d_weights, b->d_tokens,
-                                                  keep_kept ? h->d_kept_ids : nullptr, keep_kept ? h->d_kept_pr : nullptr,
-                                                  keep_kept ? h->d_kept_n : nullptr, b->d_status(), b->n_vocab, h->vocab_offset,
-                                                  (b->flags & FSB_WRITE_BACK) ? 1 : 0, h->softcap, h->stream);
-        if (e != 0) return fail(h, FSB_ERR_CUDA, "full-row kernel launch: %s", cudaGetErrorString((cudaError_t)e));
-        h->counters.kernel_launches++;
-    }
+    if (side_by_side) FSB_CUDA(h, cudaStreamWaitEvent(h->stream, h->ev_join, 0));
     b->launched = true;
     h->kept_valid = keep_kept;
     return FSB_OK;
@@ -664,10 +673,13 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
     if (fsb::prepare_full_row_kernel(max_vocab) != 0) return bail(FSB_ERR_CUDA);
     if (cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(FSB_ERR_CUDA);
     h->own_stream = true;
+    if (cudaStreamCreateWithFlags(&h->side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming) != cudaSuccess)
+        return bail(FSB_ERR_CUDA);
     // Everything a call may need is allocated here, so that no call allocates: the rows' scratch, the counters, the
-    // kept-set record, the id pool, the staging area of host logits and the full-row kernel's weights.
+    // kept-set record, the id pool and the staging area of host logits.
     h->logits_stage_elems = (size_t)max_rows * (size_t)max_vocab;
-    h->weights_elems = (size_t)max_rows * (size_t)max_vocab;
     if (cudaMalloc(reinterpret_cast<void**>(&h->d_scratch), sizeof(uint64_t) * (size_t)max_rows * fsb::kRowScratch) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_pools), sizeof(uint64_t) * (size_t)h->sm_count * h->ctas_per_sm * (fsb::kThreads / 32) * fsb::kPoolCap) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_counters), sizeof(uint32_t) * h->counter_words()) != cudaSuccess ||
@@ -676,8 +688,7 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_pr), sizeof(double) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_n), sizeof(int32_t) * (size_t)max_rows) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_pool), sizeof(int32_t) * (size_t)std::max<int64_t>(max_hist_ids, 1)) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&h->d_logits_stage), sizeof(float) * h->logits_stage_elems) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&h->d_weights), sizeof(uint64_t) * h->weights_elems) != cudaSuccess)
+        cudaMalloc(reinterpret_cast<void**>(&h->d_logits_stage), sizeof(float) * h->logits_stage_elems) != cudaSuccess)
         return bail(FSB_ERR_CUDA);
     if (alloc_batch(h, max_rows, max_hist_ids, std::max<int64_t>(max_hist_ids, 1), &h->own) != FSB_OK) return bail(FSB_ERR_CUDA);
     *out = h;
@@ -700,8 +711,10 @@ int fsb_destroy(fsb_handle* h) {
     if (h->d_kept_n) cudaFree(h->d_kept_n);
     if (h->d_pool) cudaFree(h->d_pool);
     if (h->d_logits_stage) cudaFree(h->d_logits_stage);
-    if (h->d_weights) cudaFree(h->d_weights);
     if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
+    if (h->side) cudaStreamDestroy(h->side);
+    if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+    if (h->ev_join) cudaEventDestroy(h->ev_join);
     delete h;
     return FSB_OK;
 }

@@ -93,7 +93,8 @@ def compare_with_oracle(engine, tokens, ref, params, V, check_kept=True):
             if k <= fb.MAX_CANDIDATE_K:
                 if n != nk or (ids != ref["kept_ids"][i, :nk]).any() or np.abs(pr - ref["kept_pr"][i, :nk]).max() > PROB_TOL:
                     kept_bad.append(i)
-            else:   # full-row kernel: size of the kept set, its last id and its total probability
-                if n != nk or ids[0] != ref["kept_ids"][i, nk - 1] or abs(pr[0] - ref["r_tot"][i, 1]) > PROB_TOL:
+            else:   # full-vocabulary kernel: the kept set's size, and its first MAX_CANDIDATE_K candidates one by one
+                m = min(nk, fb.MAX_CANDIDATE_K, ref["kept_ids"].shape[1])
+                if n != nk or len(ids) < m or (ids[:m] != ref["kept_ids"][i, :m]).any() or np.abs(pr[:m] - ref["kept_pr"][i, :m]).max() > PROB_TOL:
                     kept_bad.append(i)
     return hard, near, kept_bad
