@@ -43,7 +43,8 @@ PARAMS_DTYPE = np.dtype(
 API_SYMBOLS = [
     "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap", "fsb_batch_shard_launch", "fsb_batch_merge_launch", "fsb_argmax_rows_static", "fsb_stream_history_set", "fsb_stream_history_append", "fsb_stream_history_len",
     "fsb_sample_batch_resident",
-    "fsb_set_trace_buffer", "fsb_set_scan_sums", "fsb_set_vocab_shard", "fsb_verify_windows_resident",
+    "fsb_set_trace_buffer", "fsb_set_vocab_shard", "fsb_batch_max_k", "fsb_batch_shard_launch_packed", "fsb_batch_merge_launch_packed",
+    "fsb_batch_tokens_device", "fsb_batch_check", "fsb_verify_windows_resident",
     "fsb_server_defaults_init", "fsb_params_from_request", "fsb_params_apply_cli_flag",
     "fsb_params_default", "fsb_params_validate", "fsb_stream_open", "fsb_stream_close", "fsb_stream_params",
     "fsb_stream_state_get", "fsb_stream_state_set", "fsb_sample_batch", "fsb_verify_windows", "fsb_last_kept",
@@ -93,7 +94,6 @@ def load_library(build_if_missing: bool = True):
     L.fsb_set_vocab_offset.argtypes = [vp, C.c_int32]
     L.fsb_set_launch_overlap.argtypes = [vp, C.c_int]
     L.fsb_set_trace_buffer.argtypes = [vp, vp]
-    L.fsb_set_scan_sums.argtypes = [vp, C.c_int]
     L.fsb_set_vocab_shard.argtypes = [vp, C.c_int32, C.c_int32]
     L.fsb_verify_windows_resident.argtypes = [vp, i32, vp, vp, vp, vp, i64, i32, vp, vp, vp, vp, u32]
     L.fsb_params_default.argtypes = [vp]
@@ -117,6 +117,12 @@ def load_library(build_if_missing: bool = True):
     L.fsb_batch_tokens.argtypes = [vp, vp, vp]
     L.fsb_batch_shard_launch.argtypes = [vp, vp, vp, vp, vp]
     L.fsb_batch_merge_launch.argtypes = [vp, vp, vp, vp, i32]
+    L.fsb_batch_max_k.argtypes = [vp]
+    L.fsb_batch_shard_launch_packed.argtypes = [vp, vp, vp, vp, i32]
+    L.fsb_batch_merge_launch_packed.argtypes = [vp, vp, vp, i32, i32, i32, i32]
+    L.fsb_batch_tokens_device.argtypes = [vp]
+    L.fsb_batch_tokens_device.restype = vp
+    L.fsb_batch_check.argtypes = [vp, vp]
     L.fsb_batch_kernel_count.argtypes = [vp]
     L.fsb_batch_free.argtypes = [vp, vp]
     L.fsb_counters.argtypes = [vp, C.POINTER(_Counters)]
@@ -126,7 +132,7 @@ def load_library(build_if_missing: bool = True):
     L.fsb_sample_batch_resident.argtypes = [vp, i32, vp, vp, i64, i32, vp, u32]
     L.fsb_argmax_rows_static.argtypes = [C.c_int, vp, i64, i32, i32, vp, vp, u32]
     for name in API_SYMBOLS:
-        if name not in ("fsb_last_error", "fsb_params_default", "fsb_server_defaults_init"):
+        if name not in ("fsb_last_error", "fsb_params_default", "fsb_server_defaults_init", "fsb_batch_tokens_device"):
             getattr(L, name).restype = i32
     _lib = L
     return L
@@ -192,6 +198,30 @@ class Batch:
         self.engine._check(self.engine.lib.fsb_batch_merge_launch(self.engine._h, self._ptr, C.c_void_p(int(lists_dev_ptr)),
                                                                   C.c_void_p(int(counts_dev_ptr)), int(n_lists)))
 
+    @property
+    def max_k(self) -> int:
+        """Largest candidate count of the staged rows (on this shard): a packed list needs max_k + 1 words."""
+        return int(self.engine.lib.fsb_batch_max_k(self._ptr))
+
+    def shard_launch_packed(self, logits_shard_dev_ptr: int, packed_out_dev_ptr: int, stride_words: int):
+        """``fsb_batch_shard_launch_packed``: per row [count, candidates ...] in `stride_words` 64-bit words."""
+        self.engine._check(self.engine.lib.fsb_batch_shard_launch_packed(self.engine._h, self._ptr, C.c_void_p(int(logits_shard_dev_ptr)),
+                                                                         C.c_void_p(int(packed_out_dev_ptr)), int(stride_words)))
+
+    def merge_launch_packed(self, packed_dev_ptr: int, stride_words: int, n_lists: int, row_begin: int, n_rows: int):
+        """``fsb_batch_merge_launch_packed``: finish rows [row_begin, row_begin + n_rows) from [n_lists][n_rows][stride_words]."""
+        self.engine._check(self.engine.lib.fsb_batch_merge_launch_packed(self.engine._h, self._ptr, C.c_void_p(int(packed_dev_ptr)), int(stride_words),
+                                                                         int(n_lists), int(row_begin), int(n_rows)))
+
+    @property
+    def tokens_device_ptr(self) -> int:
+        """Device address of the batch's token array ([rows] int32, indexed by row)."""
+        return int(self.engine.lib.fsb_batch_tokens_device(self._ptr))
+
+    def check(self):
+        """Waits for the batch's launches and raises if the device reported an error."""
+        self.engine._check(self.engine.lib.fsb_batch_check(self.engine._h, self._ptr))
+
     def tokens(self) -> np.ndarray:
         out = np.zeros(self.n_rows, dtype=np.int32)
         self.engine._check(self.engine.lib.fsb_batch_tokens(self.engine._h, self._ptr, out.ctypes.data))
@@ -254,10 +284,6 @@ class Engine:
     def set_vocab_shard(self, offset: int, global_vocab: int):
         """This engine holds columns [offset, offset + n_vocab) of rows that are `global_vocab` columns wide."""
         self._check(self.lib.fsb_set_vocab_shard(self._h, int(offset), int(global_vocab)))
-
-    def set_scan_sums(self, on: bool):
-        """Epilogue sums by warp prefix scans instead of one thread adding in candidate order (see the C header)."""
-        self._check(self.lib.fsb_set_scan_sums(self._h, 1 if on else 0))
 
     # -- streams
     def open_stream(self, params) -> int:

@@ -13,8 +13,8 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libferro_sampler_b200.so")
-SOURCES = ["fsb_kernels.cu", "fsb_pairs.cu", "fsb_fullrow.cu", "fsb_shim.cpp", "fsb_request.cpp"]
-HEADERS = ["fsb_internal.h", "fsb_device.cuh", "fsb_pairs_internal.h", "fsb_pairs_device.cuh", os.path.join("..", "..", "include", "ferro_sampler_b200.h")]
+SOURCES = ["fsb_stream.cu", "fsb_fullrow.cu", "fsb_support.cu", "fsb_shim.cpp", "fsb_request.cpp"]
+HEADERS = ["fsb_internal.h", "fsb_device.cuh", os.path.join("..", "..", "include", "ferro_sampler_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -1,11 +1,11 @@
-// fsb_device.cuh - device-side building blocks shared by the sampler kernels (sm_100a).
+// fsb_device.cuh - device-side building blocks of the static-plan streaming kernel (sm_100a).
 //
 //  * order-preserving 64-bit candidate keys ("composites"): (logit descending, token id ascending) becomes plain
 //    unsigned descending order, with -0.0f and +0.0f mapped to the same key - the order of the reference's
 //    comparator `a.first > b.first || (a.first == b.first && a.second < b.second)` (src/sampler.cpp:31,34);
-//  * mbarrier + 1-D bulk asynchronous copy (global -> this CTA's shared memory) wrappers and the
-//    programmatic-dependent-launch controls;
-//  * CTA-wide selection and ordering of the k largest composites of a list in shared memory;
+//  * mbarrier + 1-D bulk asynchronous copy (global -> this CTA's shared memory) wrappers; streaming 16-byte
+//    loads and the programmatic-dependent-launch controls;
+//  * a CTA-wide selection of the k largest composites by bisection with counting barriers;
 //  * the per-row epilogue: softmax in fp64 with the reference's sequential sums, min-p, top-p and the draw
 //    (src/sampler.cpp:37-49).
 #pragma once
@@ -51,8 +51,6 @@ __device__ __forceinline__ float comp_floor_value(u64 L) {
     const float t = comp_value(L);
     return (t != t) ? -__int_as_float(0x7f800000) : t;
 }
-// The smallest composite a logit >= t can have (t is not NaN): its key with every token id allowed.
-__device__ __forceinline__ u64 comp_floor_of(float t) { return (u64)float_key(t) << 32; }
 
 // ---------------------------------------------------------------------------------------------- mbarrier / bulk copy
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -90,9 +88,27 @@ __device__ __forceinline__ void mbar_arrive(u64* bar) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// Ticket counter shared by the CTAs that work on one row: the add releases this thread's earlier writes - and those
-// of the CTA's other threads that a barrier ordered before it - to the whole device, and acquires what earlier
-// ticket holders released.
+// Thread-block clusters (pairs of CTAs that share a row): rank in the cluster, the address of a shared-memory
+// location in another CTA of the cluster, stores to it, and the cluster's barrier (arrive releases this thread's
+// stores to the cluster, wait acquires the others').
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned cluster_map_shared(unsigned local_addr, unsigned rank) {
+    unsigned a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void cluster_store_u64(unsigned addr, u64 v) { asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory"); }
+__device__ __forceinline__ void cluster_store_u32(unsigned addr, unsigned v) { asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// Ticket counter shared by the CTAs of a row: the add releases this thread's earlier writes - and those of the
+// CTA's other threads that a barrier ordered before it - to the whole device, and acquires what earlier ticket
+// holders released.
 __device__ __forceinline__ unsigned ticket_add_acq_rel(unsigned* p, unsigned v) {
     unsigned old;
     asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
@@ -108,41 +124,40 @@ __device__ __forceinline__ u64 global_timer_ns() {
 // ---------------------------------------------------------------------------------------------- shared control block
 constexpr int kNumWarps = kThreads / 32;
 
-// Barrier of the kThreads consumer threads of a CTA (named barrier 1).  The streaming kernel has two more warps
-// (copies, set-up), which never take part in it; kernels with only kThreads threads use it like __syncthreads().
+// Barrier of the kThreads consumer threads of a CTA (named barrier 1).  The streaming kernel has one more warp,
+// the copy producer, which never takes part in it; kernels with only kThreads threads use it like __syncthreads().
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
-// One work item of the streaming kernel as its set-up warp hands it to the copy warp and the consumers.
-struct alignas(16) ItemCtx {
-    alignas(16) RowDesc d;  // the row's descriptor (written with 16-byte stores)
-    const float* row_ptr;   // the row's logits
-    int done;               // 1: there is no more work (the other fields are not set)
-    int row;                // index of the row's descriptor
-    int chunk;              // chunk of the row
-    int tile0, ntiles;      // tiles of the row that make up the chunk
-    float thr0;             // a value that k logits of the row are already known to reach (-inf: none)
+// What the streaming kernel knows about the segment it is working on (written once per segment by one thread).
+struct SegCtx {
+    const float* row;   // the row's logits
+    float pen;          // repetition penalty of the row
+    float cap;          // softcap, 0 = off
+    int has_pen;
+    int id_base;        // token id of column 0
+    int seg_lo;         // first column of the segment (= column of bit 0 of the bitmap)
+    int n_vocab;
+    int vec_ok;         // rows start on 16-byte boundaries
+    int k;              // the row's candidate count
+    int final_in_mem;   // write-back mode: the row in global memory already holds the transformed logits
 };
 
-struct alignas(16) SharedCtl {
-    u64 full[kStages];                // "tile landed": completed by the copy (or by the copy warp for tiny tails)
+struct SharedCtl {
+    u64 full[kStages];                // "tile landed": completed by the copy (or by the producer for tiny tails)
     u64 empty[kStages];               // "tile consumed": every consumer warp hands the ring slot back
-    u64 item_posted[2];               // "the item's place in the matrix is known": the copies may start
-    u64 item_ready[2];                // "the item's descriptor and penalty bitmap are complete": the consumers may start
-    u64 item_free[2];                 // "the consumers are done with the item's descriptor and bitmap"
     u64 red[2 * kNumWarps];           // cross-warp reduction scratch
     double dsum;
-    alignas(16) u64 wbound[kNumWarps];     // per-warp admission bounds (see the streaming kernel): item tag << 32 | float bits
-    int wcount[kMaxChunks];           // lengths of a row's ordered candidate lists while they are merged
+    alignas(16) float wbound[kNumWarps];   // per-warp admission bounds (see the streaming kernel); read with 16-byte loads
+    int wcount[kNumWarps];            // lengths of a row's ordered candidate lists while they are merged
     int sum[3];                       // rotating counters of the selection steps
     int out_cnt;
-    int n_el;                         // candidates of the current item written so far
-    int last;
-    int bsel, nsel;                   // histogram selection: the bucket the k-th candidate lies in, candidates from there up
+    int base, last;
     int imax, imin1, imin2;
-    int abort;                        // a wait ran out of time: every later wait is cut short, the kernel winds down
-    RowDesc cur;                      // descriptor of the item whose end-of-item work is running
-    RowDesc prev;                     // descriptor of the row whose ticket is still on its way (see the streaming kernel)
-    alignas(16) ItemCtx item[2];
+    int need_compact;                 // a lane's queue is nearly full: the CTA must re-select
+    int abort;                        // a copy did not land in time
+    u64 ev_bound;                     // composite bound of the latest re-selection (0: nothing was dropped)
+    int recv_n[8];                    // clustered CTAs: candidates CTA r of the row's cluster has put into part r - 1 of the receive buffer (entry r)
+    SegCtx seg;
 };
 
 // ---------------------------------------------------------------------------------------------- top-k selection
@@ -241,7 +256,6 @@ struct RowTail {
     int k;
     int flags;
     int out_index;
-    int scan_sums;
 };
 
 struct TailOut {
@@ -250,78 +264,117 @@ struct TailOut {
     double* kept_pr;
     int32_t* kept_n;
     u64* shard_out;
-    int32_t* shard_n;
+    int32_t* shard_n;       // null: the count goes to the header word of the row's list
+    int shard_stride;
     unsigned* status;
 };
 
-// Bitonic sort, descending, of the 32 values held by the lanes of one warp.
-__device__ __forceinline__ u64 warp_sort32_desc(u64 v) {
+// Bitonic sort, descending, of 32 * S values held by one warp: value i sits in slot i / 32 of lane i % 32.
+template <int S>
+__device__ __forceinline__ void warp_sort_desc(u64 (&v)[S]) {
     const int lane = threadIdx.x & 31;
 #pragma unroll
-    for (int k2 = 2; k2 <= 32; k2 <<= 1) {
+    for (int k2 = 2; k2 <= 32 * S; k2 <<= 1) {
+        // exchanges between register slots (partner distance >= 32); the direction of a block depends on the slot only
 #pragma unroll
-        for (int j = k2 >> 1; j > 0; j >>= 1) {
-            const u64 o = __shfl_xor_sync(0xffffffffu, v, j);
-            const bool up = (lane & k2) == 0;
-            const bool lower = (lane & j) == 0;
-            v = (up == lower) ? max(v, o) : min(v, o);
+        for (int j = k2 >> 1; j >= 32; j >>= 1) {
+#pragma unroll
+            for (int q = 0; q < S; ++q) {
+                const int q2 = q ^ (j >> 5);
+                if (q < q2) {
+                    const bool up = ((q * 32) & k2) == 0;
+                    const u64 hi = max(v[q], v[q2]), lo = min(v[q], v[q2]);
+                    v[q] = up ? hi : lo;
+                    v[q2] = up ? lo : hi;
+                }
+            }
+        }
+        // exchanges between lanes
+#pragma unroll 1
+        for (int j = (k2 >> 1) < 16 ? (k2 >> 1) : 16; j > 0; j >>= 1) {
+#pragma unroll
+            for (int q = 0; q < S; ++q) {
+                const u64 o = __shfl_xor_sync(0xffffffffu, v[q], j);
+                const bool up = ((q * 32 + lane) & k2) == 0;
+                const bool lower = (lane & j) == 0;
+                v[q] = (up == lower) ? max(v[q], o) : min(v[q], o);
+            }
         }
     }
-    return v;
 }
 
 // Orders the k largest of buf[0..n) (distinct composites in shared memory; fewer if n < k) into out[0..kk),
-// descending, and returns kk = min(n, k).  Lists longer than kThreads entries are first cut down to k by bisection.
-// The rank of an entry is the number of entries above it: entry i is counted by kThreads / n' neighbouring threads
-// (n' = n rounded up to a power of two), each over its share of the list (every load is a broadcast), and their
-// counts are added with shuffles.  buf is overwritten only by the cut; `out` has room for kMaxK composites and must
-// not overlap buf.  All consumer threads must call, after a barrier that made buf visible; out is visible on return.
+// descending, and returns kk = min(n, k).  Long lists are first cut down to k by bisection.  What is left (at most
+// kMaxK entries) is cut into runs of 32: warp w sorts run w in registers and puts it back; then the thread that
+// holds entry i of a run finds by binary search how many entries of every other run are larger - the sum, plus i,
+// is the entry's rank.  buf is overwritten (with room for the last run's padding: 32 * ceil(n / 32) entries); `out`
+// has room for kMaxK composites and must not overlap buf.  All consumer threads must call, after a barrier that
+// made buf visible; out is visible to all on return.
 static __device__ __forceinline__ int topk_sorted(u64* buf, int n, int k, u64* out, SharedCtl* ctl) {
-    const int tid = threadIdx.x;
-    if (n > kThreads) n = select_list_topk(buf, n, k, out, ctl);
-    int shift = 0;   // log2 of the threads per entry
-    while ((n << (shift + 1)) <= kThreads && shift < 5) ++shift;
-    const int P = 1 << shift;
-    const int i = tid >> shift, part = tid & (P - 1);
-    const int len = (n + P - 1) >> shift;
-    const int j0 = part * len, j1 = min(n, j0 + len);
-    const u64 c = i < n ? buf[i] : ~0ull;
-    int cnt = 0;
-#pragma unroll 4
-    for (int j = j0; j < j1; ++j) cnt += buf[j] > c ? 1 : 0;
-    for (int o = 1; o < P; o <<= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
-    if (i < n && part == 0 && cnt < k) out[cnt] = c;
+    static_assert(kMaxK <= 32 * kNumWarps, "one run per warp");
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (n > kMaxK) n = select_list_topk(buf, n, k, out, ctl);
+    const int runs = (n + 31) >> 5;
+    u64 c = 0ull;   // 0 is below every composite: padding sorts to the end of the last run
+    if (warp < runs) {
+        u64 v[1];
+        v[0] = tid < n ? buf[tid] : 0ull;
+        warp_sort_desc<1>(v);
+        c = v[0];
+        buf[tid] = c;
+    }
+    consumer_sync();
+    if (c != 0ull) {
+        int rank = lane;
+#pragma unroll
+        for (int r2 = 0; r2 < kMaxK / 32; ++r2) {
+            if (r2 < runs && r2 != warp) {
+                const u64* run = buf + 32 * r2;   // descending: count its entries above c
+                int lo = 0;
+#pragma unroll
+                for (int step = 16; step > 0; step >>= 1)
+                    if (run[lo + step - 1] > c) lo += step;
+                if (run[lo] > c) ++lo;
+                rank += lo;
+            }
+        }
+        if (rank < k) out[rank] = c;
+    }
     consumer_sync();
     return n < k ? n : k;
 }
 
 // srt[0..kk) holds the row's candidates in order (largest first).  Either hands them out (vocabulary-sharded mode)
-// or finishes the row: softmax over the candidates in fp64, sums in candidate order, min-p, top-p, draw.  `work` is
-// scratch for 2 * kMaxK doubles that does not overlap srt.  All consumer threads must call it with the same
-// arguments; only the first warp works, so the call contains no CTA barrier.  srt and work must be visible to the
-// first warp (a barrier before the call), and must not be rewritten before the next CTA barrier after it.
-static __device__ __forceinline__ void row_epilogue(const u64* srt, int kk, const RowTail r, double* work, const TailOut o) {
+// or finishes the row: softmax over the candidates in fp64, sequential sums in candidate order, min-p, top-p,
+// draw.  `work` is scratch for 2 * kMaxK doubles that does not overlap srt.  All consumer threads must call it with
+// the same arguments.
+static __device__ __forceinline__ void row_epilogue(const u64* srt, int kk, const RowTail r, double* work, SharedCtl* ctl, const TailOut o) {
     const int tid = threadIdx.x;
-    if (tid >= 32) return;
-    const int lane = tid;
     double* e = work;
     double* P = work + kMaxK;
     if (kk <= 0) {   // nothing but NaNs in the row
-        if (lane == 0) {
+        if (tid == 0) {
             atomicOr(o.status, kStatusEmptyRow);
-            if (o.shard_out) o.shard_n[r.out_index] = 0;
+            if (o.shard_out && o.shard_n) o.shard_n[r.out_index] = 0;
+            else if (o.shard_out) o.shard_out[(size_t)r.out_index * o.shard_stride] = 0ull;
             else o.tokens[r.out_index] = 0;
             if (o.kept_n) o.kept_n[r.out_index] = 0;
         }
         return;
     }
     if (o.shard_out) {
-        for (int i = lane; i < kk; i += 32) o.shard_out[(size_t)r.out_index * kMaxK + i] = srt[i];
-        if (lane == 0) o.shard_n[r.out_index] = kk;
+        u64* list = o.shard_out + (size_t)r.out_index * o.shard_stride;
+        if (o.shard_n) {
+            if (tid < kk) list[tid] = srt[tid];
+            if (tid == 0) o.shard_n[r.out_index] = kk;
+        } else {
+            if (tid < kk) list[1 + tid] = srt[tid];
+            if (tid == 0) list[0] = (u64)kk;
+        }
         return;
     }
     if (r.flags & kRowGreedy) {   // first index of the maximum (src/sampler.cpp:19-23)
-        if (lane == 0) {
+        if (tid == 0) {
             o.tokens[r.out_index] = comp_id(srt[0]);
             if (o.kept_n) o.kept_n[r.out_index] = 0;
         }
@@ -329,102 +382,64 @@ static __device__ __forceinline__ void row_epilogue(const u64* srt, int kk, cons
     }
     // pr[i] = exp((double)(x_i - x_0) / T)   (fp32 subtraction, fp64 division, src/sampler.cpp:40)
     const float mx = comp_value(srt[0]);
-    const double temp = (double)r.temperature;
-    for (int i = lane; i < kk; i += 32) e[i] = exp(__ddiv_rn((double)__fsub_rn(comp_value(srt[i]), mx), temp));
-    __syncwarp();
-    // The reference adds in candidate order, one after the other (src/sampler.cpp:41,44,46): one lane runs the chain
-    // (the loads do not depend on it, so they run ahead).  The cumulative sums P[i] = pr[0] + ... + pr[i] serve the
-    // top-p walk, `tot` and the draw walk alike: the reference adds the same numbers in the same order in all three.
-    // With scan_sums the two chains are warp prefix scans instead: the sums then differ from the reference's in the
-    // last bits (far inside the 1e-6 the parity contract allows), and a row costs two short scans.
-    double s = 0.0;
-    if (!r.scan_sums) {
-        if (lane == 0) {
+    if (tid < kk) e[tid] = exp(__ddiv_rn((double)__fsub_rn(comp_value(srt[tid]), mx), (double)r.temperature));
+    consumer_sync();
+    // The reference adds in candidate order, one after the other: one thread runs the chain (the loads do not depend
+    // on it, so they run ahead).  The cumulative sums P[i] = pr[0] + ... + pr[i] serve the top-p walk, `tot` and the
+    // draw walk alike: the reference adds the same numbers in the same order in all three.
+    if (tid == 0) {
+        double s = 0.0;
 #pragma unroll 8
-            for (int i = 0; i < kk; ++i) s = __dadd_rn(s, e[i]);
-        }
-        s = __shfl_sync(0xffffffffu, s, 0);
-        for (int i = lane; i < kk; i += 32) e[i] = __ddiv_rn(e[i], s);
-        __syncwarp();
-        if (lane == 0) {
-            double c = 0.0;
+        for (int i = 0; i < kk; ++i) s = __dadd_rn(s, e[i]);
+        ctl->dsum = s;
+        ctl->imax = 0;
+        ctl->imin1 = 0x7fffffff;
+        ctl->imin2 = 0x7fffffff;
+    }
+    consumer_sync();
+    if (tid < kk) e[tid] = __ddiv_rn(e[tid], ctl->dsum);
+    consumer_sync();
+    if (tid == 0) {
+        double c = 0.0;
 #pragma unroll 8
-            for (int i = 0; i < kk; ++i) {
-                c = __dadd_rn(c, e[i]);
-                P[i] = c;
-            }
-        }
-    } else {
-        // lane l owns the contiguous block [l * per, l * per + per) of the candidates
-        const int per = (kk + 31) >> 5;
-        const int b0 = lane * per, b1 = min(kk, b0 + per);
-        double part = 0.0;
-        for (int i = b0; i < b1; ++i) part += e[i];
-        double inc = part;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const double t = __shfl_up_sync(0xffffffffu, inc, d);
-            if (lane >= d) inc += t;
-        }
-        s = __shfl_sync(0xffffffffu, inc, 31);
-        part = 0.0;
-        for (int i = b0; i < b1; ++i) {
-            e[i] = __ddiv_rn(e[i], s);
-            part += e[i];
-        }
-        inc = part;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const double t = __shfl_up_sync(0xffffffffu, inc, d);
-            if (lane >= d) inc += t;
-        }
-        double c = inc - part;
-        for (int i = b0; i < b1; ++i) {
-            c += e[i];
+        for (int i = 0; i < kk; ++i) {
+            c = __dadd_rn(c, e[i]);
             P[i] = c;
         }
     }
-    __syncwarp();
-    // keep = 1 + last index whose probability is not below pr[0] * min_p   (src/sampler.cpp:43)
-    int keep = kk;
-    if (r.min_p > 0.0f) {
+    consumer_sync();
+    const double pr = tid < kk ? e[tid] : 0.0;
+    if (r.min_p > 0.0f && tid < kk) {   // keep = 1 + last index whose probability is not below pr[0] * min_p
         const double thr = __dmul_rn(e[0], (double)r.min_p);
-        int last = 0;
-        for (int i = lane; i < kk; i += 32)
-            if (!(e[i] < thr)) last = i;
-        keep = __reduce_max_sync(0xffffffffu, last) + 1;
+        if (!(pr < thr)) atomicMax(&ctl->imax, tid);
     }
-    if (r.top_p < 1.0f) {   // shortest prefix whose cumulative probability reaches top_p, crossing element included (:44)
-        int first = 0x7fffffff;
-        for (int i = lane; i < keep; i += 32)
-            if (P[i] >= (double)r.top_p) {
-                first = i;
-                break;
-            }
-        first = __reduce_min_sync(0xffffffffu, first);
-        if (first != 0x7fffffff && first + 1 < keep) keep = first + 1;
+    consumer_sync();
+    int keep = kk;
+    if (r.min_p > 0.0f) keep = ctl->imax + 1;
+    if (r.top_p < 1.0f) {   // shortest prefix whose cumulative probability reaches top_p, crossing element included
+        if (tid < keep && P[tid] >= (double)r.top_p) atomicMin(&ctl->imin1, tid);
+        consumer_sync();
+        const int i1 = ctl->imin1;
+        if (i1 != 0x7fffffff && i1 + 1 < keep) keep = i1 + 1;
     }
     const double tot = P[keep - 1];
-    // one engine output -> U[0,1) as libstdc++ does it, then r = u * tot + 0.0   (:45-47)
+    // one engine output -> U[0,1) as libstdc++ does it, then r = u * tot + 0.0
     double u = __dmul_rn(__ull2double_rn(r.rng_word), 5.42101086242752217003726400434970855712890625e-20);   // 2^-64
     if (u >= 1.0) u = __longlong_as_double(0x3FEFFFFFFFFFFFFFll);
     const double rr = __dadd_rn(__dmul_rn(u, tot), 0.0);
-    int pick = 0x7fffffff;
-    for (int i = lane; i < keep; i += 32)
-        if (rr <= P[i]) {
-            pick = i;
-            break;
-        }
-    pick = __reduce_min_sync(0xffffffffu, pick);
-    if (pick == 0x7fffffff) pick = keep - 1;
-    if (lane == 0) o.tokens[r.out_index] = comp_id(srt[pick]);
+    if (tid < keep && rr <= P[tid]) atomicMin(&ctl->imin2, tid);
+    consumer_sync();
+    const int i2 = ctl->imin2;
+    const int pick = (i2 != 0x7fffffff) ? i2 : keep - 1;
+    if (tid == 0) o.tokens[r.out_index] = comp_id(srt[pick]);
     if (o.kept_n) {
-        for (int i = lane; i < keep; i += 32) {
-            o.kept_ids[(size_t)r.out_index * kMaxK + i] = comp_id(srt[i]);
-            o.kept_pr[(size_t)r.out_index * kMaxK + i] = e[i];
+        if (tid < keep) {
+            o.kept_ids[(size_t)r.out_index * kMaxK + tid] = comp_id(srt[tid]);
+            o.kept_pr[(size_t)r.out_index * kMaxK + tid] = e[tid];
         }
-        if (lane == 0) o.kept_n[r.out_index] = keep;
+        if (tid == 0) o.kept_n[r.out_index] = keep;
     }
+    consumer_sync();
 }
 
 }  // namespace fsb

@@ -19,14 +19,10 @@
 
 #include "../../include/ferro_sampler_b200.h"
 #include "fsb_internal.h"
-#include "fsb_pairs_internal.h"
 
 static_assert(sizeof(ferro_sampler_params) == 40, "parameter struct must match the reference's 40-byte SamplerParams");
 static_assert(offsetof(ferro_sampler_params, seed) == 32, "seed sits at offset 32 in the reference struct");
-static_assert(FSB_MAX_CANDIDATE_K == fsb::kMaxK && fsb::kMaxK == fsb_pairs::kMaxK, "header constant out of step with the kernel geometry");
-static_assert(sizeof(fsb::RowDesc) == sizeof(fsb_pairs::RowDesc) && offsetof(fsb::RowDesc, out_index) == offsetof(fsb_pairs::RowDesc, out_index),
-              "both streaming kernels read the same descriptor array");
-static_assert(fsb_pairs::kMergeCap <= fsb::kRowScratch, "a row's scratch serves either kernel");
+static_assert(FSB_MAX_CANDIDATE_K == fsb::kMaxK, "header constant out of step with the kernel geometry");
 
 namespace {
 
@@ -44,11 +40,6 @@ struct Stream {
     int64_t dev_len = 0;
 };
 
-struct Plan {
-    int tiles_per_row = 0, n_chunks = 0, grid = 0, slot_cap = 0;
-    uint8_t chunk_len[fsb::kMaxChunks] = {};
-};
-
 }  // namespace
 
 struct fsb_batch {
@@ -59,9 +50,7 @@ struct fsb_batch {
     int64_t cap_hist = 0;
     int n_cand = 0, n_full = 0;   // rows of the candidate kernel / of the full-row kernel
     int kmax = 1;
-    Plan plan;                    // the persistent kernel's schedule
-    fsb_pairs::Plan pplan;        // the static-plan kernel's
-    bool use_pairs = true;        // which of the two streaming kernels samples the candidate rows
+    fsb::Plan plan;               // how the candidate rows are dealt to the CTAs of the streaming kernel
     int64_t hist_ids = 0;         // window ids staged with the batch
     int64_t gather_ids = 0;       // window values a write-back for a host caller brings back
     int64_t table_ints = 0;       // int32 words of the per-stream table of a resident verification call, staged behind the window ids
@@ -92,7 +81,7 @@ struct fsb_handle {
     int device = 0;
     int max_rows = 0, max_vocab = 0;
     int64_t max_hist = 0;
-    int sm_count = 0, ctas_per_sm = 0, pairs_ctas_per_sm = 0;
+    int sm_count = 0, ctas_per_sm = 0;
     int pair_ok = 1;                   // clusters of CTAs can be launched on this device
     cudaStream_t stream = nullptr;
     bool own_stream = false;
@@ -102,13 +91,11 @@ struct fsb_handle {
     int32_t vocab_offset = 0;
     int32_t global_vocab = 0;          // vocabulary sharding: columns of the whole row (0: this engine holds whole rows)
     int launch_overlap = 0;
-    int scan_sums = 0;
     std::vector<Stream> streams;
     std::vector<int> free_ids;
     // device scratch shared by all batches of this handle
-    uint64_t* d_scratch = nullptr;     // [max_rows][kRowScratch] published candidates
-    uint64_t* d_pools = nullptr;       // [CTAs][16][kPoolCap] overflow pools of the streaming kernel's warps
-    uint32_t* d_counters = nullptr;    // [max_rows] tickets, [max_rows] row bounds, [kCounterWords] work counters: all zero between launches
+    uint64_t* d_scratch = nullptr;     // [max_rows][kMergeCap] candidates the segments of a row publish
+    uint32_t* d_counters = nullptr;    // [max_rows] tickets: all zero between launches
     int32_t* d_kept_ids = nullptr;
     double* d_kept_pr = nullptr;
     int32_t* d_kept_n = nullptr;
@@ -123,7 +110,7 @@ struct fsb_handle {
     fsb_counters_t counters{};
     std::string err;
 
-    size_t counter_words() const { return 2 * (size_t)max_rows + fsb::kCounterWords; }
+    size_t counter_words() const { return (size_t)max_rows; }
 };
 
 namespace {
@@ -154,55 +141,6 @@ int64_t window_begin(const ferro_sampler_params& p, int64_t len) {
     int64_t b = (p.repeat_last_n > 0 && (int64_t)p.repeat_last_n < len) ? len - (int64_t)p.repeat_last_n : 0;
     if (p.penalty_from > 0) b = std::max<int64_t>(b, (int64_t)p.penalty_from);
     return std::min(b, len);
-}
-
-// The launch plan of the candidate rows of a batch: the chunk schedule and the grid.  FSB_PLAN in the environment
-// ("5,5,5,4,4,4,3,1,1": tiles per chunk, summing to the row's tiles) overrides the schedule - a tuning aid of the
-// benchmark, never needed for correct results.
-Plan make_plan(const fsb_handle* h, int n_rows, int n_vocab, int kmax) {
-    Plan pl;
-    const int T = (n_vocab + fsb::kTile - 1) / fsb::kTile;
-    pl.tiles_per_row = T;
-    const int slots = std::max(1, h->sm_count * std::max(1, h->ctas_per_sm));
-    pl.n_chunks = fsb::plan_chunks(n_rows, n_vocab, kmax, slots, fsb::kGatherCap, fsb::kMaxChunks, pl.chunk_len, &pl.slot_cap);
-    if (const char* env = std::getenv("FSB_PLAN")) {
-        uint8_t tmp[fsb::kMaxChunks];
-        int n = 0, sum = 0;
-        bool ok = true;
-        for (const char* s = env; *s && ok;) {
-            char* end = nullptr;
-            const long v = std::strtol(s, &end, 10);
-            if (end == s || v < 1 || v > fsb::kItemTilesMax || n >= fsb::kMaxChunks) ok = false;
-            else {
-                tmp[n++] = (uint8_t)v;
-                sum += (int)v;
-                s = (*end == ',') ? end + 1 : end;
-                if (*end && *end != ',') ok = false;
-            }
-        }
-        if (ok && sum == T && fsb::kGatherCap / n >= std::max(1, kmax)) {
-            pl.n_chunks = n;
-            pl.slot_cap = fsb::kGatherCap / n;
-            std::memcpy(pl.chunk_len, tmp, (size_t)n);
-        }
-    }
-    pl.grid = (int)std::min<int64_t>((int64_t)n_rows * pl.n_chunks, slots);
-    return pl;
-}
-
-// Which streaming kernel samples a batch's candidate rows.  The static-plan kernel (one segment per CTA, a row's
-// CTAs exchange candidates on chip) has the shorter end of a launch: it takes the batches that are one wave of CTAs.
-// The persistent kernel (work items drawn from a counter, row ends overlapped with streaming) takes batches of many
-// rows.  FSB_KERNEL=pairs|persistent in the environment forces one - a tuning aid of the benchmark.
-bool choose_pairs_kernel(const fsb_handle* h, int n_rows, int n_vocab) {
-    if (const char* env = std::getenv("FSB_KERNEL")) {
-        if (std::strcmp(env, "pairs") == 0) return true;
-        if (std::strcmp(env, "persistent") == 0) return false;
-    }
-    (void)h;
-    (void)n_rows;
-    (void)n_vocab;
-    return true;
 }
 
 void free_batch_buffers(fsb_batch* b) {
@@ -286,10 +224,7 @@ int finalize_batch(fsb_handle* h, fsb_batch* b) {
     b->n_cand = n_cand;
     b->n_full = n_full;
     b->kmax = kmax;
-    b->plan = make_plan(h, std::max(n_cand, 1), b->n_vocab, kmax);
-    b->pplan = fsb_pairs::make_plan(std::max(n_cand, 1), b->n_vocab, kmax, std::max(1, h->sm_count * std::max(1, h->pairs_ctas_per_sm)));
-    b->use_pairs = choose_pairs_kernel(h, std::max(n_cand, 1), b->n_vocab);
-    if (n_cand > 0 && !b->use_pairs && b->plan.n_chunks <= 0) return fail(h, FSB_ERR_CAPACITY, "rows of %d logits cannot be scheduled with k = %d", b->n_vocab, kmax);
+    b->plan = fsb::make_plan(std::max(n_cand, 1), b->n_vocab, kmax, std::max(1, h->sm_count * std::max(1, h->ctas_per_sm)));
     return FSB_OK;
 }
 
@@ -299,7 +234,7 @@ int upload_batch(fsb_handle* h, fsb_batch* b) {
 }
 
 int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep_kept, uint64_t* shard_out = nullptr,
-                 int32_t* shard_n = nullptr) {
+                 int32_t* shard_n = nullptr, int shard_stride = fsb::kMaxK) {
     if (shard_out && b->n_full > 0)
         return fail(h, FSB_ERR_RANGE, "rows whose candidate count exceeds %d (top_k = 0 or large) cannot be sharded by vocabulary", fsb::kMaxK);
     const int32_t* hist = b->hist_dev ? b->hist_dev : b->d_hist();
@@ -320,10 +255,10 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         h->counters.kernel_launches++;
         if (side_by_side) FSB_CUDA(h, cudaEventRecord(h->ev_join, h->side));
     }
-    if (b->n_cand > 0 && b->use_pairs) {
-        fsb_pairs::StreamArgs a{};
+    if (b->n_cand > 0) {
+        fsb::StreamArgs a{};
         a.logits = logits_dev;
-        a.rows = reinterpret_cast<const fsb_pairs::RowDesc*>(b->d_rows());
+        a.rows = b->d_rows();
         a.hist = hist;
         a.scratch = h->d_scratch;
         a.ticket = h->d_counters;
@@ -334,13 +269,14 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.kept_n = keep_kept ? h->d_kept_n : nullptr;
         a.shard_out = shard_out;
         a.shard_n = shard_n;
+        a.shard_stride = shard_stride;
         a.trace = h->d_trace;
         a.row_ld = (b->n_full == 0) ? b->ld : -1;   // descriptors are in row order when every row takes this kernel
         a.n_rows = b->n_cand;
         a.n_vocab = b->n_vocab;
-        a.tiles_per_row = b->pplan.tiles_per_row;
-        a.tiles_per_cta = b->pplan.tiles_per_cta;
-        a.total_tiles = b->n_cand * b->pplan.tiles_per_row;
+        a.tiles_per_row = b->plan.tiles_per_row;
+        a.tiles_per_cta = b->plan.tiles_per_cta;
+        a.total_tiles = b->n_cand * b->plan.tiles_per_row;
         a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (b->ld & 3) == 0) ? 1 : 0;
         a.write_back = (b->flags & FSB_WRITE_BACK) ? 1 : 0;
         a.vocab_offset = h->vocab_offset;
@@ -351,45 +287,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.pair = 0;
         for (int c = 2; c <= 8; c *= 2)   // receive buffer: (c - 1) lists of kmax entries in 512
             if (h->pair_ok && a.tiles_per_row == c * a.tiles_per_cta && grid == c * a.n_rows && (c - 1) * b->kmax <= 512) a.pair = c;
-        const int e = fsb_pairs::launch_stream_kernel(a, grid, h->stream);
-        if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
-        h->counters.kernel_launches++;
-    } else if (b->n_cand > 0) {
-        fsb::StreamArgs a{};
-        a.logits = logits_dev;
-        a.rows = b->d_rows();
-        a.hist = hist;
-        a.scratch = h->d_scratch;
-        a.scratch_stride = fsb::kRowScratch;
-        a.ticket = h->d_counters;
-        a.row_bound = h->d_counters + h->max_rows;
-        a.work = h->d_counters + 2 * (size_t)h->max_rows;
-        a.tokens = b->d_tokens;
-        a.status = b->d_status();
-        a.kept_ids = keep_kept ? h->d_kept_ids : nullptr;
-        a.kept_pr = keep_kept ? h->d_kept_pr : nullptr;
-        a.kept_n = keep_kept ? h->d_kept_n : nullptr;
-        a.shard_out = shard_out;
-        a.shard_n = shard_n;
-        a.trace = h->d_trace;
-        a.row_ld = (b->n_full == 0) ? b->ld : -1;   // descriptors are in row order when every row takes this kernel
-        a.n_rows = b->n_cand;
-        a.n_vocab = b->n_vocab;
-        a.tiles_per_row = b->plan.tiles_per_row;
-        a.n_chunks = b->plan.n_chunks;
-        a.n_items = b->n_cand * b->plan.n_chunks;
-        a.slot_cap = b->plan.slot_cap;
-        a.pools = h->d_pools;
-        a.pool_cap = fsb::kPoolCap;
-        std::memcpy(a.chunk_len, b->plan.chunk_len, sizeof a.chunk_len);
-        a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (b->ld & 3) == 0) ? 1 : 0;
-        a.write_back = (b->flags & FSB_WRITE_BACK) ? 1 : 0;
-        a.vocab_offset = h->vocab_offset;
-        a.softcap = h->softcap;
-        a.overlap = h->launch_overlap;
-        a.scan_sums = h->scan_sums;
-        if (const char* dbg = std::getenv("FSB_DEBUG")) a.debug = std::atoi(dbg);
-        const int e = fsb::launch_stream_kernel(a, b->plan.grid, h->stream);
+        const int e = fsb::launch_stream_kernel(a, grid, h->stream);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "stream kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         h->counters.kernel_launches++;
     }
@@ -669,7 +567,7 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
     if (prop.major < 10) return bail(FSB_ERR_NO_DEVICE);   // kernels are built for sm_100a only
     h->sm_count = prop.multiProcessorCount;
     if (fsb::prepare_device_kernels(&h->ctas_per_sm) != 0 || h->ctas_per_sm <= 0) return bail(FSB_ERR_CUDA);
-    if (fsb_pairs::prepare_device_kernels(&h->pairs_ctas_per_sm) != 0 || h->pairs_ctas_per_sm <= 0) return bail(FSB_ERR_CUDA);
+    if (fsb::prepare_support_kernels() != 0) return bail(FSB_ERR_CUDA);
     if (fsb::prepare_full_row_kernel(max_vocab) != 0) return bail(FSB_ERR_CUDA);
     if (cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess) return bail(FSB_ERR_CUDA);
     h->own_stream = true;
@@ -680,8 +578,7 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
     // Everything a call may need is allocated here, so that no call allocates: the rows' scratch, the counters, the
     // kept-set record, the id pool and the staging area of host logits.
     h->logits_stage_elems = (size_t)max_rows * (size_t)max_vocab;
-    if (cudaMalloc(reinterpret_cast<void**>(&h->d_scratch), sizeof(uint64_t) * (size_t)max_rows * fsb::kRowScratch) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&h->d_pools), sizeof(uint64_t) * (size_t)h->sm_count * h->ctas_per_sm * (fsb::kThreads / 32) * fsb::kPoolCap) != cudaSuccess ||
+    if (cudaMalloc(reinterpret_cast<void**>(&h->d_scratch), sizeof(uint64_t) * (size_t)max_rows * fsb::kMergeCap) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_counters), sizeof(uint32_t) * h->counter_words()) != cudaSuccess ||
         cudaMemset(h->d_counters, 0, sizeof(uint32_t) * h->counter_words()) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_ids), sizeof(int32_t) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
@@ -705,7 +602,6 @@ int fsb_destroy(fsb_handle* h) {
     }
     if (h->d_scratch) cudaFree(h->d_scratch);
     if (h->d_counters) cudaFree(h->d_counters);
-    if (h->d_pools) cudaFree(h->d_pools);
     if (h->d_kept_ids) cudaFree(h->d_kept_ids);
     if (h->d_kept_pr) cudaFree(h->d_kept_pr);
     if (h->d_kept_n) cudaFree(h->d_kept_n);
@@ -747,12 +643,6 @@ int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer) {
 int fsb_set_launch_overlap(fsb_handle* h, int on) {
     if (!h) return FSB_ERR_INVALID;
     h->launch_overlap = on ? 1 : 0;
-    return FSB_OK;
-}
-
-int fsb_set_scan_sums(fsb_handle* h, int on) {
-    if (!h) return FSB_ERR_INVALID;
-    h->scan_sums = on ? 1 : 0;
     return FSB_OK;
 }
 
@@ -1210,12 +1100,46 @@ int fsb_batch_merge_launch(fsb_handle* h, fsb_batch* b, const uint64_t* lists_de
     cudaSetDevice(h->device);
     const bool keep_kept = (b->flags & FSB_KEEP_KEPT_SET) != 0;
     const int e = fsb::launch_merge_lists(lists_dev, counts_dev, n_lists, fsb::kMaxK, b->n_cand, b->d_rows(), b->d_tokens, keep_kept ? h->d_kept_ids : nullptr,
-                                          keep_kept ? h->d_kept_pr : nullptr, keep_kept ? h->d_kept_n : nullptr, b->d_status(), h->scan_sums, h->stream);
+                                          keep_kept ? h->d_kept_pr : nullptr, keep_kept ? h->d_kept_n : nullptr, b->d_status(), h->stream);
     if (e != 0) return fail(h, FSB_ERR_CUDA, "merge kernel launch: %s", cudaGetErrorString((cudaError_t)e));
     h->counters.kernel_launches++;
     b->launched = true;
     h->kept_valid = keep_kept;
     return FSB_OK;
+}
+int fsb_batch_max_k(const fsb_batch* b) { return b ? b->kmax : 0; }
+int fsb_batch_shard_launch_packed(fsb_handle* h, fsb_batch* b, const float* logits_shard_dev, uint64_t* packed_out_dev, int32_t stride_words) {
+    if (!h || !b || !logits_shard_dev || !packed_out_dev) return FSB_ERR_INVALID;
+    if (stride_words < b->kmax + 1) return fail(h, FSB_ERR_RANGE, "a packed list needs %d words (1 + the batch's largest k), got %d", b->kmax + 1, stride_words);
+    cudaSetDevice(h->device);
+    return launch_batch(h, b, logits_shard_dev, false, packed_out_dev, nullptr, stride_words);
+}
+int fsb_batch_merge_launch_packed(fsb_handle* h, fsb_batch* b, const uint64_t* packed_dev, int32_t stride_words, int n_lists, int32_t row_begin,
+                                  int32_t n_rows) {
+    if (!h || !b || (!packed_dev && n_rows > 0)) return FSB_ERR_INVALID;   // a rank whose block of rows is empty has nothing to pass
+    if (b->n_full > 0) return fail(h, FSB_ERR_RANGE, "the batch has rows that cannot be sharded by vocabulary");
+    if (stride_words < 2 || n_lists < 1 || (int64_t)n_lists * std::min(fsb::kMaxK, stride_words - 1) > fsb::kMergeCap)
+        return fail(h, FSB_ERR_RANGE, "%d lists of %d words exceed the %d candidates a row can merge", n_lists, stride_words, fsb::kMergeCap);
+    if (row_begin < 0 || n_rows < 0 || row_begin + n_rows > b->n_cand) return fail(h, FSB_ERR_RANGE, "rows %d..%d are not rows of the batch", row_begin, row_begin + n_rows);
+    cudaSetDevice(h->device);
+    const bool keep_kept = (b->flags & FSB_KEEP_KEPT_SET) != 0;
+    if (n_rows > 0) {
+        const int e = fsb::launch_merge_lists(packed_dev, nullptr, n_lists, stride_words, n_rows, b->d_rows() + row_begin, b->d_tokens,
+                                              keep_kept ? h->d_kept_ids : nullptr, keep_kept ? h->d_kept_pr : nullptr, keep_kept ? h->d_kept_n : nullptr,
+                                              b->d_status(), h->stream);
+        if (e != 0) return fail(h, FSB_ERR_CUDA, "merge kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+        h->counters.kernel_launches++;
+    }
+    b->launched = true;
+    h->kept_valid = keep_kept && row_begin == 0 && n_rows == b->n_cand;
+    return FSB_OK;
+}
+int32_t* fsb_batch_tokens_device(fsb_batch* b) { return b ? b->d_tokens : nullptr; }
+int fsb_batch_check(fsb_handle* h, fsb_batch* b) {
+    if (!h || !b) return FSB_ERR_INVALID;
+    if (!b->launched) return fail(h, FSB_ERR_INVALID, "the batch has not been launched");
+    cudaSetDevice(h->device);
+    return fetch_tokens(h, b, nullptr);
 }
 int fsb_batch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out) {
     if (!h || !b || !tokens_out) return FSB_ERR_INVALID;

@@ -1,4 +1,4 @@
-// fsb_pairs.cu - the static-plan streaming candidate kernel of the B200 batched token sampler (sm_100a).
+// fsb_stream.cu - the static-plan streaming candidate kernel of the B200 batched token sampler (sm_100a).
 //
 // One launch samples every row of a batch whose effective k is at most kMaxK (greedy rows are k = 1):
 //   repetition penalty (src/sampler.cpp:11-18) -> greedy argmax (:19-23) or top-k candidates (:25-35)
@@ -10,9 +10,9 @@
 #include "../../include/ferro_sampler_b200.h"
 #include <algorithm>
 
-#include "fsb_pairs_device.cuh"
+#include "fsb_device.cuh"
 
-namespace fsb_pairs {
+namespace fsb {
 namespace {
 
 constexpr int kWarps = kThreads / 32;
@@ -510,7 +510,7 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
     const int T = a.tiles_per_row, V = a.n_vocab, Q = a.tiles_per_cta;
     const RowDesc d = a.rows[row];
     unsigned* myq = m.queue + tid;
-    const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.status};
+    const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.shard_stride, a.status};
     float thr_final;
     int n_el;
     for (;;) {
@@ -982,12 +982,12 @@ Plan make_plan(int n_rows, int n_vocab, int kmax, int slots) {
     return pl;
 }
 
-}  // namespace fsb_pairs
+}  // namespace fsb
 
 // ---------------------------------------------------------------------------------------------- fsb_argmax_rows_static
 // Greedy tokens of device-resident rows with no allocation at all: the streaming kernel above, run with every piece
 // of device memory it needs taken from one array that is part of this library's image.
-namespace fsb_pairs {
+namespace fsb {
 namespace {
 
 constexpr int kStaticMaxRows = FSB_STATIC_MAX_ROWS;
@@ -1027,11 +1027,11 @@ __global__ void static_greedy_rows_kernel(RowDesc* rows, int n_rows, int64_t ld,
 }
 
 }  // namespace
-}  // namespace fsb_pairs
+}  // namespace fsb
 
 extern "C" int fsb_argmax_rows_static(int device, const float* logits_dev, int64_t ld, int n_rows, int n_vocab, int32_t* tokens_dev,
                                       void* cuda_stream, unsigned flags) {
-    using namespace fsb_pairs;
+    using namespace fsb;
     if (!logits_dev || !tokens_dev || n_rows < 0 || n_vocab <= 0 || ld < n_vocab || (flags & ~FSB_STATIC_WAIT)) return FSB_ERR_INVALID;
     if (n_rows > kStaticMaxRows) return FSB_ERR_CAPACITY;   // the static array holds FSB_STATIC_MAX_ROWS rows of scratch, no more
     if (device < 0 || device >= kStaticMaxDevices) return FSB_ERR_NO_DEVICE;

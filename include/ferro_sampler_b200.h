@@ -102,14 +102,6 @@ FSB_API int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer);
  * read anything, so they gain nothing.  No reference counterpart. */
 FSB_API int fsb_set_launch_overlap(fsb_handle* h, int on);
 
-/* Epilogue sums (off by default).  The reference adds the candidates' probabilities one after the other in
- * candidate order (src/sampler.cpp:41,44,46); by default one thread does the same, so the sums carry the reference's
- * own rounding.  When on, the two sums of a row are warp prefix scans: a few hundred nanoseconds faster per row, the
- * probabilities differ from the reference's in the last bits (~1e-16, against the 1e-6 the parity contract allows), and
- * a draw can differ only if its uniform lands that close to a boundary of the cumulative distribution.
- * No reference counterpart. */
-FSB_API int fsb_set_scan_sums(fsb_handle* h, int on);
-
 /* Column offset of this device's vocabulary shard: local column c is token id c + offset (vocab sharding).
  * fsb_set_vocab_shard also tells the engine how many columns the whole row has, so that a row's candidate count
  * follows the whole row (k = (0 < top_k < global_vocab) ? top_k : global_vocab, src/sampler.cpp:27) even when top_k
@@ -252,6 +244,20 @@ FSB_API int fsb_batch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out);
 FSB_API int fsb_batch_shard_launch(fsb_handle* h, fsb_batch* b, const float* logits_shard_dev, uint64_t* lists_out_dev,
                                    int32_t* counts_out_dev);
 FSB_API int fsb_batch_merge_launch(fsb_handle* h, fsb_batch* b, const uint64_t* lists_dev, const int32_t* counts_dev, int n_lists);
+/* The same two steps with packed lists, for exchanges that should move no more than they must: a row's list is
+ * `stride_words` 64-bit words - word 0 its length, words 1 .. length its candidates in descending order - with
+ * stride_words >= 1 + fsb_batch_max_k(b) (the largest candidate count of the staged rows on this shard), so a rank
+ * sends rows x stride_words x 8 bytes in one piece, counts included.  fsb_batch_merge_launch_packed finishes rows
+ * [row_begin, row_begin + n_rows) of the batch from `packed_dev` = [n_lists][n_rows][stride_words]: with an
+ * all-to-all that brings every rank the lists of its own block of rows, each rank merges only that block and the
+ * tokens are exchanged afterwards (fsb_batch_tokens_device gives the device array, [rows] int32 indexed by row;
+ * fsb_batch_check waits for the launches and reports the device status without copying tokens to the caller). */
+FSB_API int fsb_batch_max_k(const fsb_batch* b);
+FSB_API int fsb_batch_shard_launch_packed(fsb_handle* h, fsb_batch* b, const float* logits_shard_dev, uint64_t* packed_out_dev, int32_t stride_words);
+FSB_API int fsb_batch_merge_launch_packed(fsb_handle* h, fsb_batch* b, const uint64_t* packed_dev, int32_t stride_words, int n_lists,
+                                          int32_t row_begin, int32_t n_rows);
+FSB_API int32_t* fsb_batch_tokens_device(fsb_batch* b);
+FSB_API int fsb_batch_check(fsb_handle* h, fsb_batch* b);
 /* Number of kernels one fsb_batch_launch enqueues (for launch accounting). */
 FSB_API int fsb_batch_kernel_count(const fsb_batch* b);
 FSB_API int fsb_batch_free(fsb_handle* h, fsb_batch* b);

@@ -56,11 +56,15 @@ def _rank_main(rank, world, port, B, V, k, out_dir):
         rng = np.random.default_rng(5)                   # the same matrix on every rank; each uses its own columns
         lg = (np.round(rng.standard_normal((B, V)) * 4) / 2).astype(np.float32)   # many ties across shards
         lo, hi = sharded.vocab_partition(V, world)[rank]
+        # the bare lists with separate counts (all-gather of both) ...
         lists = np.zeros((B, sharded.MAX_K), dtype=np.uint64)
         counts = np.zeros(B, dtype=np.int32)
+        # ... and the packed ones: [count, candidates ...] in k + 1 words per row
+        packed = np.zeros((B, k + 1), dtype=np.uint64)
         for r in range(B):
             keys = np.sort(sharded.pack_candidates(lg[r, lo:hi], np.arange(lo, hi)))[::-1][:k]
             lists[r, : len(keys)], counts[r] = keys, len(keys)
+            packed[r, 0], packed[r, 1: 1 + len(keys)] = len(keys), keys
         al, ac = sharded.gather_candidate_lists(torch.from_numpy(lists.view(np.int64)), torch.from_numpy(counts))
         al, ac = al.numpy().view(np.uint64), ac.numpy()
         assert al.shape == (world, B, sharded.MAX_K) and ac.shape == (world, B)
@@ -71,6 +75,24 @@ def _rank_main(rank, world, port, B, V, k, out_dir):
         toks = sharded.gather_tokens(merged[sharded.row_partition(B, world)[rank][0]: sharded.row_partition(B, world)[rank][1], 0])
         np.save(os.path.join(out_dir, f"merged{rank}.npy"), merged)
         np.save(os.path.join(out_dir, f"tokens{rank}.npy"), toks)
+
+        def merge(lists3, n_rows):   # what the merge kernel does with [world][n_rows][k + 1]
+            out = np.zeros((n_rows, k), dtype=np.int64)
+            for r in range(n_rows):
+                keys = np.concatenate([lists3[g, r, 1: 1 + int(lists3[g, r, 0])] for g in range(world)])
+                out[r] = sharded.unpack_candidates(np.sort(keys)[::-1][:k])[1]
+            return out
+
+        tp = torch.from_numpy(packed.view(np.int64))
+        l3, b0, n = sharded.exchange_packed_lists(tp, rank, world, "all_gather")
+        assert (b0, n) == (0, B) and np.array_equal(merge(l3.numpy().view(np.uint64), n), merged)
+        l3, b0, n = sharded.exchange_packed_lists(tp, rank, world, "all_to_all")
+        assert (b0, b0 + n) == sharded.row_partition(B, world)[rank] and tuple(l3.shape) == (world, n, k + 1)
+        mine = merge(l3.numpy().view(np.uint64), n)
+        assert np.array_equal(mine, merged[b0: b0 + n])
+        tok = torch.zeros(B, dtype=torch.int32)
+        tok[b0: b0 + n] = torch.from_numpy(mine[:, 0].astype(np.int32))
+        np.save(os.path.join(out_dir, f"blocktokens{rank}.npy"), sharded.exchange_block_tokens(tok, rank, world).numpy())
     finally:
         dist.destroy_process_group()
 
@@ -78,7 +100,7 @@ def _rank_main(rank, world, port, B, V, k, out_dir):
 def test_two_ranks_exchange_candidates_and_agree_with_the_oracle(oracle, tmp_path):
     import torch.multiprocessing as mp
     from oracle import make_params
-    B, V, k, world = 6, 4099, 40, 2
+    B, V, k, world = 7, 4099, 40, 2                                   # an odd number of rows: unequal blocks
     mp.spawn(_rank_main, args=(world, _free_port(), B, V, k, str(tmp_path)), nprocs=world, join=True)
     rng = np.random.default_rng(5)
     lg = (np.round(rng.standard_normal((B, V)) * 4) / 2).astype(np.float32)
@@ -90,3 +112,5 @@ def test_two_ranks_exchange_candidates_and_agree_with_the_oracle(oracle, tmp_pat
     assert np.array_equal(m0, ref["kept_ids"][:, :k].astype(np.int64))  # and they are the reference's, in its order
     t0 = np.load(tmp_path / "tokens0.npy")
     assert np.array_equal(t0, np.load(tmp_path / "tokens1.npy")) and np.array_equal(t0, m0[:, 0].astype(np.int32))
+    for r in range(world):                                             # the all-to-all route ends with the same tokens on every rank
+        assert np.array_equal(np.load(tmp_path / f"blocktokens{r}.npy"), t0)

@@ -60,6 +60,63 @@ def test_sharded_candidates_merge_to_the_unsharded_result(engine, oracle, shape)
             engine.close_stream(int(s))
 
 
+@pytest.mark.parametrize("shape", [(16, 262144, 8, 40), (9, 70001, 3, 64), (5, 1000, 8, 200), (7, 4096, 2, 256)])
+def test_packed_lists_merged_block_by_block_match_the_oracle(oracle, shape):
+    """The all-to-all route on one GPU: G engines write packed lists; "rank" q merges only its block of rows from
+    the G lists of that block.  (5, 1000, 8, 200): top_k exceeds a shard's 125 columns, so a shard's list is its
+    whole slice and the merged row still keeps the row-wide 200."""
+    import torch
+    B, V, G, k = shape
+    rng = np.random.default_rng(77 + G)
+    lg = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+    lg[:, ::5] = np.round(lg[:, ::5])
+    p = fb.make_params(B, temperature=0.9, top_k=k, top_p=0.95, min_p=0.01, repetition_penalty=1.2)
+    p["temperature"][::3] = 0.0
+    p["seed"] = 800 + np.arange(B)
+    hists = [rng.integers(0, V, size=100).astype(np.int32) for _ in range(B)]
+    ref = oracle.sample_rows(p, oracle.new_rngs(p["seed"]), lg.copy(), hists, cap=fb.MAX_CANDIDATE_K)
+    dev = torch.from_numpy(lg).cuda()
+    parts = sharded.vocab_partition(V, G)
+    engines, batches = [], []
+    try:
+        for g, (lo, hi) in enumerate(parts):
+            eng = fb.Engine(device=0, max_rows=B, max_vocab=max(hi - lo, 1), max_hist_ids=B * 100 + 16)
+            engines.append(eng)
+            eng.set_vocab_shard(lo, V)
+            batches.append(eng.prepare_batch(eng.open_streams(p), hists, hi - lo, ld=V, flags=fb.KEEP_KEPT_SET))
+        stride = max(b.max_k for b in batches) + 1
+        assert stride == min(k, max(hi - lo for lo, hi in parts)) + 1
+        packed = torch.zeros((G, B, stride), dtype=torch.int64, device="cuda")
+        for g, (lo, hi) in enumerate(parts):
+            batches[g].shard_launch_packed(dev.data_ptr() + 4 * lo, packed[g].data_ptr(), stride)
+        torch.cuda.synchronize()
+        counts = packed[:, :, 0].cpu().numpy()
+        assert (counts == np.array([[min(k if p["temperature"][r] > 0 else 1, hi - lo) for r in range(B)] for lo, hi in parts])).all()
+        tok = np.zeros(B, dtype=np.int32)
+        for q, (r0, r1) in enumerate(sharded.row_partition(B, G)):
+            lists = packed[:, r0:r1, :].contiguous()
+            batches[q].merge_launch_packed(lists.data_ptr(), stride, G, r0, r1 - r0)
+            batches[q].check()
+            mine = torch.as_tensor(sharded._DeviceInts(batches[q].tokens_device_ptr, B), device="cuda")
+            tok[r0:r1] = mine[r0:r1].cpu().numpy()
+        assert np.array_equal(tok, ref["tokens"])
+        # all rows on one rank (the all-gather route), with the kept sets
+        batches[0].merge_launch_packed(packed.data_ptr(), stride, G, 0, B)
+        assert np.array_equal(batches[0].tokens(), ref["tokens"])
+        for i in range(B):
+            if p["temperature"][i] > 0:
+                ids, pr, n = engines[0].last_kept(i)
+                assert n == ref["n_keep"][i] and np.array_equal(ids, ref["kept_ids"][i, :n])
+                assert np.abs(pr - ref["kept_pr"][i, :n]).max() <= 1e-6
+        with pytest.raises(fb.SamplerError):                       # a list cannot be shorter than the batch's largest k + 1
+            batches[0].shard_launch_packed(dev.data_ptr(), packed[0].data_ptr(), stride - 1)
+    finally:
+        for b in batches:
+            b.free()
+        for eng in engines:
+            eng.close()
+
+
 def test_full_vocabulary_rows_are_refused_by_the_sharded_launch(engine):
     import torch
     p = fb.make_params(2, temperature=1.0, top_k=0)
