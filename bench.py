@@ -370,37 +370,39 @@ def vocab_sharded_leg(torch, dist, fb, device, rank, world, barrier):
         hh = [np.random.default_rng(1000 + r).integers(0, vocab, size=1024).astype(np.int32) for r in range(rows)]
         eng = fb.Engine(device=device.index, max_rows=rows, max_vocab=hi - lo, max_hist_ids=rows * 1024 + 16)
         eng.set_cuda_stream(torch.cuda.current_stream().cuda_stream)
-        samp = sharded.VocabShardedSampler(eng, vocab, rank, world)
-        sids = eng.open_streams(p)
-        samp.prepare(sids, hh, rows)
     except Exception as ex:
         ready = 0
         out["error"] = f"{type(ex).__name__}: {ex}"
     flag = torch.tensor([ready], dtype=torch.int32, device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)                # every rank takes part in the collectives below, or none
     if int(flag.item()) == 1:
-        barrier()
-        us = time_launches(torch, lambda i: samp.step(shard[i % 2]), 30)
-        t = torch.tensor([us], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        samp.step(shard[0])
-        tok = samp.tokens()
-        mine = torch.from_numpy(tok.astype(np.int64)).to(device)
-        allt = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(allt, mine)
-        across = int(sum(int((a != allt[0]).sum().item()) for a in allt[1:]))
-        mism = None
-        if rank == 0:                                            # the unsharded launch over the whole rows
+        want = None
+        if rank == 0:                                            # the unsharded launch over the whole rows: first draw of every stream
             e0 = fb.Engine(device=device.index, max_rows=rows, max_vocab=vocab, max_hist_ids=rows * 1024 + 16)
             e0.set_cuda_stream(torch.cuda.current_stream().cuda_stream)
-            s0 = e0.open_streams(p)
-            want = e0.sample_batch(s0, full[0], hh, n_vocab=vocab)
-            mism = int((want != tok).sum())
+            want = e0.sample_batch(e0.open_streams(p), full[0], hh, n_vocab=vocab)
             e0.close()
-        out = {"step_us": float(t.item()), "rows_per_s": rows / float(t.item()) * 1e6, "columns_per_gpu": hi - lo,
-               "exchange": samp.exchange_description(), "parity_mismatches_across_ranks": across,
-               "parity_mismatches_vs_unsharded": mism}
-        samp.release()
+        for mode in ("all_to_all", "all_gather"):
+            samp = sharded.VocabShardedSampler(eng, vocab, rank, world, exchange=mode)
+            samp.prepare(eng.open_streams(p), hh, rows)
+            for i in range(5):
+                samp.step(shard[i % 2])
+            barrier()
+            us = time_launches(torch, lambda i: samp.step(shard[i % 2]), 30)
+            t = torch.tensor([us], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            samp.prepare(eng.open_streams(p), hh, rows)      # fresh streams: their first draw, as in the unsharded launch
+            samp.step(shard[0])
+            tok = samp.tokens()
+            mine = torch.from_numpy(tok.astype(np.int64)).to(device)
+            allt = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(allt, mine)
+            across = int(sum(int((a != allt[0]).sum().item()) for a in allt[1:]))
+            out[mode] = {"step_us": float(t.item()), "rows_per_s": rows / float(t.item()) * 1e6, "exchange": samp.exchange_description(),
+                         "parity_mismatches_across_ranks": across,
+                         "parity_mismatches_vs_unsharded": int((want != tok).sum()) if want is not None else None}
+            samp.release()
+        out["columns_per_gpu"] = hi - lo
     if eng is not None:
         eng.close()
     return out
@@ -455,7 +457,7 @@ def main():
     kernels_per_step = batch.kernels_per_launch
 
     # ---- the timed steps: a train of launches on one stream, no overlap between them
-    eng.set_launch_overlap(False)
+    eng.set_launch_overlap(0)
     for i in range(args.warmup):
         batch.launch(bufs[i % n_buf].data_ptr())
     barrier()
@@ -474,20 +476,24 @@ def main():
     # parity of a timed batch: the launch on buffer 0 (the configuration's own logits), outside the timed region
     batch.launch(bufs[0].data_ptr())
     tokens = batch.tokens()
-    # the same train with launch overlap on (a launch's first work item may be read while the previous launch is in its
-    # tail): a figure for independent batches, not for the steps of one decode loop
-    eng.set_launch_overlap(True)
-    for i in range(3):
-        batch.launch(bufs[i % n_buf].data_ptr())
-    barrier()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record()
-    for i in range(args.steps):
-        batch.launch(bufs[i % n_buf].data_ptr())
-    s1.record()
-    barrier()
-    ms_overlap = s0.elapsed_time(s1) / args.steps
-    eng.set_launch_overlap(False)
+    # the same train with the launches chained by programmatic stream serialization.  Mode 2: every CTA waits for the
+    # previous launch to be complete before it touches memory - plain stream order, only the launch latency is hidden.
+    # Mode 1: a launch may read logits while the previous one is in its tail - a figure for independent batches.
+    def chained_train(mode):
+        eng.set_launch_overlap(mode)
+        for i in range(3):
+            batch.launch(bufs[i % n_buf].data_ptr())
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for i in range(args.steps):
+            batch.launch(bufs[i % n_buf].data_ptr())
+        s1.record()
+        barrier()
+        eng.set_launch_overlap(0)
+        return s0.elapsed_time(s1) / args.steps
+    ms_hidden = chained_train(2)
+    ms_overlap = chained_train(1)
     # the timed region is short: keep the device busy a little longer so that the clock record has samples under load
     if rank == 0:
         t_busy = time.perf_counter()
@@ -496,10 +502,10 @@ def main():
                 batch.launch(bufs[i % n_buf].data_ptr())
             torch.cuda.synchronize()
     clock_rec = clocks.stop() if rank == 0 else None
-    t = torch.tensor([ms_total, ms_overlap], dtype=torch.float64, device=device)
+    t = torch.tensor([ms_total, ms_overlap, ms_hidden], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_overlap = float(t[0].item()), float(t[1].item())
+    ms_total, ms_overlap, ms_hidden = float(t[0].item()), float(t[1].item()), float(t[2].item())
     ms_step = ms_total / args.steps
 
     # ---- end to end through the public call: pinned host logits in, tokens out, every step
@@ -544,7 +550,7 @@ def main():
     if not args.no_extras:
         extras = {}
         try:
-            eng.set_launch_overlap(False)
+            eng.set_launch_overlap(0)
             for resident in (False, True):   # the whole public call on device-resident logits, as a server makes it every step
                 if resident:
                     for s_, hh_ in zip(sids, hists):
@@ -554,9 +560,6 @@ def main():
                 extras["device_logits_call_us_resident_histories" if resident else "device_logits_call_us"] = time_calls(call, 100)
             extras["staging_h2d_bytes"] = ROWS * 64 + ROWS * HIST * 4
             extras["warm_launch_us"] = time_launches(torch, lambda i: batch.launch(bufs[0].data_ptr()), 100)   # the same 67 MB every launch: mostly L2
-            eng.set_scan_sums(True)
-            extras["launch_us_scan_sums"] = time_launches(torch, lambda i: batch.launch(bufs[i % n_buf].data_ptr()), 100)
-            eng.set_scan_sums(False)
             if rank == 0:
                 extras["configs"] = config_figures(torch, fb, device, peak, tanhf)
         except Exception as ex:   # side figures must never cost the headline line
@@ -583,6 +586,10 @@ def main():
                          "peak_source": peak_src, "algorithmic_bytes_per_launch": bytes_launch, "frac_of_nominal_8000": achieved / 8000.0,
                          "kernel": "stream_select_kernel", "launch_us": ms_step * 1e3,
                          "note": "achieved = algorithmic bytes / duration of one launch in the timed train (no overlap between launches)"},
+            "hidden_launch_latency_train": {"step_us": ms_hidden * 1e3, "rows_per_s": world * ROWS / (ms_hidden * 1e-3),
+                                            "achieved_gb_s": bytes_launch / (ms_hidden * 1e-3) / 1e9, "frac": bytes_launch / (ms_hidden * 1e-3) / 1e9 / peak,
+                                            "note": "fsb_set_launch_overlap(2): every CTA waits for the previous launch to complete before its first "
+                                                    "access; same results and ordering as the plain train"},
             "overlapped_train": {"step_us": ms_overlap * 1e3, "rows_per_s": world * ROWS / (ms_overlap * 1e-3), "achieved_gb_s": overlapped, "frac": overlapped / peak,
                                  "note": "programmatic stream serialization on: independent batches only"},
             "e2e": {"value": world * ROWS * e2e_steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

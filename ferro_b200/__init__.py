@@ -274,9 +274,10 @@ class Engine:
     def set_trace_buffer(self, device_ptr: int):
         self._check(self.lib.fsb_set_trace_buffer(self._h, C.c_void_p(int(device_ptr)) if device_ptr else None))
 
-    def set_launch_overlap(self, on: bool):
-        """Let consecutive launches overlap (see fsb_set_launch_overlap in the C header for when that is safe)."""
-        self._check(self.lib.fsb_set_launch_overlap(self._h, 1 if on else 0))
+    def set_launch_overlap(self, mode):
+        """0 / False: plain stream order; 1 / True: consecutive launches overlap their reads; 2: launch latency hidden,
+        plain-order semantics (see fsb_set_launch_overlap in the C header)."""
+        self._check(self.lib.fsb_set_launch_overlap(self._h, int(mode)))
 
     def set_vocab_offset(self, offset: int):
         self._check(self.lib.fsb_set_vocab_offset(self._h, int(offset)))

@@ -642,7 +642,8 @@ int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer) {
 
 int fsb_set_launch_overlap(fsb_handle* h, int on) {
     if (!h) return FSB_ERR_INVALID;
-    h->launch_overlap = on ? 1 : 0;
+    if (on < 0 || on > 2) return fail(h, FSB_ERR_RANGE, "launch overlap mode is 0, 1 or 2");
+    h->launch_overlap = on;
     return FSB_OK;
 }
 

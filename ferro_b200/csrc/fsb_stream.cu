@@ -107,6 +107,8 @@ __device__ __noinline__ void softcap_tile(float* st, int len, float cap, float* 
 // Repetition penalty on the penalised columns of a warp tile, in place in shared memory (src/sampler.cpp:17).
 // The tile's bits of the segment bitmap are one word per 32 columns; each of the first lanes owns one word and
 // patches the columns whose bits are set.  A bit is set once however often an id occurs in the window.
+// (Patching the lanes' registers after the look's loads instead - four bitmap reads per lane and tile - was measured
+// slower: the loop is bound by instruction issue, and this way most lanes do nothing.)
 __device__ __forceinline__ void patch_tile(float* st, int len, int col0, int seg_lo, float pen, const unsigned* bitmap, float* wb_row) {
     const int lane = threadIdx.x & 31;
     const int nw = (len + 31) >> 5;
@@ -714,11 +716,12 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
     const int t_end = min(t_begin + a.tiles_per_cta, a.total_tiles);
     const int nt = t_end - t_begin;
     // With launch overlap on, the next launch in the stream may start as soon as this one leaves room; like this one
-    // it waits for its predecessor before it writes anything (segment_end), so only the reading of logits overlaps.
+    // it waits for its predecessor before it writes anything (segment_end), so only the reading of logits overlaps -
+    // or, in mode 2, before it does anything at all, so only its placement on the SMs does.
     pdl_launch_dependents();
     if (nt <= 0) return;
     trace_mark(a, 0);
-    if (a.write_back) pdl_wait_prior();   // this launch stores into the logits while it streams
+    if (a.write_back || a.overlap == 2) pdl_wait_prior();   // this launch stores into the logits while it streams, or was asked to wait
 
     if (tid == 0) {   // one thread initialises every barrier, then makes the initialisation visible to the copy engine
         for (int s = 0; s < kStages; ++s) {

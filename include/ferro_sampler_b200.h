@@ -87,19 +87,24 @@ FSB_API int fsb_set_cuda_stream(fsb_handle* h, void* cuda_stream);
  * of src/model_gemma4.cpp:520-521).  cap = 0 turns it off (the default: the caller's logits are final). */
 FSB_API int fsb_set_softcap(fsb_handle* h, float cap);
 
-/* Diagnostics: when set to a device buffer of 16 uint64 per CTA (one CTA per SM at most), the streaming kernel writes
- * %globaltimer time stamps (ns) of its phases there: 0 CTA start, 1 first work item handed over, 2 first tile in
- * shared memory, 4 last tile of an item consumed, 5 the item's candidates gathered, 6 ordered, 7 published and ticket
- * drawn, 8 the row's lists merged, 9 epilogue done (4-9: the CTA's last item that got there), 10 exit; slot 3 = work
- * items the CTA processed.  NULL (the default) turns it off.  No reference counterpart. */
+/* Diagnostics: when set to a device buffer of 8 uint64 per CTA of the streaming kernel (and 64 more words after
+ * the first 4096 x 8 for the full-vocabulary kernel), the kernels write time stamps of their phases there.  The
+ * streaming kernel: word 0 %globaltimer (ns) at the CTA's start and word 7 the SM's cycle counter at the same
+ * moment; words 1, 4, 2, 5, 6 the cycle counter after set-up, after the CTA's last tile, after the candidate list of
+ * its last segment, after ordering / merging, and at the end.  NULL (the default) turns it off.  No reference
+ * counterpart. */
 FSB_API int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer);
 
-/* Overlap of consecutive launches (off by default).  When on, fsb_batch_launch starts the streaming kernel with
- * programmatic stream serialization: its CTAs may begin to read logits while the previous kernel in the stream is
- * still finishing, and every write of the launch (tokens, kept sets, scratch) waits for that kernel to be complete.
- * Turn it on only if the logits of a launch are complete before the previous kernel in the stream starts (for
- * instance logits that alternate between buffers filled well ahead); batches with FSB_WRITE_BACK wait before they
- * read anything, so they gain nothing.  No reference counterpart. */
+/* How consecutive launches follow one another (0, the default: plain stream order).
+ * 1: fsb_batch_launch starts the streaming kernel with programmatic stream serialization and its CTAs may begin to
+ *    read logits while the previous kernel in the stream is still finishing; every write of the launch (tokens, kept
+ *    sets, scratch) waits for that kernel to be complete.  Use it only if the logits of a launch are complete before
+ *    the previous kernel in the stream starts (for instance logits that alternate between buffers filled well ahead);
+ *    batches with FSB_WRITE_BACK wait before they read anything, so they gain nothing.
+ * 2: the same launch attribute, but every CTA waits for the previous kernel to be complete before it reads or writes
+ *    anything.  Results and ordering are those of plain stream order - the logits may be produced by the kernel just
+ *    before - and only the launch latency (CTA placement, barrier set-up) is hidden behind that kernel's end.
+ * No reference counterpart. */
 FSB_API int fsb_set_launch_overlap(fsb_handle* h, int on);
 
 /* Column offset of this device's vocabulary shard: local column c is token id c + offset (vocab sharding).
