@@ -44,7 +44,7 @@ API_SYMBOLS = [
     "fsb_create", "fsb_destroy", "fsb_last_error", "fsb_set_cuda_stream", "fsb_set_softcap", "fsb_set_vocab_offset", "fsb_set_launch_overlap", "fsb_batch_shard_launch", "fsb_batch_merge_launch", "fsb_argmax_rows_static", "fsb_stream_history_set", "fsb_stream_history_append", "fsb_stream_history_len",
     "fsb_sample_batch_resident",
     "fsb_set_trace_buffer", "fsb_set_vocab_shard", "fsb_batch_max_k", "fsb_batch_shard_launch_packed", "fsb_batch_merge_launch_packed",
-    "fsb_batch_tokens_device", "fsb_batch_check", "fsb_verify_windows_resident",
+    "fsb_batch_tokens_device", "fsb_batch_check", "fsb_lookup_drafts_resident", "fsb_verify_windows_resident",
     "fsb_server_defaults_init", "fsb_params_from_request", "fsb_params_apply_cli_flag",
     "fsb_params_default", "fsb_params_validate", "fsb_stream_open", "fsb_stream_close", "fsb_stream_params",
     "fsb_stream_state_get", "fsb_stream_state_set", "fsb_sample_batch", "fsb_verify_windows", "fsb_last_kept",
@@ -123,6 +123,7 @@ def load_library(build_if_missing: bool = True):
     L.fsb_batch_tokens_device.argtypes = [vp]
     L.fsb_batch_tokens_device.restype = vp
     L.fsb_batch_check.argtypes = [vp, vp]
+    L.fsb_lookup_drafts_resident.argtypes = [vp, i32, vp, vp, vp, i32, vp, i32, vp]
     L.fsb_batch_kernel_count.argtypes = [vp]
     L.fsb_batch_free.argtypes = [vp, vp]
     L.fsb_counters.argtypes = [vp, C.POINTER(_Counters)]
@@ -385,6 +386,19 @@ class Engine:
     def history_append(self, stream_id: int, ids):
         a = np.ascontiguousarray(np.atleast_1d(ids), dtype=np.int32)
         self._check(self.lib.fsb_stream_history_append(self._h, int(stream_id), a.ctypes.data, len(a)))
+
+    def lookup_drafts(self, stream_ids, kmax, min_n, eos: int):
+        """Prompt-lookup drafts of resident histories (``fsb_lookup_drafts_resident``): a list of int32 arrays."""
+        sids = np.ascontiguousarray(stream_ids, dtype=np.int32)
+        n = len(sids)
+        km = np.ascontiguousarray(np.broadcast_to(np.asarray(kmax, dtype=np.int32), (n,)))
+        mn = np.ascontiguousarray(np.broadcast_to(np.asarray(min_n, dtype=np.int32), (n,)))
+        stride = max(int(km.max()) if n else 1, 1)
+        out = np.zeros((n, stride), dtype=np.int32)
+        cnt = np.zeros(n, dtype=np.int32)
+        self._check(self.lib.fsb_lookup_drafts_resident(self._h, n, sids.ctypes.data, km.ctypes.data, mn.ctypes.data, int(eos), out.ctypes.data,
+                                                        stride, cnt.ctypes.data))
+        return [out[i, : cnt[i]].copy() for i in range(n)]
 
     def history_len(self, stream_id: int) -> int:
         n = C.c_int64(0)

@@ -99,8 +99,20 @@ size_t stream_kernel_smem_bytes();
 int prepare_device_kernels(int* ctas_per_sm);
 int launch_stream_kernel(const StreamArgs& a, int grid, void* stream);
 
+// One stream of a prompt-lookup drafting call: where its history lies in the id pool and what to look for.
+struct LookupDesc {
+    int64_t begin;         // first id of the history in the id pool
+    int32_t len;           // ids in the history
+    int32_t kmax;          // most drafts wanted
+    int32_t min_n;         // shortest suffix that may be matched (>= 1)
+    int32_t eos;           // end-of-sequence id: a draft stops before it
+};
+static_assert(sizeof(LookupDesc) == 24, "LookupDesc layout");
+constexpr int kDraftStride = 68;              // int32 words per stream of a drafting call: the count, then up to 67 drafts
+
 // Defined in fsb_support.cu.
 int prepare_support_kernels();
+int launch_lookup_drafts(const int32_t* pool, const LookupDesc* desc, int n_streams, int32_t* out, int stride, void* stream);
 int launch_append_tokens(const RowDesc* rows, int n_rows, const int32_t* tokens, int32_t* pool, void* stream);
 int launch_merge_lists(const void* lists, const int32_t* list_n, int n_lists, int list_stride, int n_rows, const RowDesc* rows, int32_t* tokens,
                        int32_t* kept_ids, double* kept_pr, int32_t* kept_n, uint32_t* status, void* stream);

@@ -100,6 +100,11 @@ struct fsb_handle {
     double* d_kept_pr = nullptr;
     int32_t* d_kept_n = nullptr;
     bool kept_valid = false;
+    // prompt-lookup drafting: descriptors up, drafts down (pinned host copies beside the device arrays)
+    fsb::LookupDesc* h_lookup = nullptr;
+    fsb::LookupDesc* d_lookup = nullptr;
+    int32_t* h_drafts = nullptr;
+    int32_t* d_drafts = nullptr;
     float* d_logits_stage = nullptr;   // device copy of host logits: max_rows x max_vocab, allocated with the engine
     size_t logits_stage_elems = 0;
     uint64_t* d_trace = nullptr;       // caller-owned diagnostics buffer, or null
@@ -585,7 +590,11 @@ int fsb_create(int device, int max_rows, int max_vocab, int64_t max_hist_ids, fs
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_pr), sizeof(double) * (size_t)max_rows * fsb::kMaxK) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_kept_n), sizeof(int32_t) * (size_t)max_rows) != cudaSuccess ||
         cudaMalloc(reinterpret_cast<void**>(&h->d_pool), sizeof(int32_t) * (size_t)std::max<int64_t>(max_hist_ids, 1)) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&h->d_logits_stage), sizeof(float) * h->logits_stage_elems) != cudaSuccess)
+        cudaMalloc(reinterpret_cast<void**>(&h->d_logits_stage), sizeof(float) * h->logits_stage_elems) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_lookup), sizeof(fsb::LookupDesc) * (size_t)max_rows) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&h->d_drafts), sizeof(int32_t) * (size_t)max_rows * fsb::kDraftStride) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void**>(&h->h_lookup), sizeof(fsb::LookupDesc) * (size_t)max_rows) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void**>(&h->h_drafts), sizeof(int32_t) * (size_t)max_rows * fsb::kDraftStride) != cudaSuccess)
         return bail(FSB_ERR_CUDA);
     if (alloc_batch(h, max_rows, max_hist_ids, std::max<int64_t>(max_hist_ids, 1), &h->own) != FSB_OK) return bail(FSB_ERR_CUDA);
     *out = h;
@@ -607,6 +616,10 @@ int fsb_destroy(fsb_handle* h) {
     if (h->d_kept_n) cudaFree(h->d_kept_n);
     if (h->d_pool) cudaFree(h->d_pool);
     if (h->d_logits_stage) cudaFree(h->d_logits_stage);
+    if (h->d_lookup) cudaFree(h->d_lookup);
+    if (h->d_drafts) cudaFree(h->d_drafts);
+    if (h->h_lookup) cudaFreeHost(h->h_lookup);
+    if (h->h_drafts) cudaFreeHost(h->h_drafts);
     if (h->own_stream && h->stream) cudaStreamDestroy(h->stream);
     if (h->side) cudaStreamDestroy(h->side);
     if (h->ev_fork) cudaEventDestroy(h->ev_fork);
@@ -761,6 +774,41 @@ int fsb_stream_history_append(fsb_handle* h, int stream_id, const int32_t* ids, 
     cudaSetDevice(h->device);
     s->hist.insert(s->hist.end(), ids, ids + n);
     return sync_history(h, s);
+}
+
+int fsb_lookup_drafts_resident(fsb_handle* h, int n_streams, const int* stream_ids, const int* kmax, const int* min_n, int32_t eos,
+                               int32_t* drafts_out, int stride, int* n_out) {
+    if (!h || !stream_ids || !kmax || !min_n || !drafts_out || !n_out) return FSB_ERR_INVALID;
+    if (n_streams <= 0 || n_streams > h->max_rows) return fail(h, FSB_ERR_CAPACITY, "%d streams, the engine holds %d rows", n_streams, h->max_rows);
+    if (stride < 1) return fail(h, FSB_ERR_INVALID, "stride must be positive");
+    cudaSetDevice(h->device);
+    for (int i = 0; i < n_streams; ++i) {
+        Stream* s = get_stream(h, stream_ids[i]);
+        if (!s) return fail(h, FSB_ERR_STREAM_ID, "unknown stream id %d", stream_ids[i]);
+        if (min_n[i] < 1) return fail(h, FSB_ERR_RANGE, "stream %d: the shortest match is one token, got %d", i, min_n[i]);
+        if (kmax[i] > stride || kmax[i] > fsb::kDraftStride - 1)
+            return fail(h, FSB_ERR_CAPACITY, "stream %d: %d drafts do not fit (stride %d, at most %d per call)", i, kmax[i], stride, fsb::kDraftStride - 1);
+        const int rc = sync_history(h, s);
+        if (rc != FSB_OK) return rc;
+        fsb::LookupDesc& d = h->h_lookup[i];
+        d.begin = s->pool_off >= 0 ? s->pool_off : 0;
+        d.len = (int32_t)s->hist.size();
+        d.kmax = std::max(0, kmax[i]);
+        d.min_n = min_n[i];
+        d.eos = eos;
+    }
+    FSB_CUDA(h, cudaMemcpyAsync(h->d_lookup, h->h_lookup, sizeof(fsb::LookupDesc) * (size_t)n_streams, cudaMemcpyHostToDevice, h->stream));
+    const int e = fsb::launch_lookup_drafts(h->d_pool, h->d_lookup, n_streams, h->d_drafts, fsb::kDraftStride, h->stream);
+    if (e != 0) return fail(h, FSB_ERR_CUDA, "draft kernel launch: %s", cudaGetErrorString((cudaError_t)e));
+    h->counters.kernel_launches++;
+    FSB_CUDA(h, cudaMemcpyAsync(h->h_drafts, h->d_drafts, sizeof(int32_t) * (size_t)n_streams * fsb::kDraftStride, cudaMemcpyDeviceToHost, h->stream));
+    FSB_CUDA(h, cudaStreamSynchronize(h->stream));
+    for (int i = 0; i < n_streams; ++i) {
+        const int32_t* src = h->h_drafts + (size_t)i * fsb::kDraftStride;
+        n_out[i] = src[0];
+        for (int k = 0; k < src[0]; ++k) drafts_out[(size_t)i * stride + k] = src[1 + k];
+    }
+    return FSB_OK;
 }
 
 int fsb_stream_history_len(const fsb_handle* h, int stream_id, int64_t* n) {

@@ -93,7 +93,51 @@ __global__ void accept_windows_kernel(const int32_t* table, int n_streams, const
     if (acc > 0) pool[end + acc - 1] = tokens[r0 + acc - 1];
 }
 
+// Prompt-lookup drafting over resident histories (lookup_draft, src/server.cpp:552-564): the tokens that followed
+// the most recent earlier occurrence of the history's last n tokens, n = 4, 3, ... min_n - at most kmax of them, cut
+// at the end-of-sequence id; an occurrence whose continuation is empty is passed over.  One CTA per stream: every
+// thread tests some start positions of an n, the largest matching position wins, one thread copies the draft.
+// out[i * stride] = number of drafts of stream i, then the drafts.
+__global__ void lookup_drafts_kernel(const int32_t* pool, const LookupDesc* desc, int n_streams, int32_t* out, int stride) {
+    __shared__ int best;
+    const int i = blockIdx.x;
+    if (i >= n_streams) return;
+    const LookupDesc d = desc[i];
+    const int32_t* h = pool + d.begin;
+    const int L = d.len;
+    int found_n = 0;
+    for (int n = min(4, L - 1); n >= d.min_n && d.kmax > 0; --n) {
+        if (threadIdx.x == 0) best = -1;
+        __syncthreads();
+        for (int p = L - n - 1 - (int)threadIdx.x; p >= 0; p -= (int)blockDim.x) {
+            bool eq = h[p + n] != d.eos;            // an occurrence followed by the end-of-sequence id drafts nothing
+            for (int k = 0; k < n && eq; ++k) eq = h[p + k] == h[L - n + k];
+            if (eq) atomicMax(&best, p);
+        }
+        __syncthreads();
+        if (best >= 0) {
+            found_n = n;
+            break;
+        }
+        __syncthreads();   // `best` is reset by thread 0 at the top of the next round
+    }
+    if (threadIdx.x == 0) {
+        int cnt = 0;
+        if (found_n > 0)
+            for (int k = best + found_n; k < L && cnt < d.kmax && cnt < stride - 1; ++k) {
+                if (h[k] == d.eos) break;
+                out[(size_t)i * stride + 1 + cnt++] = h[k];
+            }
+        out[(size_t)i * stride] = cnt;
+    }
+}
+
 }  // namespace
+
+int launch_lookup_drafts(const int32_t* pool, const LookupDesc* desc, int n_streams, int32_t* out, int stride, void* stream) {
+    lookup_drafts_kernel<<<n_streams, 256, 0, static_cast<cudaStream_t>(stream)>>>(pool, desc, n_streams, out, stride);
+    return (int)cudaGetLastError();
+}
 
 int prepare_support_kernels() {
     return (int)cudaFuncSetAttribute(merge_lists_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMerge);

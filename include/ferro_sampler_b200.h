@@ -196,6 +196,15 @@ FSB_API int fsb_stream_history_len(const fsb_handle* h, int stream_id, int64_t* 
 FSB_API int fsb_sample_batch_resident(fsb_handle* h, int n_rows, const int* stream_ids, const float* logits, int64_t ld, int n_vocab,
                                       int32_t* tokens_out, unsigned flags);
 
+/* Prompt-lookup drafting (lookup_draft, src/server.cpp:552-564) over resident histories: for stream i the tokens that
+ * followed the most recent earlier occurrence of the last n tokens of its history, n = 4, 3, ... min_n[i] - at most
+ * kmax[i] of them (and at most 67), never the end-of-sequence id `eos` or anything after it; an occurrence with an empty
+ * continuation is passed over, as in the reference.  One small kernel over the id pool, one CTA per stream; the drafts
+ * of stream i are written to drafts_out[i * stride ..] and their number to n_out[i].  min_n[i] >= 1 (the reference
+ * passes 2 or 3).  The caller builds the rows [last token, drafts ...] of fsb_verify_windows_resident from them. */
+FSB_API int fsb_lookup_drafts_resident(fsb_handle* h, int n_streams, const int* stream_ids, const int* kmax, const int* min_n, int32_t eos,
+                                       int32_t* drafts_out, int stride, int* n_out);
+
 /* Speculative verification windows (the accept loop of src/server.cpp:626-645) for n_streams streams.
  * Stream i owns rows row_off[i] .. row_off[i+1]) of `logits`; rows_flat holds, per stream, [last token, draft_1 ..
  * draft_{m-1}] as the scheduler builds them (src/server.cpp:617).  Row r is sampled with history_i followed by

@@ -84,6 +84,16 @@ class Oracle:
         L.oracle_verify_window.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p,
                                            C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
 
+        L.oracle_lookup_draft.restype = C.c_int
+        L.oracle_lookup_draft.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+
+    def lookup_draft(self, hist, kmax: int, eos: int, min_n: int) -> np.ndarray:
+        """Prompt-lookup drafts of one history (lookup_draft, src/server.cpp:552-564)."""
+        h = np.ascontiguousarray(hist, dtype=np.int32)
+        out = np.zeros(max(kmax, 1), dtype=np.int32)
+        n = self.lib.oracle_lookup_draft(h.ctypes.data, len(h), int(kmax), int(eos), int(min_n), out.ctypes.data)
+        return out[:n].copy()
+
     # --- engines
     def new_rngs(self, seeds) -> np.ndarray:
         seeds = np.asarray(seeds, dtype=np.uint64).reshape(-1)

@@ -253,3 +253,29 @@ int oracle_verify_window(const oracle_params* p, oracle_mt64* rng, float* logits
     if (confirmed) *confirmed = conf;
     return acc;
 }
+
+/*
+ * Prompt-lookup drafting (lookup_draft, src/server.cpp:552-564): for n = min(4, len - 1) down to min_n, the start
+ * positions p = len - n - 1 .. 0 are tried from the most recent one; at the first p where h[p .. p+n) equals the
+ * last n tokens, the tokens after the occurrence are copied - at most kmax, stopping before `eos` - and returned if
+ * there is at least one; otherwise the search goes on (earlier p, then shorter n).  Returns the number of drafts.
+ * Parity unpinned: the reference holds no vectors for this function (its test needs a running server); the
+ * restatement follows the source line by line and tests/ compare it with an independent brute-force search.
+ */
+int oracle_lookup_draft(const int* h, int len, int kmax, int eos, int min_n, int* drafts) {
+    for (int n = (len - 1 < 4 ? len - 1 : 4); n >= min_n; --n) {
+        for (int p = len - n - 1; p >= 0; --p) {
+            int eq = 1;
+            for (int k = 0; k < n; ++k)
+                if (h[p + k] != h[len - n + k]) { eq = 0; break; }
+            if (!eq) continue;
+            int cnt = 0;
+            for (int k = p + n; k < len && cnt < kmax; ++k) {
+                if (h[k] == eos) break;
+                drafts[cnt++] = h[k];
+            }
+            if (cnt > 0) return cnt;
+        }
+    }
+    return 0;
+}

@@ -58,7 +58,7 @@ def test_config3_large_vocabulary_headline_shape(engine, oracle):
 def test_config3_fused_softcap_variant(engine, oracle):
     # raw logits + softcap fused on the device against host tanhf + oracle: device tanhf differs from the host's in
     # the last ulps, so this variant is reported and bounded, not bit-gated
-    cfg = synth.config3(rows=16)
+    cfg = synth.config3(rows=64)
     raw, p, hists = cfg["raw_logits"], cfg["params"], cfg["hists"]
     capped = raw.copy()
     oracle.softcap(capped, 30.0)
@@ -73,7 +73,7 @@ def test_config3_fused_softcap_variant(engine, oracle):
             engine.close_stream(int(s))
     mism = int((tok != ref["tokens"]).sum())
     print(f"fused softcap: {mism} of {len(tok)} tokens differ from host-tanhf oracle")
-    assert mism <= 2
+    assert mism <= 3        # measured: 0 of 64 (bench.py reports the count on every run)
 
 
 def test_config5_serving_batch(engine, oracle):

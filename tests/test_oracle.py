@@ -92,3 +92,33 @@ def test_oracle_window_matches_reference(oracle, reflib):
         ta, acc_a, conf_a, _ = oracle.verify_window(p, oracle.new_rngs(p["seed"])[0], lg.copy(), rows, hist)
         tb, acc_b, conf_b = reflib.verify_window(p, lg.copy(), rows, hist)
         assert acc_a == acc_b and conf_a == conf_b and list(ta[:acc_a]) == list(tb[:acc_b])
+
+
+def _lookup_by_definition(h, kmax, eos, min_n):
+    """The drafting rule written as a search over all candidates, independent of the restatement's loop order."""
+    L = len(h)
+    for n in range(min(4, L - 1), min_n - 1, -1):
+        hits = [p for p in range(0, L - n) if list(h[p:p + n]) == list(h[L - n:])]
+        for p in sorted(hits, reverse=True):
+            d = []
+            for t in h[p + n:]:
+                if t == eos or len(d) >= kmax:
+                    break
+                d.append(int(t))
+            if d:
+                return d
+    return []
+
+
+def test_prompt_lookup_drafting_follows_its_definition(oracle):
+    rng = np.random.default_rng(12)
+    assert list(oracle.lookup_draft([5, 6, 7, 8, 9, 1, 5, 6, 7, 8], 3, 0, 2)) == [9, 1, 5]          # the 4-gram, three drafts
+    assert list(oracle.lookup_draft([5, 6, 7, 0, 9, 5, 6, 7], 4, 0, 2)) == []                        # only continuation starts with eos
+    assert list(oracle.lookup_draft([1, 2, 9, 3, 1, 2, 0, 4, 1, 2], 4, 0, 2)) == [9, 3, 1, 2]        # the recent hit drafts nothing: the earlier one
+    assert list(oracle.lookup_draft([7], 4, 0, 2)) == [] and list(oracle.lookup_draft([], 4, 0, 2)) == []
+    assert list(oracle.lookup_draft([3, 4, 3], 2, 0, 1)) == [4, 3] and list(oracle.lookup_draft([3, 4, 3], 2, 0, 2)) == []
+    for trial in range(300):
+        L = int(rng.integers(0, 60))
+        h = rng.integers(0, 4, size=L).astype(np.int32)            # a tiny alphabet: repeats everywhere
+        kmax, eos, min_n = int(rng.integers(1, 9)), int(rng.integers(0, 5)), int(rng.integers(1, 5))
+        assert list(oracle.lookup_draft(h, kmax, eos, min_n)) == _lookup_by_definition(h, kmax, eos, min_n), (h, kmax, eos, min_n)

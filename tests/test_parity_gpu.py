@@ -67,7 +67,7 @@ def test_random_batches_candidate_kernel(engine, oracle, shape):
     assert near_total <= 1
 
 
-@pytest.mark.parametrize("shape", [(2, 6), (3, 33), (4, 1000), (2, 4097), (4, 65536), (2, 70001)])
+@pytest.mark.parametrize("shape", [(2, 6), (3, 33), (4, 1000), (2, 4097), (4, 65536), (2, 70001), (2, 262144)])
 def test_random_batches_with_full_vocabulary_rows(engine, oracle, shape):
     B, V = shape
     rng = np.random.default_rng(2000 + B * 7 + V)
@@ -77,6 +77,23 @@ def test_random_batches_with_full_vocabulary_rows(engine, oracle, shape):
         assert not hard, (shape, trial, hard[:3])
         assert not kept_bad, (shape, trial, kept_bad[:3])
         assert near <= 1
+
+
+def test_full_vocabulary_rows_too_long_for_shared_memory(oracle):
+    """Rows of more than 8 x 32768 logits: a CTA's slice no longer fits its shared memory, so the passes of the
+    full-vocabulary kernel read the row from global memory and transform it again each time."""
+    B, V = 3, 300001
+    eng = fb.Engine(device=0, max_rows=B, max_vocab=V, max_hist_ids=B * 2100 + 16)
+    try:
+        rng = np.random.default_rng(8128)
+        for trial in range(3):
+            lg, p, hists = random_case(rng, B, V, trial, allow_full=True)
+            p["top_k"][0] = 0                                   # at least one row takes the full-vocabulary kernel
+            p["temperature"][0] = max(float(p["temperature"][0]), 0.5)
+            _, _, hard, near, kept_bad = run_batch(eng, oracle, lg, p, hists)
+            assert not hard and not kept_bad and near <= 1, (trial, hard[:3], kept_bad[:3])
+    finally:
+        eng.close()
 
 
 def test_unaligned_rows_take_the_plain_load_path(engine, oracle):
@@ -203,8 +220,10 @@ def test_overlapping_launches_give_the_same_tokens(engine, oracle, shape):
 
 @pytest.mark.parametrize("case", [(2, 262144, 40), (1, 200000, 1), (3, 150001, 64)])
 def test_rows_cut_into_many_short_segments(engine, oracle, case):
-    """A small batch of long rows is dealt one tile per CTA: a row then has more segments than a CTA has warps, and
-    its candidates are merged through the gather-and-order path instead of the ordered-list path."""
+    """Small batches of long rows, where the planner cuts a row into pieces: (2, 262144) eight pieces per row that run
+    as a cluster and exchange candidates on chip; (1, 200000) five pieces whose ordered lists meet in the row's scratch
+    behind a ticket; (3, 150001) a prime number of tiles, one CTA per row.  (Rows of more than 16 pieces, which are
+    merged by gathering and re-ordering, only arise in the static-scratch entry point: tests/test_zz_no_alloc.py.)"""
     B, V, k = case
     rng = np.random.default_rng(4242 + V)
     lg = (rng.standard_normal((B, V)) * 3).astype(np.float32)

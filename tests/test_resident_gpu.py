@@ -65,3 +65,135 @@ def test_resident_history_errors_and_region_reuse(engine):
             engine.close_stream(int(s))
     with pytest.raises(fb.SamplerError):
         engine.history_len(int(sids[0]))                                   # closed
+
+
+def test_calls_with_explicit_histories_after_a_resident_call_use_their_own_histories(engine, oracle):
+    """The engine's one internal batch serves every public call.  A resident call points it at the id pool; the next
+    call that brings its histories along (fsb_sample_batch, fsb_verify_windows) must read those, not the pool."""
+    B, V = 4, 8192
+    rng = np.random.default_rng(2718)
+    p = fb.make_params(B, temperature=0.7, top_k=30, top_p=0.9, repetition_penalty=1.5)
+    p["seed"] = 60 + np.arange(B)
+    sids = engine.open_streams(p)
+    rngs = oracle.new_rngs(p["seed"])
+    resident = [rng.integers(0, V, size=50).astype(np.int32) for _ in range(B)]
+    try:
+        for i, s in enumerate(sids):
+            engine.history_set(int(s), resident[i])
+        lg = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+        ref = oracle.sample_rows(p, rngs, lg.copy(), resident)
+        assert np.array_equal(engine.sample_batch_resident(sids, lg.copy()), ref["tokens"])
+        # explicit histories that penalise other ids than the resident ones
+        other = [rng.integers(0, V, size=70).astype(np.int32) for _ in range(B)]
+        lg = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+        for i in range(B):
+            lg[i, other[i][:5]] += 9.0                     # the penalty decides among these
+        ref = oracle.sample_rows(p, rngs, lg.copy(), other)
+        assert np.array_equal(engine.sample_batch(sids, lg.copy(), other), ref["tokens"])
+        # ... and the same for verification windows right after another resident call
+        lg = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+        ref = oracle.sample_rows(p, rngs, lg.copy(), resident)
+        assert np.array_equal(engine.sample_batch_resident(sids, lg.copy()), ref["tokens"])
+        m = 4
+        lgw = (rng.standard_normal((B * m, V)) * 3).astype(np.float32)
+        rows = []
+        for i in range(B):
+            lgw[i * m:(i + 1) * m, other[i][:5]] += 9.0
+            rows.append(np.concatenate([[int(other[i][-1])], rng.integers(0, V, size=m - 1)]).astype(np.int32))
+        want = [oracle.verify_window(p[i:i + 1], rngs[i], lgw[i * m:(i + 1) * m].copy(), rows[i], other[i]) for i in range(B)]
+        toks, acc, conf = engine.verify_windows(sids, rows, lgw.copy(), other)
+        for i in range(B):
+            t, a, c, _ = want[i]
+            assert acc[i] == a and conf[i] == c and list(toks[i][:a]) == list(t[:a]), i
+    finally:
+        for s in sids:
+            engine.close_stream(int(s))
+
+
+@pytest.mark.parametrize("append", [False, True])
+def test_resident_verification_windows_match_the_reference_accept_loop(engine, oracle, append):
+    """Speculative steps on resident histories (src/server.cpp:598-645): only the drafts go up.  With APPEND_SAMPLED
+    the accepted tokens join the history on the device, so the next step - resident as well - sees them."""
+    import torch
+    S, V, m, steps = 6, 32768, 5, 6
+    rng = np.random.default_rng(1618)
+    p = fb.make_params(S, temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.4)
+    p["temperature"][:3] = 0.0
+    p["repeat_last_n"][1] = 8
+    p["seed"] = 300 + np.arange(S)
+    sids = engine.open_streams(p)
+    rngs = oracle.new_rngs(p["seed"])
+    hists = [rng.integers(0, V, size=int(n)).astype(np.int32) for n in rng.integers(20, 40, size=S)]
+    try:
+        for i, s in enumerate(sids):
+            engine.history_set(int(s), hists[i])
+        for step in range(steps):
+            lg = (rng.standard_normal((S * m, V)) * 2).astype(np.float32)
+            rows, want = [], []
+            for i in range(S):
+                drafts = rng.integers(0, V, size=m - 1).astype(np.int32)
+                # make the first drafts right: what the oracle samples for rows 0 .. good-1 with the growing history
+                good = int(rng.integers(0, m))
+                h = list(hists[i])
+                probe = rngs[i:i + 1].copy()                 # a copy of the stream's engine: the real one must not advance
+                for r in range(good):
+                    t = int(oracle.sample_rows(p[i:i + 1], probe, lg[i * m + r:i * m + r + 1].copy(), [np.array(h, dtype=np.int32)])["tokens"][0])
+                    if r < m - 1:
+                        drafts[r] = t
+                    h.append(t)
+                rows.append(np.concatenate([[int(hists[i][-1])], drafts]).astype(np.int32))
+                want.append(oracle.verify_window(p[i:i + 1], rngs[i], lg[i * m:(i + 1) * m].copy(), rows[i], hists[i]))
+            src = torch.from_numpy(lg).cuda() if step % 2 else lg.copy()
+            toks, acc, conf = engine.verify_windows_resident(sids, rows, src, n_vocab=V,
+                                                             flags=fb.APPEND_SAMPLED if append else 0)
+            for i in range(S):
+                t, a, c, _ = want[i]
+                assert acc[i] == a and conf[i] == c and list(toks[i][:a]) == list(t[:a]), (step, i)
+                new = np.asarray(t[:a], dtype=np.int32)
+                if append:
+                    hists[i] = np.concatenate([hists[i], new]).astype(np.int32)
+                else:                                          # the caller appends what it accepted
+                    engine.history_append(int(sids[i]), new)
+                    hists[i] = np.concatenate([hists[i], new]).astype(np.int32)
+            assert [engine.history_len(int(s)) for s in sids] == [len(x) for x in hists]
+        # a plain resident step afterwards reads the histories the windows left behind
+        lg = (rng.standard_normal((S, V)) * 2).astype(np.float32)
+        for i in range(S):
+            lg[i, hists[i][-3:]] += 8.0
+        ref = oracle.sample_rows(p, rngs, lg.copy(), hists)
+        assert np.array_equal(engine.sample_batch_resident(sids, lg.copy()), ref["tokens"])
+    finally:
+        for s in sids:
+            engine.close_stream(int(s))
+
+
+def test_prompt_lookup_drafts_of_resident_histories_match_the_oracle(engine, oracle):
+    """lookup_draft (src/server.cpp:552-564) run on the device over the id pool, 40 streams at a time."""
+    rng = np.random.default_rng(99)
+    S = 40
+    p = fb.make_params(S)
+    p["seed"] = np.arange(S)
+    sids = engine.open_streams(p)
+    try:
+        for trial in range(4):
+            hists = []
+            for i in range(S):
+                L = int(rng.integers(0, 30)) if i % 4 == 0 else int(rng.integers(200, 3000))
+                alphabet = 3 if i % 3 == 0 else 200                # dense repeats / natural-looking text
+                h = rng.integers(0, alphabet, size=L).astype(np.int32)
+                if L > 100 and i % 2:                              # a copied run: the end repeats an earlier stretch
+                    a = int(rng.integers(0, L // 2))
+                    h[-12:] = h[a:a + 12]
+                hists.append(h)
+                engine.history_set(int(sids[i]), h)
+            kmax = rng.integers(1, 9, size=S).astype(np.int32)
+            min_n = rng.integers(1, 4, size=S).astype(np.int32)
+            eos = int(rng.integers(0, 3))
+            got = engine.lookup_drafts(sids, kmax, min_n, eos)
+            for i in range(S):
+                assert list(got[i]) == list(oracle.lookup_draft(hists[i], int(kmax[i]), eos, int(min_n[i]))), (trial, i)
+        with pytest.raises(fb.SamplerError):
+            engine.lookup_drafts(sids[:1], 4, 0, 0)                # a match of zero tokens is not a match
+    finally:
+        for s in sids:
+            engine.close_stream(int(s))

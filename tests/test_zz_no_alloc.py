@@ -19,7 +19,9 @@ def _greedy_through_the_handle(engine, lg):
             engine.close_stream(int(s))
 
 
-@pytest.mark.parametrize("shape", [(64, 262144), (17, 65536), (5, 70001), (1, 33)])
+# (1, 262144) and (3, 200000): one tile per CTA, so a row has 32 resp. 25 segments - more than a CTA has warps - and
+# its candidates are merged by the gather-and-order route instead of the ordered-list route
+@pytest.mark.parametrize("shape", [(64, 262144), (17, 65536), (5, 70001), (1, 33), (1, 262144), (3, 200000)])
 def test_static_scratch_entry_point_matches_the_handle_based_one_twice_in_a_row(engine, shape):
     import torch
     B, V = shape
@@ -49,6 +51,25 @@ def test_static_scratch_entry_point_without_waiting_and_with_a_row_stride(engine
     fb.argmax_rows_static(dev.data_ptr(), ld, B, V, out.data_ptr(), wait=False, cuda_stream=torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), np.argmax(wide[:, :V], axis=1).astype(np.int32))
+
+
+def test_static_scratch_entry_point_recovers_from_an_error_nobody_waited_for():
+    """A call without FSB_STATIC_WAIT whose kernel reports an error (a row without a finite logit) leaves the status
+    word set; the next call clears it before its kernel runs and must succeed."""
+    import torch
+    B, V = 4, 20000
+    bad = torch.full((B, V), float("nan"), device="cuda")
+    out = torch.zeros(B, dtype=torch.int32, device="cuda")
+    fb.argmax_rows_static(bad.data_ptr(), V, B, V, out.data_ptr(), wait=False, cuda_stream=torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    with pytest.raises(fb.SamplerError) as e:               # the same input, waited for: the error is reported
+        fb.argmax_rows_static(bad.data_ptr(), V, B, V, out.data_ptr(), cuda_stream=torch.cuda.current_stream().cuda_stream)
+    assert "FSB_ERR_DEVICE" in str(e.value)
+    lg = (np.random.default_rng(5).standard_normal((B, V)) * 2).astype(np.float32)
+    good = torch.from_numpy(lg).cuda()
+    for _ in range(2):
+        fb.argmax_rows_static(good.data_ptr(), V, B, V, out.data_ptr(), cuda_stream=torch.cuda.current_stream().cuda_stream)
+        assert np.array_equal(out.cpu().numpy(), np.argmax(lg, axis=1).astype(np.int32))
 
 
 def test_static_scratch_entry_point_refuses_what_its_array_cannot_hold():
