@@ -248,7 +248,7 @@ def time_calls(call, n, warm=3):
     return 1e6 * (time.perf_counter() - t0) / n
 
 
-def config_figures(torch, fb, device, peak, tanhf, budget_s=3.0):
+def config_figures(torch, fb, device, peak, tanhf, budget_s=3.0, only=None):
     """The other four configurations through the call a server would make, each with the reference's CPU time on the
     same rows beside it: device time per step (CUDA events, logits resident, buffers rotating past L2 where they are
     large enough to matter), wall time of the public call, algorithmic bytes and the fraction of the HBM peak."""
@@ -271,6 +271,13 @@ def config_figures(torch, fb, device, peak, tanhf, budget_s=3.0):
             d.update(extra)
         out[name] = d
 
+    def resident_call_us(e, sids, hists, devs, vocab, n):
+        for s_, h_ in zip(sids, hists):
+            e.history_set(int(s_), h_)
+        return time_calls(lambda i: e.sample_batch_resident(sids, devs[i % len(devs)].data_ptr(), n_vocab=vocab), n)
+
+    if only not in (None, "cfg1"):
+        return config_figures_rest(torch, fb, device, peak, tanhf, budget_s, only, out, engine_for, entry, resident_call_us)
     # ---- cfg 1: one row, the latency of a single stream's step
     c1 = synth.config1()
     e = engine_for(1, 65536, 1 << 12)
@@ -281,9 +288,23 @@ def config_figures(torch, fb, device, peak, tanhf, budget_s=3.0):
     batch.free()
     call = time_calls(lambda i: e.sample_batch(sid, devs[i % 4], c1["hists"], n_vocab=65536), 200)
     cpu = cpu_rows_per_s(c1["params"], c1["logits"], c1["hists"], budget_s / 2, threads=1)
-    entry("cfg1_1x65536_k40", 1, 65536, 64, step, call, cpu + (1,))
+    entry("cfg1_1x65536_k40", 1, 65536, 64, step, call, cpu + (1,), {"public_call_resident_us": resident_call_us(e, sid, c1["hists"], devs, 65536, 200)})
     e.close()
+    return config_figures_rest(torch, fb, device, peak, tanhf, budget_s, only, out, engine_for, entry, resident_call_us)
 
+
+def config_figures_rest(torch, fb, device, peak, tanhf, budget_s, only, out, engine_for, entry, resident_call_us):
+    from ferro_b200 import synth
+    if only in (None, "cfg2"):
+        config2_figures(torch, fb, device, synth, budget_s, engine_for, entry, resident_call_us)
+    if only in (None, "cfg4"):
+        config4_figures(torch, fb, device, synth, budget_s, engine_for, entry)
+    if only in (None, "cfg5"):
+        config5_figures(torch, fb, device, synth, budget_s, tanhf, engine_for, entry, resident_call_us)
+    return out
+
+
+def config2_figures(torch, fb, device, synth, budget_s, engine_for, entry, resident_call_us):
     # ---- cfg 2: the mixed decode batch, four of its eight rows take the full-vocabulary kernel
     c2 = synth.config2()
     e = engine_for(8, 65536, 1 << 14)
@@ -295,9 +316,12 @@ def config_figures(torch, fb, device, peak, tanhf, budget_s=3.0):
     batch.free()
     call = time_calls(lambda i: e.sample_batch(sids, devs[i % 4], c2["hists"], n_vocab=65536), 100)
     cpu = cpu_rows_per_s(c2["params"], c2["logits"], c2["hists"], budget_s)
-    entry("cfg2_8x65536_mixed", 8, 65536, 256, step, call, cpu + (8,), {"kernels_per_step": kernels, "full_vocabulary_rows": 4})
+    entry("cfg2_8x65536_mixed", 8, 65536, 256, step, call, cpu + (8,),
+          {"kernels_per_step": kernels, "full_vocabulary_rows": 4, "public_call_resident_us": resident_call_us(e, sids, c2["hists"], devs, 65536, 100)})
     e.close()
 
+
+def config4_figures(torch, fb, device, synth, budget_s, engine_for, entry):
     # ---- cfg 4: 8 verification windows of 17 rows through fsb_verify_windows
     c4 = synth.config4()
     e = engine_for(136, 65536, 1 << 14)
@@ -313,6 +337,8 @@ def config_figures(torch, fb, device, peak, tanhf, budget_s=3.0):
     entry("cfg4_8x17_windows_65536_greedy", 136, 65536, 0, step, call, cpu + (136,), {"public_call": "fsb_verify_windows"})
     e.close()
 
+
+def config5_figures(torch, fb, device, synth, budget_s, tanhf, engine_for, entry, resident_call_us):
     # ---- cfg 5 on one GPU: 512 rows; the first 64 are the configuration's own rows (the CPU sample), the rest are
     # drawn on the device from the same distribution
     n_own = 64
@@ -335,10 +361,10 @@ def config_figures(torch, fb, device, peak, tanhf, budget_s=3.0):
     batch.free()
     call = time_calls(lambda i: e.sample_batch(sids, devs[i % 2], hists, n_vocab=262144), 20)
     cpu = cpu_rows_per_s(c5["params"], c5["logits"], c5["hists"], budget_s)
-    entry("cfg5_512x262144_k40", 512, 262144, 1024, step, call, cpu + (n_own,))
+    entry("cfg5_512x262144_k40", 512, 262144, 1024, step, call, cpu + (n_own,),
+          {"public_call_resident_us": resident_call_us(e, sids, hists, devs, 262144, 20)})
     e.close()
     del devs
-    return out
 
 
 def softcap_mismatches(fb, eng, sids, raw, ref_tokens, hists):
@@ -349,6 +375,29 @@ def softcap_mismatches(fb, eng, sids, raw, ref_tokens, hists):
     finally:
         eng.set_softcap(0.0)
     return int((tok != ref_tokens).sum())
+
+
+def c_call_latency(fb):
+    """The public calls timed from C++ (tests/call_latency.cpp, built here with g++): medians in microseconds for the
+    headline shape.  None when the machine has no compiler or no CUDA toolkit headers."""
+    import shutil
+    import subprocess
+    import tempfile
+    gxx, cuda = shutil.which("g++"), os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    src = os.path.join(ROOT, "tests", "call_latency.cpp")
+    if not gxx or not os.path.exists(src) or not os.path.exists(os.path.join(cuda, "include", "cuda_runtime.h")):
+        return None
+    lib = fb.library_path()
+    with tempfile.TemporaryDirectory() as tmp:
+        exe = os.path.join(tmp, "call_latency")
+        cmd = [gxx, "-std=c++17", "-O2", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda, "include"), src, "-L", os.path.dirname(lib),
+               "-lferro_sampler_b200", "-Wl,-rpath," + os.path.dirname(lib), "-L", os.path.join(cuda, "lib64"), "-lcudart", "-o", exe]
+        if subprocess.run(cmd, capture_output=True).returncode != 0:
+            return None
+        r = subprocess.run([exe, str(ROWS), str(VOCAB), str(HIST), "200"], capture_output=True, text=True, timeout=300)
+        if r.returncode != 0:
+            return {"error": (r.stderr or r.stdout)[-200:]}
+        return json.loads(r.stdout.strip().splitlines()[-1])
 
 
 def vocab_sharded_leg(torch, dist, fb, device, rank, world, barrier):
@@ -416,6 +465,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the side figures (other configurations, staging, vocabulary sharding)")
+    ap.add_argument("--only", choices=["cfg1", "cfg2", "cfg4", "cfg5"], help="run one side configuration alone and print its figures (a small "
+                    "command to profile: cfg2 launches the full-vocabulary kernel); not a benchmark line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -442,6 +493,11 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.only:
+        peak, _ = measured_hbm_peak()
+        print(json.dumps({"only": args.only, "figures": config_figures(torch, fb, device, peak, c_softcap(), budget_s=0.5, only=args.only)}), flush=True)
+        return
 
     # ---- workload, resident in HBM before anything is timed
     tanhf = c_softcap()
@@ -562,6 +618,7 @@ def main():
             extras["warm_launch_us"] = time_launches(torch, lambda i: batch.launch(bufs[0].data_ptr()), 100)   # the same 67 MB every launch: mostly L2
             if rank == 0:
                 extras["configs"] = config_figures(torch, fb, device, peak, tanhf)
+                extras["c_call_latency"] = c_call_latency(fb)
         except Exception as ex:   # side figures must never cost the headline line
             extras["error"] = f"{type(ex).__name__}: {ex}"
         if world > 1:   # (every rank reaches this point: the figures above involve no collective and are guarded per rank)

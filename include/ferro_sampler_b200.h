@@ -301,10 +301,12 @@ FSB_API int fsb_counters(const fsb_handle* h, fsb_counters_t* out);
  *   kernel error as FSB_ERR_DEVICE; without it the call returns as soon as the work is enqueued.
  *   n_rows > FSB_STATIC_MAX_ROWS is refused with FSB_ERR_CAPACITY (the array has room for that many rows).
  * The first call on a device looks up the array's address and sets the kernel's attributes (with that device
- * current); make that first call before any stream capture begins.  All calls on a device share the one array: its
- * counters and status word must be zero when a call starts (they are when the library is loaded, every finished call
- * leaves them so, and a call that reports FSB_ERR_DEVICE clears them), and two calls whose kernels can run at the
- * same time - different streams, different threads - race on it.  Not thread-safe.  No reference counterpart. */
+ * current); make that first call before any stream capture begins.  All calls on a device share the one array: every
+ * call begins, in stream order, by clearing its counters and its status word, so a kernel error of an earlier call
+ * that nobody waited for does not leak into the next one - and is lost: a caller that does not pass FSB_STATIC_WAIT
+ * learns of kernel errors only by making a later call with it on the same input.  Two calls whose kernels can run at
+ * the same time - different streams, different threads - race on the array.  Not thread-safe.  No reference
+ * counterpart. */
 #define FSB_STATIC_MAX_ROWS 64
 #define FSB_STATIC_WAIT 1u
 FSB_API int fsb_argmax_rows_static(int device, const float* logits_dev, int64_t ld, int n_rows, int n_vocab, int32_t* tokens_dev,

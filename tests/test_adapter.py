@@ -34,3 +34,32 @@ def test_adapter_reproduces_the_reference_known_answer_vector(tmp_path):
     r = subprocess.run([_build(tmp_path)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
     assert r.stdout.split() == ["4", "2", "1", "2", "2"]
+
+
+def _build_call_latency(tmp_path):
+    gxx = shutil.which("g++")
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    if not gxx or not os.path.exists(os.path.join(cuda, "include", "cuda_runtime.h")):
+        pytest.skip("no g++ or no CUDA toolkit on this machine")
+    lib = fb.library_path()
+    fb.load_library()
+    exe = str(tmp_path / "call_latency")
+    cmd = [gxx, "-std=c++17", "-O2", "-Wall", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda, "include"),
+           os.path.join(ROOT, "tests", "call_latency.cpp"), "-L", os.path.dirname(lib), "-lferro_sampler_b200", "-Wl,-rpath," + os.path.dirname(lib),
+           "-L", os.path.join(cuda, "lib64"), "-lcudart", "-o", exe]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    return exe
+
+
+def test_call_latency_driver_compiles(tmp_path):
+    _build_call_latency(tmp_path)
+
+
+@pytest.mark.gpu
+def test_call_latency_driver_runs_every_public_call(tmp_path):
+    import json
+    r = subprocess.run([_build_call_latency(tmp_path), "34", "8192", "64", "5"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["rows"] == 34 and all(v > 0 for k, v in out.items() if k.endswith("_us"))
