@@ -38,6 +38,7 @@ struct Stream {
     int64_t pool_off = -1;
     int pool_class = -1;
     int64_t dev_len = 0;
+    uint64_t seen = 0;   // number of the last call that listed this stream (a stream may appear once per call)
 };
 
 }  // namespace
@@ -91,6 +92,7 @@ struct fsb_handle {
     int32_t vocab_offset = 0;
     int32_t global_vocab = 0;          // vocabulary sharding: columns of the whole row (0: this engine holds whole rows)
     int launch_overlap = 0;
+    uint64_t call_no = 0;              // counts the calls that check their streams for duplicates
     std::vector<Stream> streams;
     std::vector<int> free_ids;
     // device scratch shared by all batches of this handle
@@ -234,7 +236,9 @@ int finalize_batch(fsb_handle* h, fsb_batch* b) {
 }
 
 int upload_batch(fsb_handle* h, fsb_batch* b) {
-    FSB_CUDA(h, cudaMemcpyAsync(b->d_in, b->h_in, b->in_bytes_used(), cudaMemcpyHostToDevice, h->stream));
+    // descriptors, then (behind room for cap_rows of them) window ids and tables: one copy, cut short when only descriptors go up
+    const size_t bytes = (b->hist_ids + b->table_ints == 0) ? sizeof(fsb::RowDesc) * (size_t)b->n_rows : b->in_bytes_used();
+    FSB_CUDA(h, cudaMemcpyAsync(b->d_in, b->h_in, bytes, cudaMemcpyHostToDevice, h->stream));
     return FSB_OK;
 }
 
@@ -829,11 +833,12 @@ int fsb_sample_batch_resident(fsb_handle* h, int n_rows, const int* stream_ids, 
     if (rc) return rc;
     const bool append = (flags & FSB_APPEND_SAMPLED) != 0;
     // validate first, without touching any engine: known streams, each at most once, room for the new ids
+    ++h->call_no;
     for (int i = 0; i < n_rows; ++i) {
         Stream* s = get_stream(h, stream_ids[i]);
         if (!s) return fail(h, FSB_ERR_STREAM_ID, "row %d: unknown stream id %d", i, stream_ids[i]);
-        for (int j = 0; j < i; ++j)
-            if (stream_ids[j] == stream_ids[i]) return fail(h, FSB_ERR_INVALID, "stream %d appears twice in one resident batch", stream_ids[i]);
+        if (s->seen == h->call_no) return fail(h, FSB_ERR_INVALID, "stream %d appears twice in one resident batch", stream_ids[i]);
+        s->seen = h->call_no;
     }
     int64_t gather = 0;
     for (int i = 0; i < n_rows; ++i) {
@@ -914,11 +919,12 @@ static int verify_windows_impl(fsb_handle* h, int n_streams, const int* stream_i
     if (rc) return rc;
     // validate, size the staging
     int64_t need = 0;
+    ++h->call_no;
     for (int i = 0; i < n_streams; ++i) {
         Stream* s = get_stream(h, stream_ids[i]);
         if (!s) return fail(h, FSB_ERR_STREAM_ID, "stream %d: unknown stream id %d", i, stream_ids[i]);
-        for (int j = 0; j < i; ++j)
-            if (stream_ids[j] == stream_ids[i]) return fail(h, FSB_ERR_INVALID, "stream id %d appears twice", stream_ids[i]);
+        if (s->seen == h->call_no) return fail(h, FSB_ERR_INVALID, "stream id %d appears twice", stream_ids[i]);
+        s->seen = h->call_no;
         const int m = row_off[i + 1] - row_off[i];
         const int64_t len = resident ? (int64_t)s->hist.size() : hist_off[i + 1] - hist_off[i];
         if (m <= 0 || len < 0) return fail(h, FSB_ERR_INVALID, "stream %d: empty window or bad history offsets", i);
