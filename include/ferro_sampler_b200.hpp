@@ -9,7 +9,7 @@
 //     tests/test_kernels.cpp:351-353   Sampler s(p); s.sample(lg.data(), (int)lg.size(), std::vector<int>{1, 2, 3})
 // One call samples one row through the C ABI (host logits are staged to the device; the penalised entries are
 // written back into the caller's row, as the reference modifies it in place).  Schedulers that want the batched
-// path call fsb_sample_batch / fsb_verify_windows directly: see BatchedSampler below.
+// path call fsb_sample_batch / fsb_verify_windows directly, or ferro::sample_rows below.
 //
 // Unlike the reference class this one can fail (no device, CUDA error): failures throw std::runtime_error.
 #pragma once
