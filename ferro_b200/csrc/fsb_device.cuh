@@ -156,6 +156,7 @@ struct SharedCtl {
     int need_compact;                 // a lane's queue is nearly full: the CTA must re-select
     int abort;                        // a copy did not land in time
     u64 ev_bound;                     // composite bound of the latest re-selection (0: nothing was dropped)
+    int rank[kMaxK];                  // ranks of the entries while a list is ordered
     int recv_n[8];                    // clustered CTAs: candidates CTA r of the row's cluster has put into part r - 1 of the receive buffer (entry r)
     SegCtx seg;
 };
@@ -269,76 +270,38 @@ struct TailOut {
     unsigned* status;
 };
 
-// Bitonic sort, descending, of 32 * S values held by one warp: value i sits in slot i / 32 of lane i % 32.
-template <int S>
-__device__ __forceinline__ void warp_sort_desc(u64 (&v)[S]) {
-    const int lane = threadIdx.x & 31;
-#pragma unroll
-    for (int k2 = 2; k2 <= 32 * S; k2 <<= 1) {
-        // exchanges between register slots (partner distance >= 32); the direction of a block depends on the slot only
-#pragma unroll
-        for (int j = k2 >> 1; j >= 32; j >>= 1) {
-#pragma unroll
-            for (int q = 0; q < S; ++q) {
-                const int q2 = q ^ (j >> 5);
-                if (q < q2) {
-                    const bool up = ((q * 32) & k2) == 0;
-                    const u64 hi = max(v[q], v[q2]), lo = min(v[q], v[q2]);
-                    v[q] = up ? hi : lo;
-                    v[q2] = up ? lo : hi;
-                }
-            }
-        }
-        // exchanges between lanes
-#pragma unroll 1
-        for (int j = (k2 >> 1) < 16 ? (k2 >> 1) : 16; j > 0; j >>= 1) {
-#pragma unroll
-            for (int q = 0; q < S; ++q) {
-                const u64 o = __shfl_xor_sync(0xffffffffu, v[q], j);
-                const bool up = ((q * 32 + lane) & k2) == 0;
-                const bool lower = (lane & j) == 0;
-                v[q] = (up == lower) ? max(v[q], o) : min(v[q], o);
-            }
-        }
-    }
-}
-
 // Orders the k largest of buf[0..n) (distinct composites in shared memory; fewer if n < k) into out[0..kk),
 // descending, and returns kk = min(n, k).  Long lists are first cut down to k by bisection.  What is left (at most
-// kMaxK entries) is cut into runs of 32: warp w sorts run w in registers and puts it back; then the thread that
-// holds entry i of a run finds by binary search how many entries of every other run are larger - the sum, plus i,
-// is the entry's rank.  buf is overwritten (with room for the last run's padding: 32 * ceil(n / 32) entries); `out`
-// has room for kMaxK composites and must not overlap buf.  All consumer threads must call, after a barrier that
-// made buf visible; out is visible to all on return.
+// kMaxK entries) is ranked by counting: entry e is looked after by kThreads / n threads, each of which counts the
+// larger entries in its part of the list - two per 16-byte broadcast read, no dependency between the reads - and
+// the parts are added up with one shared-memory atomic each.  buf (16-byte aligned, room for one entry of padding)
+// is overwritten; `out` has room for kMaxK composites and must not overlap buf; the ranks live in ctl->rank.  All
+// consumer threads must call, after a barrier that made buf visible; out is visible to all on return.
 static __device__ __forceinline__ int topk_sorted(u64* buf, int n, int k, u64* out, SharedCtl* ctl) {
-    static_assert(kMaxK <= 32 * kNumWarps, "one run per warp");
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     if (n > kMaxK) n = select_list_topk(buf, n, k, out, ctl);
-    const int runs = (n + 31) >> 5;
-    u64 c = 0ull;   // 0 is below every composite: padding sorts to the end of the last run
-    if (warp < runs) {
-        u64 v[1];
-        v[0] = tid < n ? buf[tid] : 0ull;
-        warp_sort_desc<1>(v);
-        c = v[0];
-        buf[tid] = c;
+    if (n <= 0) return 0;
+    const int parts = kThreads / n;                    // >= 2 threads per entry
+    const int part = tid / n, e = tid - part * n;
+    if (tid < kMaxK) ctl->rank[tid] = 0;
+    if (tid == 0 && (n & 1)) buf[n] = 0ull;            // padding: 0 is below every composite
+    consumer_sync();
+    if (part < parts) {
+        const u64 c = buf[e];
+        const int per = (((n + parts - 1) / parts) + 1) & ~1;   // entries per part, even: parts start on 16-byte boundaries
+        const int j0 = part * per, j1 = min(n, j0 + per);
+        int larger = 0;
+#pragma unroll 4
+        for (int j = j0; j < j1; j += 2) {
+            const ulonglong2 v = *reinterpret_cast<const ulonglong2*>(buf + j);
+            larger += (v.x > c ? 1 : 0) + (v.y > c ? 1 : 0);
+        }
+        if (larger) atomicAdd(&ctl->rank[e], larger);
     }
     consumer_sync();
-    if (c != 0ull) {
-        int rank = lane;
-#pragma unroll
-        for (int r2 = 0; r2 < kMaxK / 32; ++r2) {
-            if (r2 < runs && r2 != warp) {
-                const u64* run = buf + 32 * r2;   // descending: count its entries above c
-                int lo = 0;
-#pragma unroll
-                for (int step = 16; step > 0; step >>= 1)
-                    if (run[lo + step - 1] > c) lo += step;
-                if (run[lo] > c) ++lo;
-                rank += lo;
-            }
-        }
-        if (rank < k) out[rank] = c;
+    if (tid < n) {
+        const int r = ctl->rank[tid];
+        if (r < k) out[r] = buf[tid];
     }
     consumer_sync();
     return n < k ? n : k;

@@ -567,7 +567,8 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
         *reinterpret_cast<volatile int*>(&ctl->need_compact) = 1;
     }
     if (mark) trace_mark(a, 2);
-    pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
+    if (mark && a.trace && tid == 0) a.trace[(size_t)blockIdx.x * 8 + 3] = (u64)n_el;
+    if (a.overlap == 1) pdl_wait_prior();   // from here on this launch writes what the previous launch in the stream may still be using
     // the segment's k best logits (or all, if fewer), in order
     const int first_cta = (row * T) / Q, last_cta = (row * T + T - 1) / Q;
     const int nseg = last_cta - first_cta + 1;

@@ -91,7 +91,8 @@ FSB_API int fsb_set_softcap(fsb_handle* h, float cap);
  * the first 4096 x 8 for the full-vocabulary kernel), the kernels write time stamps of their phases there.  The
  * streaming kernel: word 0 %globaltimer (ns) at the CTA's start and word 7 the SM's cycle counter at the same
  * moment; words 1, 4, 2, 5, 6 the cycle counter after set-up, after the CTA's last tile, after the candidate list of
- * its last segment, after ordering / merging, and at the end.  NULL (the default) turns it off.  No reference
+ * its last segment, after ordering / merging, and at the end; word 3 the length of that candidate list.  NULL (the
+ * default) turns it off.  No reference
  * counterpart. */
 FSB_API int fsb_set_trace_buffer(fsb_handle* h, void* device_buffer);
 
