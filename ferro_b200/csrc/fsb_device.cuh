@@ -261,6 +261,8 @@ struct RowTail {
 
 struct TailOut {
     int32_t* tokens;
+    int32_t* tokens_host;   // mirror of the tokens in mapped host memory, or null
+    unsigned* status_host;  // takes a non-zero word whenever a status bit is set, or null
     int32_t* kept_ids;
     double* kept_pr;
     int32_t* kept_n;
@@ -307,6 +309,17 @@ static __device__ __forceinline__ int topk_sorted(u64* buf, int n, int k, u64* o
     return n < k ? n : k;
 }
 
+// A status bit for the host: the device word collects the bits, the host mirror (if any) just becomes non-zero.
+__device__ __forceinline__ void report_status(unsigned* status, unsigned* status_host, unsigned bit) {
+    atomicOr(status, bit);
+    if (status_host) *reinterpret_cast<volatile unsigned*>(status_host) = bit;
+}
+// A row's token: to the device array and, if the caller reads its own memory, to the host mirror.
+__device__ __forceinline__ void put_token(int32_t* tokens, int32_t* tokens_host, int index, int token) {
+    tokens[index] = token;
+    if (tokens_host) tokens_host[index] = token;
+}
+
 // srt[0..kk) holds the row's candidates in order (largest first).  Either hands them out (vocabulary-sharded mode)
 // or finishes the row: softmax over the candidates in fp64, sequential sums in candidate order, min-p, top-p,
 // draw.  `work` is scratch for 2 * kMaxK doubles that does not overlap srt.  All consumer threads must call it with
@@ -317,10 +330,10 @@ static __device__ __forceinline__ void row_epilogue(const u64* srt, int kk, cons
     double* P = work + kMaxK;
     if (kk <= 0) {   // nothing but NaNs in the row
         if (tid == 0) {
-            atomicOr(o.status, kStatusEmptyRow);
+            report_status(o.status, o.status_host, kStatusEmptyRow);
             if (o.shard_out && o.shard_n) o.shard_n[r.out_index] = 0;
             else if (o.shard_out) o.shard_out[(size_t)r.out_index * o.shard_stride] = 0ull;
-            else o.tokens[r.out_index] = 0;
+            else put_token(o.tokens, o.tokens_host, r.out_index, 0);
             if (o.kept_n) o.kept_n[r.out_index] = 0;
         }
         return;
@@ -338,7 +351,7 @@ static __device__ __forceinline__ void row_epilogue(const u64* srt, int kk, cons
     }
     if (r.flags & kRowGreedy) {   // first index of the maximum (src/sampler.cpp:19-23)
         if (tid == 0) {
-            o.tokens[r.out_index] = comp_id(srt[0]);
+            put_token(o.tokens, o.tokens_host, r.out_index, comp_id(srt[0]));
             if (o.kept_n) o.kept_n[r.out_index] = 0;
         }
         return;
@@ -394,7 +407,7 @@ static __device__ __forceinline__ void row_epilogue(const u64* srt, int kk, cons
     consumer_sync();
     const int i2 = ctl->imin2;
     const int pick = (i2 != 0x7fffffff) ? i2 : keep - 1;
-    if (tid == 0) o.tokens[r.out_index] = comp_id(srt[pick]);
+    if (tid == 0) put_token(o.tokens, o.tokens_host, r.out_index, comp_id(srt[pick]));
     if (o.kept_n) {
         if (tid < keep) {
             o.kept_ids[(size_t)r.out_index * kMaxK + tid] = comp_id(srt[tid]);

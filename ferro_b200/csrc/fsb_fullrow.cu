@@ -128,6 +128,8 @@ struct FullArgs {
     const RowDesc* rows;      // the rows of this kernel
     const int32_t* hist;
     int32_t* tokens;
+    int32_t* tokens_host;     // mirror of the tokens in mapped host memory, or null
+    unsigned* status_host;    // takes a non-zero word whenever a status bit is set, or null
     int32_t* kept_ids;        // [rows][kMaxK]
     double* kept_pr;          // [rows][kMaxK]; also the staging of the kept set's first candidates while they are gathered
     int32_t* kept_n;
@@ -549,8 +551,8 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
     const int out = d.out_index;
     if (cmax == 0ull) {   // nothing but NaNs
         if (rank == 0 && tid == 0) {
-            atomicOr(a.status, kStatusEmptyRow);
-            a.tokens[out] = 0;
+            report_status(a.status, a.status_host, kStatusEmptyRow);
+            put_token(a.tokens, a.tokens_host, out, 0);
             a.kept_n[out] = 0;
         }
         cluster_sync_all();   // no CTA leaves while another may still read its shared memory
@@ -668,7 +670,7 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
     if (!draw_from_list) {
         const Crossing ct = cluster_descent(rc, sh, c_k, cmax, target, false, have_l1, false, par);
         const u64 c_tok = (ct.found && ct.c >= c_keep) ? ct.c : c_keep;
-        if (rank == 0 && tid == 0) a.tokens[out] = comp_id(c_tok);
+        if (rank == 0 && tid == 0) put_token(a.tokens, a.tokens_host, out, comp_id(c_tok));
     }
     FTR(8);
 
@@ -728,7 +730,7 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
             }
             __syncthreads();
             if (tid == 0) {
-                if (draw_from_list) a.tokens[out] = comp_id(by_rank_c[sh->pick]);
+                if (draw_from_list) put_token(a.tokens, a.tokens_host, out, comp_id(by_rank_c[sh->pick]));
                 a.kept_n[out] = (int)n_keep;
             }
         }
@@ -751,15 +753,17 @@ int prepare_full_row_kernel(int max_vocab) {
     return (int)e;
 }
 
-int launch_full_row_kernel(const float* logits, const RowDesc* rows, int n_rows, const int32_t* hist, int32_t* tokens, int32_t* kept_ids,
-                           double* kept_pr, int32_t* kept_n, int record, uint32_t* status, int n_vocab, int vocab_offset, int write_back,
-                           float softcap, uint64_t* trace, void* stream) {
+int launch_full_row_kernel(const float* logits, const RowDesc* rows, int n_rows, const int32_t* hist, int32_t* tokens, int32_t* tokens_host,
+                           int32_t* kept_ids, double* kept_pr, int32_t* kept_n, int record, uint32_t* status, uint32_t* status_host, int n_vocab,
+                           int vocab_offset, int write_back, float softcap, uint64_t* trace, void* stream) {
     if (n_vocab > (1 << 22)) return (int)cudaErrorInvalidValue;   // the histogram's limb sums are sized for 4 M logits
     FullArgs a{};
     a.logits = logits;
     a.rows = rows;
     a.hist = hist;
     a.tokens = tokens;
+    a.tokens_host = tokens_host;
+    a.status_host = status_host;
     a.kept_ids = kept_ids;
     a.kept_pr = kept_pr;
     a.kept_n = kept_n;

@@ -63,6 +63,11 @@ struct StreamArgs {
     uint32_t* ticket;          // [n_rows] segments that have finished (self-resetting)
     int32_t* tokens;           // output tokens, indexed by RowDesc::out_index
     uint32_t* status;          // one word, OR of kStatus* bits
+    // optional mirror in mapped host memory (device addresses of pinned host words; null = off): tokens are stored
+    // there as well, and a non-zero word is stored to status_host whenever a status bit is set, so that a synchronous
+    // caller needs no copy back - it waits for the stream and reads its own memory
+    int32_t* tokens_host;
+    uint32_t* status_host;
     // optional kept-set record, indexed by out_index (null = off)
     int32_t* kept_ids;         // [rows][kMaxK]
     double* kept_pr;           // [rows][kMaxK]
@@ -124,8 +129,8 @@ int launch_gather_patched(const float* logits, const RowDesc* rows, int n_rows, 
 // Defined in fsb_fullrow.cu.
 size_t full_row_smem_bytes(int n_vocab);
 int prepare_full_row_kernel(int max_vocab);
-int launch_full_row_kernel(const float* logits, const RowDesc* rows, int n_rows, const int32_t* hist, int32_t* tokens, int32_t* kept_ids,
-                           double* kept_pr, int32_t* kept_n, int record, uint32_t* status, int n_vocab, int vocab_offset, int write_back,
-                           float softcap, uint64_t* trace, void* stream);
+int launch_full_row_kernel(const float* logits, const RowDesc* rows, int n_rows, const int32_t* hist, int32_t* tokens, int32_t* tokens_host,
+                           int32_t* kept_ids, double* kept_pr, int32_t* kept_n, int record, uint32_t* status, uint32_t* status_host, int n_vocab,
+                           int vocab_offset, int write_back, float softcap, uint64_t* trace, void* stream);
 
 }  // namespace fsb

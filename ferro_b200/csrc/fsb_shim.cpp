@@ -58,6 +58,8 @@ struct fsb_batch {
     // pinned host staging: [RowDesc x cap_rows][int32 x cap_hist], tokens, gathered window values
     unsigned char* h_in = nullptr;
     int32_t* h_tokens = nullptr;
+    int32_t* h_tokens_dev = nullptr;   // the device's address of h_tokens (pinned memory is mapped): kernels mirror tokens and a status flag there
+    bool mirrored = false;            // the last launch wrote the mirror: tokens need no copy back
     float* h_patched = nullptr;
     // device
     unsigned char* d_in = nullptr;
@@ -71,7 +73,11 @@ struct fsb_batch {
 
     fsb::RowDesc* h_rows() const { return reinterpret_cast<fsb::RowDesc*>(h_in); }
     int32_t* h_hist() const { return reinterpret_cast<int32_t*>(h_in + sizeof(fsb::RowDesc) * (size_t)cap_rows); }
-    fsb::RowDesc* d_rows() const { return reinterpret_cast<fsb::RowDesc*>(d_in); }
+    // where the kernels read the descriptors: the device copy, or the pinned host block itself through its device address
+    // (see upload_batch)
+    fsb::RowDesc* d_rows() const { return rows_from_host ? reinterpret_cast<fsb::RowDesc*>(h_in_dev) : reinterpret_cast<fsb::RowDesc*>(d_in); }
+    unsigned char* h_in_dev = nullptr;
+    bool rows_from_host = false;
     int32_t* d_hist() const { return reinterpret_cast<int32_t*>(d_in + sizeof(fsb::RowDesc) * (size_t)cap_rows); }
     // the kernels' status word sits right behind the tokens, so that one copy brings both back
     uint32_t* d_status() const { return reinterpret_cast<uint32_t*>(d_tokens + cap_rows); }
@@ -174,6 +180,14 @@ int alloc_batch(fsb_handle* h, int cap_rows, int64_t cap_hist, int64_t patched, 
     const size_t in_bytes = sizeof(fsb::RowDesc) * (size_t)cap_rows + sizeof(int32_t) * (size_t)cap_hist;
     cudaError_t e = cudaMallocHost(reinterpret_cast<void**>(&b->h_in), in_bytes);
     if (e == cudaSuccess) e = cudaMallocHost(reinterpret_cast<void**>(&b->h_tokens), sizeof(int32_t) * ((size_t)cap_rows + 1));
+    if (e == cudaSuccess && cudaHostGetDevicePointer(reinterpret_cast<void**>(&b->h_in_dev), b->h_in, 0) != cudaSuccess) {
+        b->h_in_dev = nullptr;
+        cudaGetLastError();
+    }
+    if (e == cudaSuccess && cudaHostGetDevicePointer(reinterpret_cast<void**>(&b->h_tokens_dev), b->h_tokens, 0) != cudaSuccess) {
+        b->h_tokens_dev = nullptr;   // no mapping on this system: tokens come back by copy
+        cudaGetLastError();
+    }
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->d_in), in_bytes);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&b->d_tokens), sizeof(int32_t) * ((size_t)cap_rows + 1));
     if (e == cudaSuccess) e = cudaMemset(b->d_tokens, 0, sizeof(int32_t) * ((size_t)cap_rows + 1));
@@ -235,15 +249,32 @@ int finalize_batch(fsb_handle* h, fsb_batch* b) {
     return FSB_OK;
 }
 
-int upload_batch(fsb_handle* h, fsb_batch* b) {
+// Sends what the kernels need to know about the batch.  `lone_launch`: the sampling kernels are the only readers of the
+// descriptors (nothing is appended, gathered or drafted on the device afterwards).  Then, if only descriptors are to be
+// sent, the batch is one wave of CTAs and long enough to hide a read across PCIe behind its first tiles (measured on
+// B200: 64 x 262144 gains 6 us per call, 8 x 65536 nothing, one row loses 2 us), nothing is copied at all: the kernels
+// read the descriptors from the pinned host block.
+int upload_batch(fsb_handle* h, fsb_batch* b, bool lone_launch = false) {
     // descriptors, then (behind room for cap_rows of them) window ids and tables: one copy, cut short when only descriptors go up
+    b->rows_from_host = false;
+    if (lone_launch && b->hist_ids + b->table_ints == 0 && b->h_in_dev && b->n_rows <= h->sm_count &&
+        (int64_t)b->n_rows * b->n_vocab >= ((int64_t)4 << 20)) {
+        b->rows_from_host = true;
+        return FSB_OK;
+    }
     const size_t bytes = (b->hist_ids + b->table_ints == 0) ? sizeof(fsb::RowDesc) * (size_t)b->n_rows : b->in_bytes_used();
     FSB_CUDA(h, cudaMemcpyAsync(b->d_in, b->h_in, bytes, cudaMemcpyHostToDevice, h->stream));
     return FSB_OK;
 }
 
 int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep_kept, uint64_t* shard_out = nullptr,
-                 int32_t* shard_n = nullptr, int shard_stride = fsb::kMaxK) {
+                 int32_t* shard_n = nullptr, int shard_stride = fsb::kMaxK, bool mirror = false) {
+    // `mirror`: the caller is about to wait for the tokens - the kernels store them (and a flag for any status bit) into
+    // the batch's pinned host words as well, and fetch_tokens only waits for the stream
+    int32_t* tokens_host = (mirror && b->h_tokens_dev) ? b->h_tokens_dev : nullptr;
+    uint32_t* status_host = tokens_host ? reinterpret_cast<uint32_t*>(tokens_host + b->cap_rows) : nullptr;
+    if (tokens_host) b->h_tokens[b->cap_rows] = 0;
+    b->mirrored = tokens_host != nullptr;
     if (shard_out && b->n_full > 0)
         return fail(h, FSB_ERR_RANGE, "rows whose candidate count exceeds %d (top_k = 0 or large) cannot be sharded by vocabulary", fsb::kMaxK);
     const int32_t* hist = b->hist_dev ? b->hist_dev : b->d_hist();
@@ -257,8 +288,8 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
             FSB_CUDA(h, cudaStreamWaitEvent(h->side, h->ev_fork, 0));
             where = h->side;
         }
-        const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, hist, b->d_tokens,
-                                                  h->d_kept_ids, h->d_kept_pr, h->d_kept_n, keep_kept ? 1 : 0, b->d_status(), b->n_vocab, h->vocab_offset,
+        const int e = fsb::launch_full_row_kernel(logits_dev, b->d_rows() + b->n_cand, b->n_full, hist, b->d_tokens, tokens_host,
+                                                  h->d_kept_ids, h->d_kept_pr, h->d_kept_n, keep_kept ? 1 : 0, b->d_status(), status_host, b->n_vocab, h->vocab_offset,
                                                   (b->flags & FSB_WRITE_BACK) ? 1 : 0, h->softcap, h->d_trace ? h->d_trace + 4096 * 8 : nullptr, where);
         if (e != 0) return fail(h, FSB_ERR_CUDA, "full-row kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         h->counters.kernel_launches++;
@@ -273,6 +304,8 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.ticket = h->d_counters;
         a.tokens = b->d_tokens;
         a.status = b->d_status();
+        a.tokens_host = tokens_host;
+        a.status_host = status_host;
         a.kept_ids = keep_kept ? h->d_kept_ids : nullptr;
         a.kept_pr = keep_kept ? h->d_kept_pr : nullptr;
         a.kept_n = keep_kept ? h->d_kept_n : nullptr;
@@ -308,10 +341,15 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
 
 // Tokens and the status word behind them in one copy; `extra` floats of gathered window values in a second one.
 int fetch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out, int64_t patched = 0) {
-    FSB_CUDA(h, cudaMemcpyAsync(b->h_tokens, b->d_tokens, sizeof(int32_t) * ((size_t)b->cap_rows + 1), cudaMemcpyDeviceToHost, h->stream));
+    if (!b->mirrored)
+        FSB_CUDA(h, cudaMemcpyAsync(b->h_tokens, b->d_tokens, sizeof(int32_t) * ((size_t)b->cap_rows + 1), cudaMemcpyDeviceToHost, h->stream));
     if (patched > 0) FSB_CUDA(h, cudaMemcpyAsync(b->h_patched, b->d_patched, sizeof(float) * (size_t)patched, cudaMemcpyDeviceToHost, h->stream));
     FSB_CUDA(h, cudaStreamSynchronize(h->stream));
-    const unsigned st = (unsigned)b->h_tokens[b->cap_rows];
+    unsigned st = (unsigned)b->h_tokens[b->cap_rows];
+    if (st != 0u && b->mirrored) {   // the mirror only says "something": the device word has the bits
+        uint32_t word = 0;
+        if (cudaMemcpy(&word, b->d_status(), sizeof word, cudaMemcpyDeviceToHost) == cudaSuccess && word != 0u) st = word;
+    }
     if (st != 0u) {
         // put the self-resetting counters and the status word back into their idle state
         cudaMemsetAsync(h->d_counters, 0, sizeof(uint32_t) * h->counter_words(), h->stream);
@@ -493,7 +531,7 @@ int run_staged(fsb_handle* h, fsb_batch* b, const float* logits, unsigned flags,
                bool window_append = false) {
     const bool on_host = (flags & FSB_LOGITS_ON_HOST) != 0;
     const bool host_wb = on_host && (flags & FSB_WRITE_BACK) && b->gather_ids > 0;
-    int rc = upload_batch(h, b);
+    int rc = upload_batch(h, b, !append && window_streams == 0 && !host_wb);
     const float* dev = logits;
     if (rc == FSB_OK && on_host) rc = stage_host_logits(h, logits, b->n_rows, b->ld, b->n_vocab, &dev);
     if (rc == FSB_OK && window_streams > 0) {
@@ -501,7 +539,7 @@ int run_staged(fsb_handle* h, fsb_batch* b, const float* logits, unsigned flags,
         if (e != 0) rc = fail(h, FSB_ERR_CUDA, "draft kernel launch: %s", cudaGetErrorString((cudaError_t)e));
         else h->counters.kernel_launches++;
     }
-    if (rc == FSB_OK) rc = launch_batch(h, b, dev, (flags & FSB_KEEP_KEPT_SET) != 0);
+    if (rc == FSB_OK) rc = launch_batch(h, b, dev, (flags & FSB_KEEP_KEPT_SET) != 0, nullptr, nullptr, fsb::kMaxK, true);
     if (rc == FSB_OK && window_streams > 0 && window_append) {
         const int e = fsb::launch_accept_windows(b->d_hist() + b->hist_ids, window_streams, b->d_tokens, h->d_pool, h->stream);
         if (e != 0) rc = fail(h, FSB_ERR_CUDA, "accept kernel launch: %s", cudaGetErrorString((cudaError_t)e));

@@ -473,7 +473,7 @@ __device__ __forceinline__ void producer_loop(const StreamArgs& a, float* stage,
         // the first kStages tiles find their slots free; later ones wait for the consumers' hand-back
         if (i >= kStages && !mbar_try_wait(&ctl->empty[slot], (unsigned)((i / kStages - 1) & 1))) {
             if (clock64() - t_last > kCopyWaitCycles) {   // the consumers never came back: report and stop
-                atomicOr(a.status, kStatusCopyTimeout);
+                report_status(a.status, a.status_host, kStatusCopyTimeout);
                 return;
             }
             continue;
@@ -512,7 +512,7 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
     const int T = a.tiles_per_row, V = a.n_vocab, Q = a.tiles_per_cta;
     const RowDesc d = a.rows[row];
     unsigned* myq = m.queue + tid;
-    const TailOut tout{a.tokens, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.shard_stride, a.status};
+    const TailOut tout{a.tokens, a.tokens_host, a.status_host, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.shard_stride, a.status};
     float thr_final;
     int n_el;
     for (;;) {
@@ -648,7 +648,7 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
             for (int i = tid; i < kk; i += kThreads) dst[seg * d.k + i] = m.sorted[i];
             if (tid == 0) dst[kMergeCap - 1 - seg] = (u64)kk;
         } else if (tid == 0) {
-            atomicOr(a.status, kStatusMergeOverflow);
+            report_status(a.status, a.status_host, kStatusMergeOverflow);
         }
         consumer_sync();   // orders the CTA's stores before the ticket, whose release publishes them to the device
         if (tid == 0) ctl->last = (ticket_add_acq_rel(&a.ticket[row], 1u) == (unsigned)(nseg - 1)) ? 1 : 0;
@@ -820,7 +820,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
                             if (__any_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&ctl->need_compact) != 0)) break;
                             if (clock64() - t0 > lim) {   // the copy never landed: report, carry on with what is there
                                 ctl->abort = 1;
-                                atomicOr(a.status, kStatusCopyTimeout);
+                                report_status(a.status, a.status_host, kStatusCopyTimeout);
                                 landed = true;
                                 break;
                             }

@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(kThreads, 1) merge_lists_kernel(const u64* lis
         }
     }
     consumer_sync();
-    const TailOut tout{tokens, kept_ids, kept_pr, kept_n, nullptr, nullptr, 0, status};
+    const TailOut tout{tokens, nullptr, nullptr, kept_ids, kept_pr, kept_n, nullptr, nullptr, 0, status};
     const RowTail rt{d.rng_word, d.temperature, d.top_p, d.min_p, d.k_global, d.flags, d.out_index};
     const int kk = topk_sorted(buf, total, d.k_global, out, ctl);
     row_epilogue(out, kk, rt, reinterpret_cast<double*>(buf), ctl, tout);
