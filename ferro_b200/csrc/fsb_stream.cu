@@ -972,7 +972,7 @@ Plan make_plan(int n_rows, int n_vocab, int kmax, int slots) {
             const int nseg = T / c;
             const double busy = std::min(1.0, (double)n_rows * nseg / slots);
             const bool on_chip = (nseg == 2 || nseg == 4 || nseg == 8) && (nseg - 1) * std::max(1, kmax) <= 512;   // a cluster per row
-            const double merge = nseg == 1 ? 0.0 : on_chip ? (nseg == 2 ? 1.4 : nseg == 4 ? 2.0 : 3.3)
+            const double merge = nseg == 1 ? 0.0 : on_chip ? (nseg == 2 ? 1.4 : nseg == 4 ? 2.8 : 4.3)
                                  : nseg <= 8 ? 2.4 + 0.25 * nseg : nseg <= 16 ? 4.4 + 0.5 * nseg : 10.0 + 0.3 * nseg;
             const double cost = (0.4 + 0.2 * busy) * c + merge;
             if (cost < best) {
