@@ -96,6 +96,22 @@ def test_full_vocabulary_rows_too_long_for_shared_memory(oracle):
         eng.close()
 
 
+def test_many_rows_dealt_as_equal_runs_of_tiles(engine, oracle):
+    """300 rows of 262144 logits on 148 SMs would be three waves of whole-row CTAs; the planner deals the 9600 tiles
+    in equal runs instead, so a CTA works through two rows and a bit, and most rows straddle two CTAs."""
+    B, V = 300, 262144
+    rng = np.random.default_rng(300)
+    lg = (rng.standard_normal((B, V), dtype=np.float32) * 3).astype(np.float32)
+    lg[:, ::9] = np.round(lg[:, ::9])
+    p = fb.make_params(B, temperature=0.8, top_k=40, top_p=0.9, min_p=0.01, repetition_penalty=1.1)
+    p["temperature"][::5] = 0.0
+    p["top_k"][1::7] = 200
+    p["seed"] = 3000 + np.arange(B)
+    hists = [rng.integers(0, V, size=300).astype(np.int32) for _ in range(B)]
+    _, _, hard, near, kept_bad = run_batch(engine, oracle, lg, p, hists)
+    assert not hard and not kept_bad and near <= 1, (hard[:3], near, kept_bad[:3])
+
+
 def test_unaligned_rows_take_the_plain_load_path(engine, oracle):
     import torch
     rng = np.random.default_rng(7)
