@@ -246,8 +246,8 @@ FSB_API int fsb_batch_redraw(fsb_handle* h, fsb_batch* b);
 FSB_API int fsb_batch_launch(fsb_handle* h, fsb_batch* b, const float* logits_dev);
 /* Wait for the last launch of `b` and copy its tokens (n_rows int32) to host memory. */
 FSB_API int fsb_batch_tokens(fsb_handle* h, fsb_batch* b, int32_t* tokens_out);
-/* Vocabulary sharding: this device holds columns [offset, offset + n_vocab) of every row (fsb_set_vocab_offset gives
- * the offset; history ids stay global).  fsb_batch_shard_launch runs the streaming kernel on the shard and leaves,
+/* Vocabulary sharding: this device holds columns [offset, offset + n_vocab) of every row (fsb_set_vocab_shard gives
+ * the offset and the width of the whole row; history ids stay global).  fsb_batch_shard_launch runs the streaming kernel on the shard and leaves,
  * per row, the shard's best k candidates in descending order: `lists_out_dev` is [n_rows][FSB_MAX_CANDIDATE_K]
  * 64-bit keys (order-preserving value key << 32 | 0xFFFFFFFF - global token id), `counts_out_dev` [n_rows] how many
  * are valid.  The caller brings the lists of all shards into this device's memory (an all-gather: [n_lists][n_rows]
