@@ -208,8 +208,20 @@ def bind_to_gpu_numa_node(local_rank):
             bus = bus[4:]   # sysfs uses a four-digit domain
         node_file = f"/sys/bus/pci/devices/{bus}/numa_node"
         node = int(open(node_file).read().strip())
-        if node < 0:
-            return "numa node unknown"
+        if node < 0:   # sysfs does not say (virtual machines): ask NVML for the GPU's ideal CPUs (a read-only query)
+            try:
+                import pynvml
+                pynvml.nvmlInit()
+                words = pynvml.nvmlDeviceGetCpuAffinity(pynvml.nvmlDeviceGetHandleByIndex(local_rank), 16)
+                ideal = {64 * w + b for w, x in enumerate(words) for b in range(64) if (int(x) >> b) & 1}
+            except Exception:
+                return "numa node unknown"
+            here = os.sched_getaffinity(0)
+            allowed = sorted(ideal & here)
+            if not allowed or len(allowed) == len(here):
+                return f"one numa node visible ({len(here)} cpus): nothing to bind"
+            os.sched_setaffinity(0, allowed)
+            return f"nvml cpu affinity, {len(allowed)} of {len(here)} cpus"
         cpus = open(f"/sys/devices/system/node/node{node}/cpulist").read().strip()
         ids = []
         for part in cpus.split(","):
