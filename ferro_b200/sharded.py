@@ -7,10 +7,10 @@ collective at all; ``row_partition`` gives the blocks and ``gather_tokens`` an o
 Vocabulary sharding is for a logits matrix that is split by columns (a tensor-parallel LM head leaves columns
 [g V/G, (g+1) V/G) of every row on GPU g).  Every rank selects the best k candidates of its columns and writes
 them as packed lists - per row one count word and k candidates, (k + 1) x 8 bytes, 168 KB for 512 rows at k = 40.
-Then, by default, one all-to-all hands every rank the G lists of its own block of rows (row_partition), the merge
-kernel finishes that block, and one all-gather of 4 bytes per row leaves all tokens on all ranks; the alternative
-(``exchange="all_gather"``) gathers all lists everywhere and every rank merges every row - one collective instead
-of two, G times the bytes and G times the merge work.  The global top-k is a subset of the union of the shards'
+Then either one all-to-all hands every rank the G lists of its own block of rows (row_partition), the merge
+kernel finishes that block, and one all-gather of 4 bytes per row leaves all tokens on all ranks; or
+(``exchange="all_gather"``) all lists are gathered everywhere and every rank merges every row - one collective instead
+of two, G times the bytes and G times the merge work, the faster route up to four ranks and the default there.  The global top-k is a subset of the union of the shards'
 top-k lists and the (value descending, id ascending) order does not depend on the split, so the result is the
 unsharded one.  Rows with top_k = 0 (the whole vocabulary is the candidate set) cannot be done this way: shard
 those by rows.
@@ -154,9 +154,11 @@ class VocabShardedSampler:
     shard launch, exchange, merge, token exchange, all queued on the current CUDA stream - and ``tokens`` waits and
     returns the ids; ``sample`` does all three for one-off use."""
 
-    def __init__(self, engine, n_vocab: int, rank: int, world: int, group=None, exchange: str = "all_to_all"):
+    def __init__(self, engine, n_vocab: int, rank: int, world: int, group=None, exchange: str = "auto"):
+        if exchange == "auto":   # measured on B200: one all-gather is the faster route at two and four ranks
+            exchange = "all_gather" if world <= 4 else "all_to_all"
         if exchange not in ("all_to_all", "all_gather"):
-            raise ValueError("exchange is 'all_to_all' or 'all_gather'")
+            raise ValueError("exchange is 'auto', 'all_to_all' or 'all_gather'")
         self.engine, self.rank, self.world, self.group, self.exchange = engine, rank, world, group, exchange
         self.n_vocab = n_vocab
         self.lo, self.hi = vocab_partition(n_vocab, world)[rank]
