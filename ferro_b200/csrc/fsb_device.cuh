@@ -136,6 +136,7 @@ struct SegCtx {
     int has_pen;
     int id_base;        // token id of column 0
     int seg_lo;         // first column of the segment (= column of bit 0 of the bitmap)
+    int seg_hi;         // one past its last column
     int n_vocab;
     int vec_ok;         // rows start on 16-byte boundaries
     int k;              // the row's candidate count

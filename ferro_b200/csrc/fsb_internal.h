@@ -88,6 +88,8 @@ struct StreamArgs {
     int32_t vocab_offset;      // token id of column 0
     float softcap;             // 0 = off
     int32_t overlap;           // launch with programmatic stream serialization (see fsb_set_launch_overlap)
+    int32_t all_greedy;        // every row of the launch is greedy: the variant of the kernel that keeps one best logit per lane
+                               // instead of queues of candidates
     int32_t pair;              // 0, or c = 2, 4, 8: every row is exactly c aligned CTAs (c r .. c r + c - 1), launched as a cluster
                                // whose CTAs hand their candidates to the first one through shared memory instead of the row's scratch
 };

@@ -51,6 +51,7 @@ struct fsb_batch {
     int64_t cap_hist = 0;
     int n_cand = 0, n_full = 0;   // rows of the candidate kernel / of the full-row kernel
     int kmax = 1;
+    bool all_greedy = false;      // every row of the streaming kernel is greedy
     fsb::Plan plan;               // how the candidate rows are dealt to the CTAs of the streaming kernel
     int64_t hist_ids = 0;         // window ids staged with the batch
     int64_t gather_ids = 0;       // window values a write-back for a host caller brings back
@@ -234,11 +235,14 @@ int finalize_batch(fsb_handle* h, fsb_batch* b) {
     int n_cand = 0, kmax = 1;
     fsb::RowDesc* dst = b->h_rows();
     auto on_chip = [](const fsb::RowDesc& d) { return d.k <= fsb::kMaxK && d.k_global <= fsb::kMaxK; };
+    bool all_greedy = true;
     for (const auto& d : b->descs)
         if (on_chip(d)) {
             dst[n_cand++] = d;
             kmax = std::max(kmax, d.k);
+            all_greedy = all_greedy && (d.flags & fsb::kRowGreedy) != 0;
         }
+    b->all_greedy = all_greedy && n_cand > 0;
     int n_full = 0;
     for (const auto& d : b->descs)
         if (!on_chip(d)) dst[n_cand + n_full++] = d;
@@ -324,6 +328,7 @@ int launch_batch(fsb_handle* h, fsb_batch* b, const float* logits_dev, bool keep
         a.vocab_offset = h->vocab_offset;
         a.softcap = h->softcap;
         a.overlap = h->launch_overlap;
+        a.all_greedy = b->all_greedy ? 1 : 0;
         const int grid = (a.total_tiles + a.tiles_per_cta - 1) / a.tiles_per_cta;
         // rows of exactly 2, 4 or 8 aligned segments: the CTAs of a row run as a cluster and exchange candidates on chip
         a.pair = 0;

@@ -503,8 +503,11 @@ __device__ __forceinline__ void producer_loop(const StreamArgs& a, float* stage,
 // The end of a segment.  All consumer threads call it once they have looked at their last tile of the segment:
 // re-selections that were still asked for, the rendez-vous of the finished warps, the element list, the segment's
 // k best logits in order, and - in the CTA that draws the row's last ticket - the merge and the row's epilogue.
-template <bool SOFTCAP>
-__device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn, int nkept, float thr_f, float run_max, bool mark) {
+// With GREEDY (a launch whose rows are all greedy: a verification step, the static entry point) the streaming loop has
+// kept no queues: every lane brings the best logit it saw as a composite (`lane_best`, 0 = none), the CTA takes the
+// largest, and that one candidate goes through the same merge and epilogue as an ordered list of length one.
+template <bool SOFTCAP, bool GREEDY>
+__device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn, int nkept, float thr_f, float run_max, bool mark, u64 lane_best) {
     const Smem m = smem_view();
     SharedCtl* ctl = m.ctl;
     const SegCtx& sc = ctl->seg;
@@ -514,8 +517,30 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
     unsigned* myq = m.queue + tid;
     const TailOut tout{a.tokens, a.tokens_host, a.status_host, a.kept_ids, a.kept_pr, a.kept_n, reinterpret_cast<u64*>(a.shard_out), a.shard_n, a.shard_stride, a.status};
     float thr_final;
-    int n_el;
-    for (;;) {
+    int n_el = 0;
+    int kk = 0;
+    if (GREEDY) {
+        u64 mn = lane_best ? lane_best : ~0ull, mx = lane_best;
+        cta_minmax(mn, mx, ctl);
+        if (mx == 0ull && !SOFTCAP) {
+            // No lane saw anything above minus infinity.  A segment of nothing but -inf (and NaN) still has an argmax in
+            // the reference - its first -inf - so look for one in memory (the penalty leaves -inf as it is).
+            u64 mine = 0ull;
+            for (int c = sc.seg_lo + tid; c < sc.seg_hi; c += kThreads) {
+                const float x = __ldcg(sc.row + c);
+                if (x == -__int_as_float(0x7f800000)) mine = max(mine, make_comp(x, c + sc.id_base));
+            }
+            mn = mine ? mine : ~0ull;
+            mx = mine;
+            cta_minmax(mn, mx, ctl);
+        }
+        if (mark) trace_mark(a, 4);
+        if (tid == 0) m.sorted[0] = mx;
+        consumer_sync();
+        kk = mx != 0ull ? 1 : 0;
+        n_el = kk;
+    }
+    for (; !GREEDY;) {
         for (;;) {   // re-selections that were still asked for, then the rendez-vous of the finished warps
             const int ev = cta_event<SOFTCAP>(qn, nkept, run_max, thr_f);
             if (!event_happened(ev)) break;
@@ -573,7 +598,7 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
     const int first_cta = (row * T) / Q, last_cta = (row * T + T - 1) / Q;
     const int nseg = last_cta - first_cta + 1;
     bool merge_here = true;
-    int kk = topk_sorted(m.list, n_el, d.k, m.sorted, ctl);
+    if (!GREEDY) kk = topk_sorted(m.list, n_el, d.k, m.sorted, ctl);
     if (a.pair) {
         // The row's CTAs are a cluster: CTA r > 0 puts its ordered candidates into part r - 1 of CTA 0's receive
         // buffer, all arrive at the cluster's barrier (the only phase of it in this kernel: the producer warps arrived
@@ -707,7 +732,7 @@ __device__ __forceinline__ void segment_end(const StreamArgs& a, int row, int qn
     if (mark) trace_mark(a, 6);
 }
 
-template <bool SOFTCAP>
+template <bool SOFTCAP, bool GREEDY>
 __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const __grid_constant__ StreamArgs a) {
     const Smem m = smem_view();
     SharedCtl* ctl = m.ctl;
@@ -770,6 +795,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
             sc.has_pen = has_pen ? 1 : 0;
             sc.id_base = a.vocab_offset;
             sc.seg_lo = seg_lo;
+            sc.seg_hi = seg_hi;
             sc.n_vocab = V;
             sc.vec_ok = a.bulk_ok;
             sc.k = row_k;
@@ -788,6 +814,10 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
         consumer_sync();
 
         float thr_f = ninf, run_max = ninf;
+        // GREEDY: the lane's best logit so far - the cell it sits in, that cell's first column, the cell's maximum
+        float4 best_cell = make_float4(0.f, 0.f, 0.f, 0.f);
+        float best = ninf;
+        int best_col = -1;
         u64 thr_comp = 0ull;
         int qn = 0;       // cells in this lane's queue
         int nkept = 0;    // cells in the survivors' list (the same value in every thread)
@@ -799,7 +829,7 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
                               // 2 = another warp asked for a re-selection while this one was waiting for a copy
             unsigned slot = (unsigned)it % kStages, par = ((unsigned)it / kStages) & 1u;   // ring slot of tile `it` and its phase
             for (; s < seg_nt; ++s, ++it, col0 += kTile, slot = (slot + 1u) % kStages, par ^= (slot == 0u ? 1u : 0u)) {
-                if (__any_sync(0xffffffffu, qn > kLaneQueue - 4)) {
+                if (!GREEDY && __any_sync(0xffffffffu, qn > kLaneQueue - 4)) {
                     reason = 1;
                     break;
                 }
@@ -853,6 +883,15 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
                 run_max = fmaxf(max3(run_max, m0, m1), fmaxf(m2, m3));
                 __syncwarp();
                 if (lane == 0 && a.bulk_ok) mbar_arrive(&ctl->empty[slot]);   // the slot goes back to the producer
+                if (GREEDY) {
+                    // the lane meets its cells in ascending column order, so "strictly larger" keeps the first of equals
+                    const int c0 = col0 + 4 * lane;
+                    if (m0 > best) { best = m0; best_cell = x0; best_col = c0; }
+                    if (m1 > best) { best = m1; best_cell = x1; best_col = c0 + 128; }
+                    if (m2 > best) { best = m2; best_cell = x2; best_col = c0 + 256; }
+                    if (m3 > best) { best = m3; best_cell = x3; best_col = c0 + 384; }
+                    continue;
+                }
 
                 // ---- the admission bound: set at the segment's first tile (all warps must have posted: one barrier per
                 // segment), then refreshed without a barrier at tiles 1, 2, 4, 8, ... of the segment
@@ -897,7 +936,12 @@ __global__ void __launch_bounds__(kBlockThreads, 1) stream_select_kernel(const _
                 }
             }
         }
-        segment_end<SOFTCAP>(a, row, qn, nkept, thr_f, run_max, tile + seg_nt >= t_end);
+        u64 lane_best = 0ull;
+        if (GREEDY && best_col >= 0) {   // the first logit of the cell that equals its maximum (-0 and +0 are equal here and in a composite)
+            const int e = best_cell.x == best ? 0 : best_cell.y == best ? 1 : best_cell.z == best ? 2 : 3;
+            lane_best = make_comp(best, best_col + e + a.vocab_offset);
+        }
+        segment_end<SOFTCAP, GREEDY>(a, row, qn, nkept, thr_f, run_max, tile + seg_nt >= t_end, lane_best);
         tile += seg_nt;
     }
 }
@@ -908,12 +952,16 @@ size_t stream_kernel_smem_bytes() { return kSmemTotal; }
 
 // Per-device set-up (the current device): opt in to the large dynamic shared memory; report resident CTAs per SM.
 int prepare_device_kernels(int* ctas_per_sm) {
-    cudaError_t e = cudaFuncSetAttribute(stream_select_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
+    cudaError_t e = cudaFuncSetAttribute(stream_select_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(stream_select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
+    e = cudaFuncSetAttribute(stream_select_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(stream_select_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(stream_select_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemTotal);
     if (e != cudaSuccess) return (int)e;
     int n = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, stream_select_kernel<false>, kBlockThreads, kSmemTotal);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, stream_select_kernel<false, false>, kBlockThreads, kSmemTotal);
     if (e != cudaSuccess) return (int)e;
     if (ctas_per_sm) *ctas_per_sm = n;
     return 0;
@@ -941,8 +989,12 @@ int launch_stream_kernel(const StreamArgs& a, int grid, void* stream) {
     cfg.stream = static_cast<cudaStream_t>(stream);
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    if (a.softcap != 0.0f) return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<true>, a);
-    return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<false>, a);
+    if (a.all_greedy) {
+        if (a.softcap != 0.0f) return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<true, true>, a);
+        return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<false, true>, a);
+    }
+    if (a.softcap != 0.0f) return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<true, false>, a);
+    return (int)cudaLaunchKernelEx(&cfg, stream_select_kernel<false, false>, a);
 }
 
 // The launch plan (host).  A row's scratch holds kMergeCap entries: k candidates and a count per segment.
@@ -1084,6 +1136,7 @@ extern "C" int fsb_argmax_rows_static(int device, const float* logits_dev, int64
         int q = (a.total_tiles + sd.slots - 1) / sd.slots;   // equal contiguous ranges of tiles, one per resident CTA
         q = q < 1 ? 1 : (q > kMaxTilesPerCta ? kMaxTilesPerCta : q);
         a.tiles_per_cta = q;
+        a.all_greedy = 1;
         a.bulk_ok = ((reinterpret_cast<uintptr_t>(logits_dev) & 15u) == 0 && (ld & 3) == 0) ? 1 : 0;
         if (rc != FSB_OK) {
         } else if (2 * ((a.tiles_per_row + q - 1) / q + 1) > kMergeCap) {   // one candidate and one count per segment

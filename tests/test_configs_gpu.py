@@ -171,3 +171,36 @@ def test_full_size_serving_batch_tokens_lie_in_the_top_k(engine, oracle):
     for s in sids:
         engine.close_stream(int(s))
     assert not hard and not kept_bad and near <= 1
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+def test_greedy_rows_with_masked_logits(engine, oracle, mixed):
+    """A launch whose rows are all greedy runs the variant of the streaming kernel that keeps one best logit per lane;
+    a mixed launch runs the general one.  Both must give the reference's argmax for rows that are mostly - or wholly -
+    minus infinity (a fully masked row has its first logit as argmax, src/sampler.cpp:19-23), with ties and a penalty."""
+    B, V = 6, 70001
+    rng = np.random.default_rng(55)
+    lg = (rng.standard_normal((B, V)) * 2).astype(np.float32)
+    lg[0, :] = -np.inf                                   # wholly masked
+    lg[1, :] = -np.inf
+    lg[1, 40000] = -3.5                                  # one survivor
+    lg[2, :] = 1.25                                      # all equal: the first wins
+    lg[3, 10:] = -np.inf                                 # the maximum in the first cells
+    lg[4, ::3] = np.round(lg[4, ::3])
+    p = fb.make_params(B, temperature=0.0, top_k=50, repetition_penalty=1.3)
+    if mixed:
+        p["temperature"][5] = 0.9
+    p["seed"] = 70 + np.arange(B)
+    hists = [rng.integers(0, V, size=50).astype(np.int32) for _ in range(B)]
+    hists[3] = np.arange(0, 10, dtype=np.int32)          # the penalty moves the maximum among the first ten
+    ref = oracle.sample_rows(p, oracle.new_rngs(p["seed"]), lg.copy(), hists)
+    sids = engine.open_streams(p)
+    try:
+        import torch
+        tok_host = engine.sample_batch(sids, lg.copy(), hists)
+        tok_dev = engine.sample_batch(engine.open_streams(p), torch.from_numpy(lg).cuda(), hists, n_vocab=V)
+    finally:
+        for s_ in sids:
+            engine.close_stream(int(s_))
+    assert np.array_equal(tok_host, ref["tokens"]) and np.array_equal(tok_dev, ref["tokens"])
+    assert tok_host[0] == 0 and tok_host[1] == 40000 and tok_host[2] == 0
