@@ -40,7 +40,7 @@ METRIC, UNIT = "sampled_rows_per_s", "rows/s"
 WORKLOAD = "cfg3: B=64 x V=262144 fp32, Student-t(3)*4 softcap 30, T=1 top_k=64 top_p=0.95, penalty 1.0/1.1 alternating, 512-id histories"
 # DRAM traffic of one launch of the streaming kernel on this workload, from the committed ncu summary
 # (profiles/stream_select_kernel_cfg3.md: dram__bytes_read.sum + dram__bytes_write.sum)
-NCU_TRAFFIC_BYTES = 68.44e6   # dram__bytes_read.sum + dram__bytes_write.sum per launch, mean of two captured launches (profiles/stream_select_kernel_cfg3.md)
+NCU_TRAFFIC_BYTES = 68.57e6   # dram__bytes_read.sum + dram__bytes_write.sum per launch, mean of two captured launches (profiles/stream_select_kernel_cfg3.md)
 
 
 def algorithmic_bytes(rows=ROWS, vocab=VOCAB, hist=HIST):
