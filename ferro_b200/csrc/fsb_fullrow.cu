@@ -29,6 +29,7 @@ namespace {
 
 constexpr int kFullThreads = 1024;
 constexpr int kFullWarps = kFullThreads / 32;
+static_assert(kFullWarps == 32, "the block reductions read one partial per lane");
 constexpr int kFullCluster = 8;                 // CTAs per row
 constexpr int kSliceCache = 32768;              // logits of a slice that are kept in shared memory (rows up to 8 x this)
 constexpr int kStripes = 8;                     // copies of the level histogram (by warp): fewer warps hit one word at once
@@ -173,10 +174,37 @@ __device__ __forceinline__ u64 block_max_u64(u64 v, FullShared* sh) {
     for (int o = 16; o; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
     if (lane == 0) sh->red[warp] = v;
     __syncthreads();
-    u64 r = sh->red[0];
-    for (int w = 1; w < kFullWarps; ++w) r = max(r, sh->red[w]);
+    u64 r = sh->red[lane];   // kFullWarps == 32: one partial per lane
+#pragma unroll
+    for (int o = 16; o; o >>= 1) r = max(r, __shfl_xor_sync(0xffffffffu, r, o));
     __syncthreads();
     return r;
+}
+
+// Largest `hi` and smallest `lo` over the CTA in one go.
+__device__ __forceinline__ void block_max2_u64(u64& hi, u64& lo, FullShared* sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    u64 a = hi, b = ~lo;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        a = max(a, __shfl_xor_sync(0xffffffffu, a, o));
+        b = max(b, __shfl_xor_sync(0xffffffffu, b, o));
+    }
+    if (lane == 0) {
+        sh->red[warp] = a;
+        sh->red_hi[warp] = b;
+    }
+    __syncthreads();
+    a = sh->red[lane];
+    b = sh->red_hi[lane];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        a = max(a, __shfl_xor_sync(0xffffffffu, a, o));
+        b = max(b, __shfl_xor_sync(0xffffffffu, b, o));
+    }
+    __syncthreads();
+    hi = a;
+    lo = ~b;
 }
 
 // Exchanges up to four 64-bit values per CTA across the cluster: every CTA gets all kFullCluster x 4 values.
@@ -222,9 +250,9 @@ __device__ __forceinline__ void block_sum_u128(U128& v, unsigned& cnt, FullShare
 // Adds (digit, weight, one candidate) to the level histogram: native 32-bit shared-memory atomics on the count and on
 // the weight's non-zero 16-bit limbs.  The lanes of a warp spread over the stripes, and the stripes start in
 // different banks, so that lanes with the same digit seldom meet in one word.
-__device__ __forceinline__ void hist_add(FullShared* sh, bool active, int digit, u64 weight, bool weighted) {
+__device__ __forceinline__ void hist_add(FullShared* sh, bool active, int digit, u64 weight, bool weighted, unsigned stripe_mask) {
     if (!active) return;
-    unsigned* h = &sh->h[threadIdx.x & (kStripes - 1)][digit];
+    unsigned* h = &sh->h[threadIdx.x & stripe_mask][digit];
     atomicAdd(h + kLimbs * 256, 1u);
     if (weighted) {
         const unsigned l0 = (unsigned)(weight & 0xFFFFull), l1 = (unsigned)((weight >> 16) & 0xFFFFull);
@@ -252,7 +280,7 @@ struct Crossing {
 // before it in shared memory; digit -1 if the target is beyond all candidates.  If `keep_l1`, the cluster-wide
 // histogram is also stored for later descents.  All threads of all CTAs of the cluster must call.
 __device__ __forceinline__ void level_reduce_and_walk(FullShared* sh, int par, U128 target, U128 above, unsigned above_cnt, bool by_count,
-                                                      bool keep_l1, bool from_l1) {
+                                                      bool keep_l1, bool from_l1, unsigned stripe_mask) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     u64 lo = 0ull, hi = 0ull;
     unsigned cnt = 0u;
@@ -267,7 +295,7 @@ __device__ __forceinline__ void level_reduce_and_walk(FullShared* sh, int par, U
             u64 l0 = 0ull, l1 = 0ull, l2 = 0ull, l3 = 0ull;   // limb sums over the stripes: below 2^35 each
             unsigned c = 0u;
 #pragma unroll
-            for (int s = 0; s < kStripes; ++s) {
+            for (int s = 0; s <= (int)stripe_mask; ++s) {
                 l0 += sh->h[s][tid];
                 l1 += sh->h[s][256 + tid];
                 l2 += sh->h[s][512 + tid];
@@ -382,10 +410,15 @@ __device__ Crossing cluster_descent(const RowCtx& rc, FullShared* sh, u64 floor_
         const int w = hb + 1 < 8 ? hb + 1 : 8, lo = hb + 1 - w;
         const unsigned dmask = (1u << w) - 1u;
         const bool from_l1 = first && use_l1;
+        // the first level sees every candidate, a few digits take most of them: eight stripes keep the lanes of a warp
+        // apart.  Deeper levels see the few candidates that match the prefix: one stripe, an eighth of the clearing
+        // and adding up.
+        // (a 16-bit limb summed over one stripe stays below 2^32 for slices of up to 65536 logits)
+        const unsigned stripe_mask = (first || rc.n > 65536) ? (unsigned)(kStripes - 1) : 0u;
         const bool dbg = rc.dbg && build_l1;
         if (dbg) rc.dbg[16] = global_timer_ns();
         if (!from_l1) {
-            for (int i = tid; i < (int)(sizeof(sh->h) / sizeof(uint4)); i += kFullThreads)
+            for (int i = tid; i < (int)((stripe_mask + 1u) * sizeof(sh->h[0]) / sizeof(uint4)); i += kFullThreads)
                 reinterpret_cast<uint4*>(&sh->h[0][0])[i] = make_uint4(0u, 0u, 0u, 0u);
             __syncthreads();
             if (dbg) rc.dbg[17] = global_timer_ns();
@@ -406,12 +439,12 @@ __device__ Crossing cluster_descent(const RowCtx& rc, FullShared* sh, u64 floor_
                         }
                     }
                 }
-                hist_add(sh, active, digit, wgt, !by_count);
+                hist_add(sh, active, digit, wgt, !by_count, stripe_mask);
             }
             __syncthreads();
             if (dbg) rc.dbg[18] = global_timer_ns();
         }
-        level_reduce_and_walk(sh, par, target, above, above_cnt, by_count, first && build_l1, from_l1);
+        level_reduce_and_walk(sh, par, target, above, above_cnt, by_count, first && build_l1, from_l1, stripe_mask);
         if (dbg) rc.dbg[19] = global_timer_ns();
         if (!from_l1) par ^= 1;
         first = false;
@@ -438,13 +471,14 @@ __device__ Crossing cluster_descent(const RowCtx& rc, FullShared* sh, u64 floor_
                 if (c >= floor_c && (c & mask) == pfx) mine = c;
             }
         }
-        mine = block_max_u64(mine, sh);
-        u64 v[4] = {mine, 0ull, 0ull, 0ull}, all[kFullCluster][4];
-        cluster_exchange(sh, par, v, all);
+        // exactly one thread of the cluster holds it: that thread tells every CTA, one barrier makes it visible
+        if (mine != 0ull) {
+#pragma unroll
+            for (unsigned r = 0; r < (unsigned)kFullCluster; ++r) cluster_store_u64(map_to_rank(&sh->x_small[par][0], r), mine);
+        }
+        cluster_sync_all();
+        pfx = sh->x_small[par][0];
         par ^= 1;
-        u64 c = 0ull;
-        for (int r = 0; r < kFullCluster; ++r) c = max(c, all[r][0]);
-        pfx = c;
     }
     out.c = pfx;
     out.above = above;
@@ -537,8 +571,7 @@ __global__ void __launch_bounds__(kFullThreads, 1) full_row_kernel(const FullArg
     }
     FTR(1);
     // ---- 1. the row's extremes
-    cmax = block_max_u64(cmax, sh);
-    cmin = ~block_max_u64(~cmin, sh);
+    block_max2_u64(cmax, cmin, sh);
     {
         u64 v[4] = {cmax, ~cmin, 0ull, 0ull}, all[kFullCluster][4];
         cluster_exchange(sh, par, v, all);
