@@ -782,7 +782,9 @@ size_t full_row_smem_bytes(int n_vocab) {
 }
 
 int prepare_full_row_kernel(int max_vocab) {
-    cudaError_t e = cudaFuncSetAttribute(full_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)full_row_smem_bytes(max_vocab));
+    // the largest request of any row length up to max_vocab: rows that still fit the slice cache need the most
+    const size_t most = std::max(full_row_smem_bytes(max_vocab), full_row_smem_bytes(std::min(max_vocab, kFullCluster * kSliceCache)));
+    cudaError_t e = cudaFuncSetAttribute(full_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
     return (int)e;
 }
 

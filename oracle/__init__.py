@@ -123,7 +123,7 @@ class Oracle:
         tokens = np.zeros(B, dtype=np.int32)
         n_keep = np.zeros(B, dtype=np.int32)
         words = np.zeros(B, dtype=np.uint64)
-        r_tot = np.zeros((B, 2), dtype=np.float64)
+        r_tot = np.zeros((B, 3), dtype=np.float64)   # r, tot, probability of the last kept candidate
         kept_ids = np.full((B, max(cap, 1)), -1, dtype=np.int32)
         kept_pr = np.zeros((B, max(cap, 1)), dtype=np.float64)
         rc = self.lib.oracle_sample_rows(B, params.ctypes.data, rngs.ctypes.data, logits.ctypes.data, V, V,

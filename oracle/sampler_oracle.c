@@ -130,7 +130,8 @@ int64_t oracle_window_begin(const oracle_params* p, int64_t hist_len) {
  *   n_keep                       size of the kept set after min-p / top-p
  *   n_cand                       k, the number of candidates that entered the softmax
  *   rng_word                     the raw 64-bit engine output consumed (0 for greedy)
- *   r_tot[2]                     {r, tot} of the draw
+ *   r_tot[3]                     {r, tot} of the draw, and the probability of the last kept candidate (tot minus it is
+ *                                the cumulative probability the top-p cut saw just before its last step)
  * Returns the token id, or -1 on allocation failure.
  */
 int oracle_sample(const oracle_params* p, oracle_mt64* rng, float* logits, int n, const int* hist, int64_t hist_len,
@@ -200,7 +201,7 @@ int oracle_sample(const oracle_params* p, oracle_mt64* rng, float* logits, int n
     if (n_keep) *n_keep = (int)keep;
     if (n_cand) *n_cand = k;
     if (rng_word) *rng_word = w;
-    if (r_tot) { r_tot[0] = r; r_tot[1] = tot; }
+    if (r_tot) { r_tot[0] = r; r_tot[1] = tot; r_tot[2] = pr[keep - 1]; }
     for (size_t i = 0; i < keep && (int)i < cap; ++i) {
         if (kept_ids) kept_ids[i] = c[i].id;
         if (kept_pr) kept_pr[i] = pr[i];
@@ -222,7 +223,7 @@ int oracle_sample_rows(int n_rows, const oracle_params* params, oracle_mt64* rng
         int t = oracle_sample(&params[i], rngs ? &rngs[i] : NULL, logits + (int64_t)i * ld, n,
                               hist_flat + hist_off[i], hist_off[i + 1] - hist_off[i],
                               kept_ids ? kept_ids + (int64_t)i * cap : NULL, kept_pr ? kept_pr + (int64_t)i * cap : NULL, cap,
-                              n_keep ? n_keep + i : NULL, NULL, rng_words ? rng_words + i : NULL, r_tot ? r_tot + 2 * i : NULL);
+                              n_keep ? n_keep + i : NULL, NULL, rng_words ? rng_words + i : NULL, r_tot ? r_tot + 3 * i : NULL);
         if (t < 0) return -1;
         tokens[i] = t;
     }

@@ -90,6 +90,15 @@ def compare_with_oracle(engine, tokens, ref, params, V, check_kept=True):
         if check_kept and k > 1:
             ids, pr, n = engine.last_kept(i)
             nk = int(ref["n_keep"][i])
+            if n != nk and abs(n - nk) == 1 and params[i]["top_p"] < 1.0:
+                # The top-p cut sits on a boundary of the cumulative distribution: the reference's sequential sum
+                # reached top_p (or missed it) by rounding alone, e.g. equal probabilities that add up to exactly top_p.
+                # Counted like a draw that lands on a boundary; what both kept is still compared.
+                tot, last = ref["r_tot"][i, 1], ref["r_tot"][i, 2]
+                if min(abs(tot - params[i]["top_p"]), abs(tot - last - params[i]["top_p"])) < CDF_TOL:
+                    near += 1
+                    nk = n = min(n, nk)
+                    ids, pr = ids[:n], pr[:n]
             if k <= fb.MAX_CANDIDATE_K:
                 if n != nk or (ids != ref["kept_ids"][i, :nk]).any() or np.abs(pr - ref["kept_pr"][i, :nk]).max() > PROB_TOL:
                     kept_bad.append(i)

@@ -86,6 +86,13 @@ def test_full_vocabulary_rows_too_long_for_shared_memory(oracle):
     eng = fb.Engine(device=0, max_rows=B, max_vocab=V, max_hist_ids=B * 2100 + 16)
     try:
         rng = np.random.default_rng(8128)
+        # the same engine must also take shorter rows, whose slices do fit (and need more shared memory than the long ones)
+        for v2 in (262144, 5000):
+            lg, p, hists = random_case(rng, B, v2, 1, allow_full=True)
+            p["top_k"][0] = 0
+            p["temperature"][0] = 1.0
+            _, _, hard, near, kept_bad = run_batch(eng, oracle, lg, p, hists)
+            assert not hard and not kept_bad and near <= 1, (v2, hard[:3], kept_bad[:3])
         for trial in range(3):
             lg, p, hists = random_case(rng, B, V, trial, allow_full=True)
             p["top_k"][0] = 0                                   # at least one row takes the full-vocabulary kernel
