@@ -70,8 +70,8 @@ __global__ void append_tokens_kernel(const RowDesc* rows, int n_rows, const int3
 
 // Resident verification windows.  Before the launch: draft r of a stream is the last id of row r's window, and goes
 // to that place of the id pool.  After it: per stream the accept loop of src/server.cpp:630-636 over the sampled
-// tokens (accept while the token equals the next draft, at most `lim` rows), and the last accepted token is stored
-// where the history will end - the confirmed drafts before it are in place already.  Table entry of a stream:
+// tokens (accept while the token equals the next draft, at most `lim` rows), and the accepted tokens are stored
+// behind the history.  Table entry of a stream:
 // first row, rows m, limit, unused, end of the history in the pool (two words), then the m - 1 drafts.
 __global__ void write_drafts_kernel(const RowDesc* rows, int n_rows, int32_t* pool) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -90,7 +90,9 @@ __global__ void accept_windows_kernel(const int32_t* table, int n_streams, const
         if (r + 1 < m && tokens[r0 + r] == t[6 + r]) continue;
         break;
     }
-    if (acc > 0) pool[end + acc - 1] = tokens[r0 + acc - 1];
+    // every accepted token, not only the last: a row whose penalty window is empty (penalty off) never had its draft
+    // written into the pool before the launch
+    for (int r = 0; r < acc; ++r) pool[end + r] = tokens[r0 + r];
 }
 
 // Prompt-lookup drafting over resident histories (lookup_draft, src/server.cpp:552-564): the tokens that followed

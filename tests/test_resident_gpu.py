@@ -197,3 +197,45 @@ def test_prompt_lookup_drafts_of_resident_histories_match_the_oracle(engine, ora
     finally:
         for s in sids:
             engine.close_stream(int(s))
+
+
+def test_resident_windows_of_streams_without_a_penalty_keep_their_device_history(engine, oracle):
+    """A stream whose penalty is off has empty penalty windows, so its drafts are never written into the id pool before
+    the launch; the accepted tokens must still reach the device copy of its history (the drafting kernel reads it)."""
+    S, V, m = 4, 33, 5                                     # a tiny vocabulary: n-grams repeat, the lookup finds matches
+    rng = np.random.default_rng(4711)
+    p = fb.make_params(S, temperature=0.8, top_k=10, top_p=0.9, repetition_penalty=1.2)
+    p["repetition_penalty"][:2] = 1.0                      # penalty off
+    p["repeat_last_n"][2] = 0                              # window off
+    p["temperature"][1] = 0.0
+    p["seed"] = 900 + np.arange(S)
+    sids = engine.open_streams(p)
+    rngs = oracle.new_rngs(p["seed"])
+    hists = [rng.integers(0, V, size=int(n)).astype(np.int32) for n in rng.integers(5, 30, size=S)]
+    try:
+        for i, s in enumerate(sids):
+            engine.history_set(int(s), hists[i])
+        for step in range(5):
+            lg = (rng.standard_normal((S * m, V)) * 2).astype(np.float32)
+            rows = []
+            for i in range(S):
+                drafts = rng.integers(0, V, size=m - 1).astype(np.int32)
+                h, probe = list(hists[i]), rngs[i:i + 1].copy()
+                for r in range(int(rng.integers(0, m))):           # a prefix of right drafts
+                    t = int(oracle.sample_rows(p[i:i + 1], probe, lg[i * m + r:i * m + r + 1].copy(), [np.array(h, dtype=np.int32)])["tokens"][0])
+                    if r < m - 1:
+                        drafts[r] = t
+                    h.append(t)
+                rows.append(np.concatenate([[int(hists[i][-1])], drafts]).astype(np.int32))
+            want = [oracle.verify_window(p[i:i + 1], rngs[i], lg[i * m:(i + 1) * m].copy(), rows[i], hists[i]) for i in range(S)]
+            toks, acc, conf = engine.verify_windows_resident(sids, rows, lg.copy(), n_vocab=V, flags=fb.APPEND_SAMPLED)
+            for i in range(S):
+                t, a, c, _ = want[i]
+                assert acc[i] == a and conf[i] == c and list(toks[i][:a]) == list(t[:a]), (step, i)
+                hists[i] = np.concatenate([hists[i], np.asarray(t[:a], dtype=np.int32)]).astype(np.int32)
+            got = engine.lookup_drafts(sids, 6, 1, V)               # eos outside the vocabulary: never cuts
+            for i in range(S):
+                assert list(got[i]) == list(oracle.lookup_draft(hists[i], 6, V, 1)), (step, i)
+    finally:
+        for s in sids:
+            engine.close_stream(int(s))
